@@ -1,0 +1,452 @@
+#!/usr/bin/env python
+"""Benchmark of the CSR SpMV / SpMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line (rank 0).  The default workload is the power-law SpMV the headline metric
+is quoted on: float64 values / int64 indices, 2^24 x 2^24, Zipf(1.8) row lengths with mean 16 and
+rows up to 100,000 entries, y = 1.5 * A x + 0.5 * y.  A step is one such product.
+
+  value         effective HBM GB/s = algorithmic bytes / device time, inputs resident in HBM
+  roofline      the same figure against the measured copy bandwidth of this GPU pool
+  e2e           the same product through the public API with x, y0 in pinned HOST memory and
+                y copied back, copies inside the timed region
+  cpu_baseline  the CPU oracle (oracle/, a restatement of the reference's arithmetic) timed on
+                a bounded row slice of the same matrix, all host cores
+  --impl reference   only that CPU measurement, as its own line
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank owns one row block of the same
+size (weak scaling): x is broadcast from rank 0, each rank multiplies its block, y is
+all-gathered; value counts the bytes all ranks processed over the slowest rank's time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# -------------------------------------------------------------------------------------------------
+# clocks during the timed region
+# -------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index, period_s=0.002):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.sm_max = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip() != ""]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                bits = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.sm_max,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# -------------------------------------------------------------------------------------------------
+# workloads
+# -------------------------------------------------------------------------------------------------
+def make_problem(name, device, scale, seed):
+    from flagsparse_b200 import workloads as W
+    if name == "cfg1":
+        return W.cfg1_uniform_spmv(device, scale, seed), "spmv"
+    if name == "cfg2":
+        return W.cfg2_powerlaw_spmv(device, scale, seed), "spmv"
+    if name == "cfg2mm":
+        return W.cfg2_powerlaw_spmv(device, scale, seed, n_dense=32), "spmm"
+    if name == "cfg3":
+        return W.cfg3_banded_spmm(device, scale, seed), "spmm"
+    if name == "cfg4":
+        return W.cfg4_poisson_spmm(device, scale, seed), "spmm"
+    if name == "cfg4c":
+        return W.cfg4_poisson_spmm(device, scale, seed, dtype=torch.complex64), "spmm"
+    if name == "cfg5":
+        return W.cfg5_scaling(device, scale, seed, with_B=False), "spmv"
+    if name == "cfg5mm":
+        return W.cfg5_scaling(device, scale, seed), "spmm"
+    raise SystemExit(f"unknown workload {name}")
+
+
+WORKLOAD_TEXT = {
+    "cfg1": "CSR SpMV float32/int32 65536x65536, 1..32 entries per row, alpha=1 beta=0",
+    "cfg2": "CSR SpMV float64/int64 2^24x2^24, Zipf(1.8) row lengths mean 16 max 100000, "
+            "alpha=1.5 beta=0.5",
+    "cfg2mm": "CSR SpMM float64/int64 N=32 on the 2^24-row Zipf(1.8) matrix",
+    "cfg3": "CSR SpMM float32/int32 op=non, banded 2^22x2^22 (band 64, 40% fill), N=32",
+    "cfg4": "CSR SpMM float32/int32 op=trans, 1e6 x 5e5 Poisson(24) rows, N=64",
+    "cfg4c": "CSR SpMM complex64/int32 op=conj, 1e6 x 5e5 Poisson(24) rows, N=64",
+    "cfg5": "CSR SpMV float32/int64 2^26x2^26, Zipf(2.0) row lengths mean 16",
+    "cfg5mm": "CSR SpMM float32/int64 N=16 on the 2^26-row Zipf(2.0) matrix",
+}
+
+DTYPE_TEXT = {torch.float32: "f32", torch.float64: "f64", torch.complex64: "c64",
+              torch.complex128: "c128"}
+
+
+def problem_bytes_flops(p, kind):
+    """Algorithmic bytes of one product: row_ptr + col + val + x/B once + y/C written (and read
+    when beta != 0), with the caller's index widths."""
+    from flagsparse_b200 import workloads as W
+    vb, ib, pb = p.data.element_size(), p.indices.element_size(), p.indptr.element_size()
+    op = p.extra.get("op", "non")
+    n_out, n_in = (p.shape[1], p.shape[0]) if op != "non" else p.shape
+    beta_nz = p.extra.get("beta", 0.0) != 0.0
+    if kind == "spmv":
+        b = W.spmv_bytes(n_out, n_in, p.nnz, vb, ib, pb, beta_nz)
+        f = W.sp_flops(p.nnz, 1, p.data.is_complex())
+    else:
+        n = int(p.B.shape[1])
+        b = W.spmm_bytes(n_out, n_in, p.nnz, n, vb, ib, pb, beta_nz)
+        f = W.sp_flops(p.nnz, n, p.data.is_complex())
+    return b, f
+
+
+def make_step(p, kind):
+    """Returns (step callable, output tensor, kernels launched per step)."""
+    from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr
+    op = p.extra.get("op", "non")
+    alpha, beta = p.extra.get("alpha", 1.0), p.extra.get("beta", 0.0)
+    n_out = p.shape[1] if op != "non" else p.shape[0]
+    if kind == "spmv":
+        out = p.extra["y0"].clone() if beta != 0.0 else torch.empty(
+            n_out, dtype=p.data.dtype, device=p.data.device)
+
+        def step():
+            flagsparse_spmv_csr(p.data, p.indices, p.indptr, p.x, p.shape, out=out, op=op,
+                                alpha=alpha, beta=beta)
+    else:
+        out = torch.empty((n_out, p.B.shape[1]), dtype=p.data.dtype, device=p.data.device)
+
+        def step():
+            flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape, out=out, op=op,
+                                alpha=alpha, beta=beta)
+    return step, out, 2  # tile kernel + carry fix-up kernel
+
+
+def time_device(step, steps, warmup, sampler=None):
+    """Device time of `steps` back-to-back steps (CUDA events on the launching stream)."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        start.record()
+        for _ in range(steps):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+    return start.elapsed_time(stop) / 1000.0
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+# -------------------------------------------------------------------------------------------------
+# end to end through the public API with host buffers
+# -------------------------------------------------------------------------------------------------
+def time_e2e(p, kind, steps, warmup):
+    from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr
+    op = p.extra.get("op", "non")
+    alpha, beta = p.extra.get("alpha", 1.0), p.extra.get("beta", 0.0)
+    dev = p.data.device
+    dense_dev = p.x if kind == "spmv" else p.B
+    dense_host = dense_dev.cpu().pin_memory()
+    n_out = p.shape[1] if op != "non" else p.shape[0]
+    out_shape = (n_out,) if kind == "spmv" else (n_out, p.B.shape[1])
+    y0_host = p.extra["y0"].cpu().pin_memory() if beta != 0.0 else None
+    out_host = torch.empty(out_shape, dtype=p.data.dtype).pin_memory()
+    dense_buf = torch.empty_like(dense_dev)
+    out_buf = torch.empty(out_shape, dtype=p.data.dtype, device=dev)
+    h2d = dense_host.numel() * dense_host.element_size()
+    if y0_host is not None:
+        h2d += y0_host.numel() * y0_host.element_size()
+    d2h = out_host.numel() * out_host.element_size()
+
+    def step():
+        dense_buf.copy_(dense_host, non_blocking=True)
+        if y0_host is not None:
+            out_buf.copy_(y0_host, non_blocking=True)
+        if kind == "spmv":
+            flagsparse_spmv_csr(p.data, p.indices, p.indptr, dense_buf, p.shape, out=out_buf,
+                                op=op, alpha=alpha, beta=beta)
+        else:
+            flagsparse_spmm_csr(p.data, p.indices, p.indptr, dense_buf, p.shape, out=out_buf,
+                                op=op, alpha=alpha, beta=beta)
+        out_host.copy_(out_buf, non_blocking=True)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / steps, h2d, d2h
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle port on a bounded row slice
+# -------------------------------------------------------------------------------------------------
+def cpu_baseline(p, kind, target_seconds=12.0, max_nnz=40_000_000):
+    """Rows are independent, so the first rows of the matrix holding <= max_nnz entries stand in
+    for the whole: same x / B, same arithmetic, all host cores (OpenMP over rows)."""
+    import numpy as np
+
+    import oracle
+    from flagsparse_b200 import workloads as W
+    op = p.extra.get("op", "non")
+    ptr_all = p.indptr
+    if op != "non":
+        # the transposed product is timed on the reference's route: materialise op(A) first
+        n_slice = p.shape[0]
+    else:
+        n_slice = int(torch.searchsorted(ptr_all.long(), torch.tensor(
+            [max_nnz], device=ptr_all.device), right=True).item()) - 1
+        n_slice = max(1, min(n_slice, p.shape[0]))
+    nnz_s = int(ptr_all[n_slice].item())
+    data = p.data[:nnz_s].cpu().numpy()
+    idx = p.indices[:nnz_s].cpu().numpy().astype(np.int64)
+    ptr = ptr_all[: n_slice + 1].cpu().numpy().astype(np.int64)
+    shape = (n_slice, p.shape[1])
+    vb, ib, pb = p.data.element_size(), p.indices.element_size(), p.indptr.element_size()
+    if op != "non":
+        data, idx, ptr, shape = oracle.transpose_csr(data, idx, ptr, shape, conj=(op == "conj"))
+    n_out, n_in = shape
+    if kind == "spmv":
+        dense = p.x.cpu().numpy()
+        fn = lambda: oracle.spmv_acc(data, idx, ptr, dense, shape)  # noqa: E731
+        nbytes = W.spmv_bytes(n_out, n_in, nnz_s, vb, ib, pb, p.extra.get("beta", 0.0) != 0.0)
+    else:
+        dense = p.B.cpu().numpy()
+        fn = lambda: oracle.spmm_acc(data, idx, ptr, dense, shape)  # noqa: E731
+        nbytes = W.spmm_bytes(n_out, n_in, nnz_s, dense.shape[1], vb, ib, pb, False)
+    fn()  # warm the caches and the thread pool
+    reps, t_total, best = 0, 0.0, float("inf")
+    while reps < 3 or (t_total < target_seconds and reps < 200):
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        best = min(best, dt)
+        t_total += dt
+        reps += 1
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
+    scipy_gbs = None
+    try:
+        import scipy.sparse as sp
+        A = sp.csr_matrix((data, idx, ptr), shape=shape)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            A @ dense
+        scipy_gbs = nbytes / ((time.perf_counter() - t0) / 3) / 1e9
+    except Exception:
+        pass
+    return {
+        "value": nbytes / best / 1e9,
+        "unit": "GB/s",
+        "cores": cores,
+        "kind": "port",
+        "sample": f"first {n_slice} rows ({nnz_s} non-zeros) of the same matrix, full x/B, "
+                  f"best of {reps} runs of oracle/csr_oracle.c (OpenMP over rows)",
+        "scipy_1core_gbs": scipy_gbs,
+    }
+
+
+# -------------------------------------------------------------------------------------------------
+def run_reference_arm(args, rank, world):
+    """The reference has no CPU implementation of this path (its functions reject CPU tensors
+    and its kernels are Triton); the arm times the CPU restatement of its arithmetic."""
+    if rank != 0:
+        return
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    p, kind = make_problem(args.workload, dev, args.scale, args.seed)
+    samples = []
+    base = None
+    for _ in range(max(1, args.warmup) + max(1, args.steps)):
+        base = cpu_baseline(p, kind, target_seconds=2.0)
+        samples.append(base["value"])
+    samples = samples[max(1, args.warmup):]
+    value = statistics.median(samples)
+    base["value"] = value
+    line = {
+        "impl": "reference", "metric": "effective HBM GB/s (algorithmic bytes / time)",
+        "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype], "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[args.workload], "rows": p.shape[0], "nnz": p.nnz},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOAD_TEXT))
+    ap.add_argument("--scale", type=int, default=1, help="divide the row count (debugging)")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the SpMM N=32 side measurement")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+
+    if world > 1:
+        from flagsparse_b200 import distributed as D
+        D.bench_multi_gpu(args, rank, world, local_rank, WORKLOAD_TEXT, DTYPE_TEXT)
+        return
+
+    peak, peak_kind = measured_peaks()
+    p, kind = make_problem(args.workload, device, args.scale, args.seed)
+    nbytes, flops = problem_bytes_flops(p, kind)
+    step, out, launches_per_step = make_step(p, kind)
+    step()  # builds the plan (validation, tiles, transpose) outside every timed region
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    seconds = time_device(step, args.steps, args.warmup, sampler)
+    per_step = seconds / args.steps
+    gbs = nbytes / per_step / 1e9
+
+    e2e_s, h2d, d2h = time_e2e(p, kind, max(3, min(args.steps, 10)), 3)
+
+    extra = {"gflops": flops / per_step / 1e9, "pct_of_8tbs_nominal": 100.0 * gbs / NOMINAL_HBM_GBS,
+             "algorithmic_bytes_per_step": nbytes}
+    if args.workload == "cfg2" and not args.no_extra:
+        # the second half of the target: SpMM N=32 on the same matrix
+        from flagsparse_b200 import workloads as W
+        g = torch.Generator(device=device)
+        g.manual_seed(args.seed + 1)
+        p.extra["B"] = torch.randn(p.shape[0] * 32, dtype=p.data.dtype, device=device,
+                                   generator=g).view(p.shape[0], 32)
+        saved = (p.extra.pop("alpha"), p.extra.pop("beta"))
+        mm_bytes, mm_flops = problem_bytes_flops(p, "spmm")
+        mm_step, mm_out, _ = make_step(p, "spmm")
+        mm_step()
+        torch.cuda.synchronize()
+        mm_s = time_device(mm_step, max(3, args.steps // 5), 3) / max(3, args.steps // 5)
+        extra["spmm_n32_same_matrix"] = {
+            "ms_per_step": mm_s * 1e3, "gbs": mm_bytes / mm_s / 1e9,
+            "gflops": mm_flops / mm_s / 1e9, "frac_of_measured_peak": mm_bytes / mm_s / 1e9 / peak,
+            "algorithmic_bytes_per_step": mm_bytes,
+        }
+        p.extra["alpha"], p.extra["beta"] = saved
+        del p.extra["B"], mm_out
+        torch.cuda.empty_cache()
+
+    line = {
+        "metric": "effective HBM GB/s (algorithmic bytes / time)",
+        "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype], "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[args.workload], "rows": p.shape[0], "nnz": p.nnz,
+                   "l2": "inputs_exceed_l2" if nbytes > 2 * 126e6 else "l2_resident_inputs",
+                   "seed": args.seed, "scale": args.scale},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind},
+        "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": sampler.summary(),
+        "extra": extra,
+    }
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(p, kind)
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,102 @@
+"""ctypes binding of libb200sparse.so (declarations: include/b200sparse.h).
+
+There is no fallback: if the library is missing or a call returns a non-zero status, a
+RuntimeError is raised.  Build it with ``python -m flagsparse_b200._build``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libb200sparse.so"
+
+# dtype codes of include/b200sparse.h
+B2S_F32, B2S_F64, B2S_C64, B2S_C128 = 0, 1, 2, 3
+B2S_I32, B2S_I64 = 0, 1
+B2S_ERR_TIMEOUT = 5
+
+VALUE_CODE = {
+    torch.float32: B2S_F32,
+    torch.float64: B2S_F64,
+    torch.complex64: B2S_C64,
+    torch.complex128: B2S_C128,
+}
+INDEX_CODE = {torch.int32: B2S_I32, torch.int64: B2S_I64}
+
+# every symbol include/b200sparse.h declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "b2s_version": (c_int, []),
+    "b2s_status_string": (c_char_p, [c_int]),
+    "b2s_csr_inspect": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p,
+                                c_void_p]),
+    "b2s_tile_count": (c_int64, [c_int64, c_int64, c_int]),
+    "b2s_tile_plan": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "b2s_spmv_tile_items": (c_int, [c_int, c_int]),
+    "b2s_spmm_tile_items": (c_int, [c_int, c_int]),
+    "b2s_spmv_csr": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                             c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p]),
+    "b2s_spmm_csr": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                             c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b2s_csr2csc_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "b2s_csr2csc": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                            c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                            c_void_p]),
+}
+
+_lib = None
+
+
+def load():
+    """Return the loaded library; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA extension has not been built "
+            "(run `python -m flagsparse_b200._build`). There is no CPU or Triton fallback."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = load().b2s_status_string(int(status)).decode()
+        raise RuntimeError(f"{what} failed: b2s status {status} ({msg})")
+
+
+def ptr(t):
+    """Device address of a tensor (None -> NULL)."""
+    if t is None:
+        return None
+    return c_void_p(t.data_ptr())
+
+
+def stream_handle(device) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def scalar_buffer(value, dtype):
+    """Host buffer holding one scalar of the value dtype (alpha / beta are host pointers)."""
+    if dtype == torch.float32:
+        return (ctypes.c_float * 1)(float(value))
+    if dtype == torch.float64:
+        return (ctypes.c_double * 1)(float(value))
+    z = complex(value)
+    if dtype == torch.complex64:
+        return (ctypes.c_float * 2)(z.real, z.imag)
+    if dtype == torch.complex128:
+        return (ctypes.c_double * 2)(z.real, z.imag)
+    raise TypeError(f"unsupported value dtype {dtype}")

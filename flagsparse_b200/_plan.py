@@ -1,0 +1,182 @@
+"""Per-matrix device state: the checked CSR arrays, merge-path tile plans, scratch and the
+cached transpose.  Everything here is built by kernels of libb200sparse.so; torch only owns the
+memory.
+
+A plan is found again through a small LRU cache keyed on the identity of the three CSR tensors
+(address, length, dtype, torch version counter), so that the steady-state call of
+``flagsparse_spmv_csr`` / ``flagsparse_spmm_csr`` does no validation, no host synchronisation
+and no allocation -- the role ``PreparedCsrSpmv`` plays in FlagSparse (spmv_csr.py:55-130),
+extended to SpMM, which there re-validates and re-transposes on every call
+(spmm_csr.py:3330-3390).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from collections import OrderedDict
+
+import torch
+
+from . import _lib
+
+INDEX_LIMIT_INT32 = 2**31 - 1
+
+# stats words written by b2s_csr_inspect
+ST_PTR0, ST_PTRN, ST_DECREASING, ST_MINCOL, ST_MAXCOL, ST_MAXLEN, ST_EMPTY = range(7)
+
+
+def inspect_csr(indices, indptr, n_rows, nnz):
+    """One pass over indptr / indices on the device; returns the eight statistics as ints.
+
+    This is the only host synchronisation a new matrix costs.
+    """
+    lib = _lib.load()
+    stats = torch.empty(8, dtype=torch.int64, device=indptr.device)
+    with torch.cuda.device(indptr.device):
+        st = lib.b2s_csr_inspect(
+            _lib.ptr(indptr), _lib.INDEX_CODE[indptr.dtype],
+            _lib.ptr(indices) if nnz > 0 else None, _lib.INDEX_CODE[indices.dtype],
+            n_rows, nnz, _lib.ptr(stats), _lib.stream_handle(indptr.device))
+    _lib.check(st, "b2s_csr_inspect")
+    return [int(v) for v in stats.tolist()]
+
+
+class CsrPlan:
+    """Device arrays of one CSR matrix plus everything derived from them."""
+
+    def __init__(self, data, indices, indptr, shape, max_row_nnz, keepalive=()):
+        self.data = data
+        self.indices = indices
+        self.indptr = indptr
+        self.n_rows = int(shape[0])
+        self.n_cols = int(shape[1])
+        self.shape = (self.n_rows, self.n_cols)
+        self.nnz = int(data.numel())
+        self.max_row_nnz = int(max_row_nnz)
+        self.device = data.device
+        self.vcode = _lib.VALUE_CODE[data.dtype]
+        self.icode = _lib.INDEX_CODE[indices.dtype]
+        self.pcode = _lib.INDEX_CODE[indptr.dtype]
+        self._keepalive = keepalive          # caller tensors this plan was derived from
+        self._tiles = {}                     # tile_items -> (T, int64[T+1])
+        self._scratch = {}                   # (tag, width, stream) -> tensor
+        self._transposed = {}                # conj flag -> CsrPlan of the transpose
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status_checked = False
+
+    # -- tile plans ---------------------------------------------------------------------------
+    def tiles(self, items):
+        hit = self._tiles.get(items)
+        if hit is not None:
+            return hit
+        lib = _lib.load()
+        n_tiles = int(lib.b2s_tile_count(self.n_rows, self.nnz, items))
+        tile_row = torch.empty(n_tiles + 1, dtype=torch.int64, device=self.device)
+        if n_tiles > 0:
+            with torch.cuda.device(self.device):
+                st = lib.b2s_tile_plan(_lib.ptr(self.indptr), self.pcode, self.n_rows, self.nnz,
+                                       items, _lib.ptr(tile_row),
+                                       _lib.stream_handle(self.device))
+            _lib.check(st, "b2s_tile_plan")
+        self._tiles[items] = (n_tiles, tile_row)
+        return self._tiles[items]
+
+    def scratch(self, tag, n_values, dtype=None):
+        """Scratch of n_values elements, one buffer per (purpose, size, stream)."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        key = (tag, int(n_values), stream)
+        buf = self._scratch.get(key)
+        if buf is None:
+            buf = torch.empty(max(int(n_values), 1), dtype=dtype or self.data.dtype,
+                              device=self.device)
+            self._scratch[key] = buf
+        return buf
+
+    # -- transpose ----------------------------------------------------------------------------
+    def transposed(self, conj):
+        """CsrPlan of A^T (conj=False) or A^H (conj=True), built once by b2s_csr2csc."""
+        conj = bool(conj) and self.data.dtype.is_complex
+        hit = self._transposed.get(conj)
+        if hit is not None:
+            return hit
+        lib = _lib.load()
+        if self.indices.dtype == torch.int32 and self.n_rows > INDEX_LIMIT_INT32:
+            raise ValueError("row ids of the transpose do not fit int32 indices")
+        t_data = torch.empty_like(self.data)
+        t_idx = torch.empty_like(self.indices)
+        t_ptr = torch.empty(self.n_cols + 1, dtype=self.indptr.dtype, device=self.device)
+        nbytes = int(lib.b2s_csr2csc_bytes(self.n_rows, self.n_cols, self.nnz))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            st = lib.b2s_csr2csc(self.vcode, self.icode, self.pcode, _lib.ptr(self.data),
+                                 _lib.ptr(self.indices), _lib.ptr(self.indptr), self.n_rows,
+                                 self.n_cols, self.nnz, 1 if conj else 0, _lib.ptr(t_data),
+                                 _lib.ptr(t_idx), _lib.ptr(t_ptr), _lib.ptr(ws), nbytes,
+                                 _lib.stream_handle(self.device))
+        _lib.check(st, "b2s_csr2csc")
+        ws.record_stream(torch.cuda.current_stream(self.device))
+        del ws
+        plan = CsrPlan(t_data, t_idx, t_ptr, (self.n_cols, self.n_rows), max_row_nnz=-1)
+        self._transposed[conj] = plan
+        return plan
+
+    def check_status(self):
+        """Read the device status word (synchronises); raise if a kernel reported an error."""
+        bits = int(self.status.item())
+        self.status_checked = True
+        if bits:
+            self.status.zero_()
+            if bits & (1 << _lib.B2S_ERR_TIMEOUT):
+                raise RuntimeError("a bounded wait inside a b200sparse kernel ran out "
+                                   "(bulk copy did not complete)")
+            raise RuntimeError(f"b200sparse kernels reported error bits {bits:#x}")
+
+
+# -------------------------------------------------------------------------------------------------
+# plan cache
+# -------------------------------------------------------------------------------------------------
+_CACHE = OrderedDict()
+_CACHE_CAPACITY = 16
+
+
+def set_plan_cache_capacity(n):
+    """Number of matrices whose plans are kept (least recently used is dropped first)."""
+    global _CACHE_CAPACITY
+    _CACHE_CAPACITY = max(0, int(n))
+    while len(_CACHE) > _CACHE_CAPACITY:
+        _CACHE.popitem(last=False)
+
+
+def clear_plan_cache():
+    _CACHE.clear()
+
+
+def plan_key(kind, data, indices, indptr, shape):
+    return (
+        kind,
+        data.data_ptr(), indices.data_ptr(), indptr.data_ptr(),
+        data.numel(), indptr.numel(),
+        data.dtype, indices.dtype, indptr.dtype,
+        data._version, indices._version, indptr._version,
+        data.stride(0) if data.ndim == 1 and data.numel() > 1 else 1,
+        indices.stride(0) if indices.ndim == 1 and indices.numel() > 1 else 1,
+        indptr.stride(0) if indptr.ndim == 1 and indptr.numel() > 1 else 1,
+        int(shape[0]), int(shape[1]),
+        data.device.index,
+    )
+
+
+def cache_get(key):
+    plan = _CACHE.get(key)
+    if plan is not None:
+        _CACHE.move_to_end(key)
+    return plan
+
+
+def cache_put(key, plan):
+    if _CACHE_CAPACITY == 0:
+        return
+    _CACHE[key] = plan
+    _CACHE.move_to_end(key)
+    while len(_CACHE) > _CACHE_CAPACITY:
+        _CACHE.popitem(last=False)

@@ -1,0 +1,210 @@
+// Shared device helpers: value types, warp shuffles, mbarrier + bulk-copy (TMA) wrappers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/b200sparse.h"
+
+namespace b2s {
+
+// ---------------------------------------------------------------------------------------------
+// value types
+// ---------------------------------------------------------------------------------------------
+struct __align__(8) c64 {
+  float re, im;
+};
+struct __align__(16) c128 {
+  double re, im;
+};
+
+__host__ __device__ inline c64 operator+(c64 a, c64 b) { return {a.re + b.re, a.im + b.im}; }
+__host__ __device__ inline c128 operator+(c128 a, c128 b) { return {a.re + b.re, a.im + b.im}; }
+__host__ __device__ inline c64 operator*(c64 a, c64 b) {
+  return {a.re * b.re - a.im * b.im, a.re * b.im + a.im * b.re};
+}
+__host__ __device__ inline c128 operator*(c128 a, c128 b) {
+  return {a.re * b.re - a.im * b.im, a.re * b.im + a.im * b.re};
+}
+
+template <class V> struct vt;
+template <> struct vt<float> {
+  __host__ __device__ static float zero() { return 0.f; }
+  __host__ __device__ static bool is_zero(float a) { return a == 0.f; }
+  __host__ __device__ static float conj(float a) { return a; }
+};
+template <> struct vt<double> {
+  __host__ __device__ static double zero() { return 0.0; }
+  __host__ __device__ static bool is_zero(double a) { return a == 0.0; }
+  __host__ __device__ static double conj(double a) { return a; }
+};
+template <> struct vt<c64> {
+  __host__ __device__ static c64 zero() { return {0.f, 0.f}; }
+  __host__ __device__ static bool is_zero(c64 a) { return a.re == 0.f && a.im == 0.f; }
+  __host__ __device__ static c64 conj(c64 a) { return {a.re, -a.im}; }
+};
+template <> struct vt<c128> {
+  __host__ __device__ static c128 zero() { return {0.0, 0.0}; }
+  __host__ __device__ static bool is_zero(c128 a) { return a.re == 0.0 && a.im == 0.0; }
+  __host__ __device__ static c128 conj(c128 a) { return {a.re, -a.im}; }
+};
+
+// acc = acc + a * b with the contraction the hardware offers
+__device__ inline void fma_acc(float& acc, float a, float b) { acc = fmaf(a, b, acc); }
+__device__ inline void fma_acc(double& acc, double a, double b) { acc = fma(a, b, acc); }
+__device__ inline void fma_acc(c64& acc, c64 a, c64 b) {
+  acc.re = fmaf(a.re, b.re, acc.re);
+  acc.re = fmaf(-a.im, b.im, acc.re);
+  acc.im = fmaf(a.re, b.im, acc.im);
+  acc.im = fmaf(a.im, b.re, acc.im);
+}
+__device__ inline void fma_acc(c128& acc, c128 a, c128 b) {
+  acc.re = fma(a.re, b.re, acc.re);
+  acc.re = fma(-a.im, b.im, acc.re);
+  acc.im = fma(a.re, b.im, acc.im);
+  acc.im = fma(a.im, b.re, acc.im);
+}
+
+// read-only (non-coherent) global load of one value
+__device__ inline float ldg_val(const float* p) { return __ldg(p); }
+__device__ inline double ldg_val(const double* p) { return __ldg(p); }
+__device__ inline c64 ldg_val(const c64* p) {
+  float2 t = __ldg(reinterpret_cast<const float2*>(p));
+  return {t.x, t.y};
+}
+__device__ inline c128 ldg_val(const c128* p) {
+  double2 t = __ldg(reinterpret_cast<const double2*>(p));
+  return {t.x, t.y};
+}
+
+// epilogue: alpha * s (+ beta * y0 when beta != 0; y0 is not touched otherwise)
+template <class V>
+__device__ inline V axpby(V alpha, V s, bool has_beta, V beta, const V* y0) {
+  V r = alpha * s;
+  if (has_beta) r = r + beta * (*y0);
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// warp shuffles for 4 / 8 / 16-byte values
+// ---------------------------------------------------------------------------------------------
+__device__ inline float shfl_xor(float v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+__device__ inline double shfl_xor(double v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+__device__ inline c64 shfl_xor(c64 v, int m) {
+  return {__shfl_xor_sync(0xffffffffu, v.re, m), __shfl_xor_sync(0xffffffffu, v.im, m)};
+}
+__device__ inline c128 shfl_xor(c128 v, int m) {
+  return {__shfl_xor_sync(0xffffffffu, v.re, m), __shfl_xor_sync(0xffffffffu, v.im, m)};
+}
+
+// butterfly sum over aligned groups of `width` lanes (width a power of two <= 32); every lane of
+// the warp must call it.  The tree is fixed, so the result does not depend on scheduling.
+template <class V>
+__device__ inline V group_sum(V v, int width) {
+  for (int m = width >> 1; m > 0; m >>= 1) v = v + shfl_xor(v, m);
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// mbarrier + 1-D bulk asynchronous copy (TMA engine), CTA-local destination, no multicast
+// ---------------------------------------------------------------------------------------------
+__device__ inline uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ inline void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+  // make the initialised barrier visible to the async proxy that completes the copies
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ inline void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+// L2 eviction-priority descriptors
+__device__ inline uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ inline uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// global -> this CTA's shared memory; src, dst 16-byte aligned, bytes a multiple of 16
+__device__ inline void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
+                                uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1], %2, [%3], %4;" ::"r"(smem_addr(dst_smem)),
+      "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+}
+
+// Bounded wait for a barrier phase.  try_wait suspends the thread for a hardware-chosen slice
+// each time, so the limit below is generous in time yet finite: a lost copy ends the kernel
+// with an error bit instead of hanging the GPU.
+constexpr int kMbarSpinLimit = 1 << 22;
+
+__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t a = smem_addr(bar);
+  for (int it = 0; it < kMbarSpinLimit; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
+        "selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+// 128-bit global loads with an eviction hint for streams read exactly once
+__device__ inline uint4 ldg_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-side dispatch helpers
+// ---------------------------------------------------------------------------------------------
+inline size_t vsize(int vtype) {
+  switch (vtype) {
+    case B2S_F32: return 4;
+    case B2S_F64: return 8;
+    case B2S_C64: return 8;
+    case B2S_C128: return 16;
+  }
+  return 0;
+}
+inline size_t isize(int itype) { return itype == B2S_I32 ? 4 : (itype == B2S_I64 ? 8 : 0); }
+
+#define B2S_DISPATCH_V(vtype, ...)                          \
+  switch (vtype) {                                          \
+    case B2S_F32: { using V = float; __VA_ARGS__; } break;  \
+    case B2S_F64: { using V = double; __VA_ARGS__; } break; \
+    case B2S_C64: { using V = b2s::c64; __VA_ARGS__; } break;    \
+    case B2S_C128: { using V = b2s::c128; __VA_ARGS__; } break;  \
+    default: return B2S_ERR_DTYPE;                          \
+  }
+#define B2S_DISPATCH_I(itype, NAME, ...)                       \
+  switch (itype) {                                             \
+    case B2S_I32: { using NAME = int32_t; __VA_ARGS__; } break; \
+    case B2S_I64: { using NAME = int64_t; __VA_ARGS__; } break; \
+    default: return B2S_ERR_DTYPE;                             \
+  }
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? B2S_OK : B2S_ERR_LAUNCH;
+}
+
+}  // namespace b2s

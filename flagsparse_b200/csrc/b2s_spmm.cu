@@ -1,0 +1,395 @@
+// CSR SpMM for sm_100a: C = alpha * A B + beta * C_in, B and C row-major.
+//
+// Same merge-path tiles as SpMV.  A tile's col / val range is streamed into shared memory by
+// bulk asynchronous copies; rows of B are read with 16-byte loads, G lanes per B row
+// (G * 16 bytes covers one dense-column tile; G is picked from N).  Each lane owns 16 bytes of
+// the output row, so there is no reduction across lanes of one group; groups that share a row
+// combine with a fixed butterfly (inside a warp) or a fixed-order pass over shared memory
+// (whole CTA).  Rows that cross tile borders leave N-wide partials in `carry`; a second kernel
+// adds them in ascending tile order.  No floating-point atomics.
+#include "b2s_tile.cuh"
+
+namespace b2s {
+
+template <class V, class I>
+struct SpmmCfg {
+  static constexpr int THREADS = 256;
+  static constexpr int ITEMS = 1024;
+};
+
+constexpr int kSpmmWarpRowMax = 512;
+constexpr int kSpmmQueue2Cap = 256;
+constexpr int kSpmmQueue3Cap = 8;
+
+template <class V>
+struct alignas(16) Pack {  // the 16 bytes of a B / C row one lane owns
+  static constexpr int N = sizeof(V) >= 16 ? 1 : 16 / static_cast<int>(sizeof(V));
+  V e[N];
+};
+
+template <class V>
+__device__ inline Pack<V> pack_zero() {
+  Pack<V> p;
+#pragma unroll
+  for (int i = 0; i < Pack<V>::N; ++i) p.e[i] = vt<V>::zero();
+  return p;
+}
+
+// load the lane's slice of B row `brow` (elements e0 .. e0+N-1 of n_dense)
+template <class V>
+__device__ inline Pack<V> load_pack(const V* __restrict__ brow, int64_t e0, int64_t n_dense,
+                                    bool vec_ok) {
+  Pack<V> p;
+  if (vec_ok && e0 + Pack<V>::N <= n_dense) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(brow + e0));
+    *reinterpret_cast<uint4*>(&p) = raw;
+  } else {
+#pragma unroll
+    for (int i = 0; i < Pack<V>::N; ++i)
+      p.e[i] = (e0 + i < n_dense) ? ldg_val(brow + e0 + i) : vt<V>::zero();
+  }
+  return p;
+}
+
+template <class V>
+__device__ inline void fma_pack(Pack<V>& acc, V a, const Pack<V>& b) {
+#pragma unroll
+  for (int i = 0; i < Pack<V>::N; ++i) fma_acc(acc.e[i], a, b.e[i]);
+}
+
+template <class V>
+__device__ inline Pack<V> add_pack(const Pack<V>& a, const Pack<V>& b) {
+  Pack<V> r;
+#pragma unroll
+  for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = a.e[i] + b.e[i];
+  return r;
+}
+
+template <class V>
+__device__ inline Pack<V> shfl_xor_pack(const Pack<V>& a, int m) {
+  Pack<V> r;
+#pragma unroll
+  for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = shfl_xor(a.e[i], m);
+  return r;
+}
+
+// out[e0..] = alpha * acc + beta * in[e0..]
+template <class V>
+__device__ inline void store_pack(V* out, const V* in, int64_t e0, int64_t n_dense,
+                                  const Pack<V>& acc, V alpha, V beta, bool has_beta,
+                                  bool vec_ok) {
+  if (e0 >= n_dense) return;
+  Pack<V> r;
+  if (vec_ok && e0 + Pack<V>::N <= n_dense) {
+    if (has_beta) {
+      Pack<V> old;
+      *reinterpret_cast<uint4*>(&old) = *reinterpret_cast<const uint4*>(in + e0);
+#pragma unroll
+      for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = alpha * acc.e[i] + beta * old.e[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = alpha * acc.e[i];
+    }
+    *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(&r);
+  } else {
+#pragma unroll
+    for (int i = 0; i < Pack<V>::N; ++i) {
+      if (e0 + i < n_dense) out[e0 + i] = axpby(alpha, acc.e[i], has_beta, beta, in + e0 + i);
+    }
+  }
+}
+
+template <class V>
+__device__ inline void store_raw(V* out, int64_t e0, int64_t n_dense, const Pack<V>& acc) {
+#pragma unroll
+  for (int i = 0; i < Pack<V>::N; ++i)
+    if (e0 + i < n_dense) out[e0 + i] = acc.e[i];
+}
+
+template <int THREADS, int ITEMS, class V, class I>
+constexpr size_t spmm_smem_bytes() {
+  return 16 + sizeof(int) * (ITEMS + 4) + sizeof(I) * ITEMS + 16 + sizeof(V) * ITEMS + 16 +
+         sizeof(int) * (kSpmmQueue2Cap + kSpmmQueue3Cap + 4) + 16 * THREADS;
+}
+
+// Accumulate A[piece] * B over non-zeros s + first, s + first + step, ... < e of the staged tile.
+// Four gathers of B are in flight per lane before the first multiply.
+template <class V, class I>
+__device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
+                                  const V* __restrict__ sval, int s, int e, int first, int step,
+                                  const V* __restrict__ B, int64_t ldb, int64_t e0,
+                                  int64_t n_dense, bool vec_ok) {
+  int i = s + first;
+  for (; i + 3 * step < e; i += 4 * step) {
+    const int64_t c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step],
+                  c3 = scol[i + 3 * step];
+    const Pack<V> b0 = load_pack(B + c0 * ldb, e0, n_dense, vec_ok);
+    const Pack<V> b1 = load_pack(B + c1 * ldb, e0, n_dense, vec_ok);
+    const Pack<V> b2 = load_pack(B + c2 * ldb, e0, n_dense, vec_ok);
+    const Pack<V> b3 = load_pack(B + c3 * ldb, e0, n_dense, vec_ok);
+    fma_pack(acc, sval[i], b0);
+    fma_pack(acc, sval[i + step], b1);
+    fma_pack(acc, sval[i + 2 * step], b2);
+    fma_pack(acc, sval[i + 3 * step], b3);
+  }
+  for (; i < e; i += step) {
+    const int64_t c = scol[i];
+    const Pack<V> b = load_pack(B + c * ldb, e0, n_dense, vec_ok);
+    fma_pack(acc, sval[i], b);
+  }
+}
+
+// G = lanes per B row (power of two, 1..32); blockIdx.y selects the dense-column tile of
+// G * Pack::N columns when N is wider than one tile.
+template <class V, class I, class P, int THREADS, int ITEMS>
+__global__ void __launch_bounds__(THREADS)
+spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
+                 const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
+                 int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,
+                 int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int vec_b,
+                 int vec_c, int32_t* status) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
+  int* row_end = reinterpret_cast<int*>(smem + 16);
+  unsigned char* col_buf = smem + 16 + sizeof(int) * (ITEMS + 4);
+  unsigned char* val_buf = col_buf + sizeof(I) * ITEMS + 16;
+  int* queue2 = reinterpret_cast<int*>(val_buf + sizeof(V) * ITEMS + 16);
+  int* queue3 = queue2 + kSpmmQueue2Cap;
+  int* qcount = queue3 + kSpmmQueue3Cap;
+  Pack<V>* part = reinterpret_cast<Pack<V>*>(qcount + 4);  // THREADS slots of 16 bytes
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const bool has_beta = has_beta_i != 0;
+  const int64_t t = blockIdx.x;
+  const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
+  const int n_nz = static_cast<int>(tc.j1 - tc.j0);
+  const int n_end = static_cast<int>(tc.r1 - tc.r0);
+
+  const I* gcol = col + tc.j0;
+  const V* gval = val + tc.j0;
+  const Staged<I> sc = stage_layout<I>(col_buf, gcol, n_nz);
+  const Staged<V> sv = stage_layout<V>(val_buf, gval, n_nz);
+  const uint32_t tx = stage_bytes(sc) + stage_bytes(sv);
+  if (tid == 0) {
+    qcount[0] = 0;
+    qcount[1] = 0;
+    if (tx) mbar_init(bar, 1);
+  }
+  __syncthreads();
+  if (tid == 0 && tx) {
+    const uint64_t pol = policy_evict_first();
+    mbar_expect_tx(bar, tx);
+    stage_issue(sc, gcol, bar, pol);
+    stage_issue(sv, gval, bar, pol);
+  }
+  stage_edges(sc, gcol, n_nz, tid, THREADS);
+  stage_edges(sv, gval, n_nz, tid, THREADS);
+  for (int k = tid; k < n_end; k += THREADS)
+    row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
+  if (tid == 0) row_end[n_end] = n_nz;
+  if (tx) {
+    if (!mbar_wait(bar, 0)) {
+      if (status) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
+      mbar_wait(bar, 0);
+    }
+  }
+  __syncthreads();
+
+  const I* scol = sc.s;
+  const V* sval = sv.s;
+  const bool open_row = tc.r1 < n_rows;
+  const int n_seg = n_end + 1;
+  const int64_t e0 =
+      (static_cast<int64_t>(blockIdx.y) * G + (tid & (G - 1))) * Pack<V>::N;  // lane's columns
+  const bool vb = vec_b != 0, vc = vec_c != 0;
+  V* carry_row = carry + t * n_dense;
+
+  // groups per row piece: power of two so that each group sees about four non-zeros
+  const int groups_per_warp = 32 / G;
+  int S = 1;
+  {
+    const int mean = (n_nz + n_seg - 1) / n_seg;
+    while (S * 4 < mean && S < groups_per_warp) S <<= 1;
+  }
+  const int team = S * G;  // lanes per row piece
+  const int p1max = (S == groups_per_warp) ? kSpmmWarpRowMax : 16 * S;
+
+  // ---- strategy 1: one team of S groups per row piece ---------------------------------------
+  {
+    const int team_id = tid / team;
+    const int n_team = THREADS / team;
+    const int grp_in_team = (tid % team) / G;
+    for (int kb = 0; kb < n_seg; kb += n_team) {
+      const int k = kb + team_id;
+      const bool live = k < n_seg;
+      int s = 0, e = 0;
+      if (live) {
+        s = k ? row_end[k - 1] : 0;
+        e = row_end[k];
+      }
+      const int len = e - s;
+      Pack<V> acc = pack_zero<V>();
+      if (len <= p1max) {
+        accumulate<V, I>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, vb);
+      } else if ((tid % team) == 0) {
+        if (len <= kSpmmWarpRowMax) {
+          const int q = atomicAdd(&qcount[0], 1);
+          if (q < kSpmmQueue2Cap) queue2[q] = k;
+        } else {
+          const int q = atomicAdd(&qcount[1], 1);
+          if (q < kSpmmQueue3Cap) queue3[q] = k;
+        }
+      }
+      for (int m = team >> 1; m >= G; m >>= 1) acc = add_pack(acc, shfl_xor_pack(acc, m));
+      if (live && grp_in_team == 0 && len <= p1max) {
+        if (k < n_end) {
+          const int64_t r = tc.r0 + k;
+          store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc);
+        } else if (open_row) {
+          store_raw(carry_row, e0, n_dense, acc);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- strategy 2: one warp per row piece -----------------------------------------------------
+  const int n2 = min(qcount[0], kSpmmQueue2Cap);
+  for (int q = warp; q < n2; q += THREADS / 32) {
+    const int k = queue2[q];
+    const int s = k ? row_end[k - 1] : 0;
+    const int e = row_end[k];
+    Pack<V> acc = pack_zero<V>();
+    accumulate<V, I>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0, n_dense, vb);
+    for (int m = 16; m >= G; m >>= 1) acc = add_pack(acc, shfl_xor_pack(acc, m));
+    if (lane < G) {
+      if (k < n_end) {
+        const int64_t r = tc.r0 + k;
+        store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc);
+      } else if (open_row) {
+        store_raw(carry_row, e0, n_dense, acc);
+      }
+    }
+  }
+
+  // ---- strategy 3: the whole CTA on one row piece ---------------------------------------------
+  const int n3 = min(qcount[1], kSpmmQueue3Cap);
+  const int n_grp = THREADS / G;
+  for (int q = 0; q < n3; ++q) {
+    const int k = queue3[q];
+    const int s = k ? row_end[k - 1] : 0;
+    const int e = row_end[k];
+    Pack<V> acc = pack_zero<V>();
+    accumulate<V, I>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, vb);
+    part[tid] = acc;
+    __syncthreads();
+    if (tid < G) {
+      Pack<V> tot = part[tid];
+      for (int g = 1; g < n_grp; ++g) tot = add_pack(tot, part[g * G + tid]);
+      if (k < n_end) {
+        const int64_t r = tc.r0 + k;
+        store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, tot, alpha, beta, has_beta, vc);
+      } else if (open_row) {
+        store_raw(carry_row, e0, n_dense, tot);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <class V>
+__global__ void spmm_fixup_kernel(V* C, int64_t ldc, int64_t n_dense,
+                                  const V* __restrict__ carry,
+                                  const int64_t* __restrict__ tile_row, int64_t n_tiles,
+                                  V alpha) {
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t t = idx / n_dense;
+  const int64_t n = idx - t * n_dense;
+  if (t < 1 || t >= n_tiles) return;
+  const int64_t r = tile_row[t];
+  if (tile_row[t + 1] <= r) return;
+  int64_t u0 = t - 1;
+  while (u0 >= 1 && tile_row[u0] == r) --u0;
+  V s = carry[u0 * n_dense + n];
+  for (int64_t u = u0 + 1; u < t; ++u) s = s + carry[u * n_dense + n];
+  C[r * ldc + n] = C[r * ldc + n] + alpha * s;
+}
+
+template <class V, class I, class P>
+int spmm_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
+                int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
+                void* C, int64_t ldc, const void* alpha, const void* beta,
+                const int64_t* tile_row, void* carry, int32_t* status, cudaStream_t stream) {
+  using Cfg = SpmmCfg<V, I>;
+  constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
+  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
+  if (n_tiles == 0 || n_dense == 0) return B2S_OK;
+  if (n_tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
+  const V a = *static_cast<const V*>(alpha);
+  const V b = *static_cast<const V*>(beta);
+  const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
+  if (has_beta && C_in == nullptr) return B2S_ERR_ARG;
+  constexpr int PN = Pack<V>::N;
+  // lanes per B row: enough 16-byte slices to cover N, at most a warp
+  const int64_t slices = (n_dense + PN - 1) / PN;
+  int G = 1;
+  while (G < slices && G < 32) G <<= 1;
+  const int64_t col_tiles = (slices + G - 1) / G;
+  if (col_tiles > 65535) return B2S_ERR_RANGE;
+  const int vec_b = (reinterpret_cast<uintptr_t>(B) % 16 == 0) && ((ldb * sizeof(V)) % 16 == 0);
+  const int vec_c = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * sizeof(V)) % 16 == 0) &&
+                    (!has_beta || reinterpret_cast<uintptr_t>(C_in) % 16 == 0);
+  auto kern = spmm_tile_kernel<V, I, P, THREADS, ITEMS>;
+  constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
+  ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
+  dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(col_tiles));
+  kern<<<grid, THREADS, smem, stream>>>(
+      static_cast<const V*>(data), static_cast<const I*>(indices),
+      static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
+      static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
+      n_rows, nnz, a, b, has_beta, G, vec_b, vec_c, status);
+  if (n_tiles > 1) {
+    const int fb = 256;
+    const int64_t work = n_tiles * n_dense;
+    spmm_fixup_kernel<V><<<static_cast<unsigned>((work + fb - 1) / fb), fb, 0, stream>>>(
+        static_cast<V*>(C), ldc, n_dense, static_cast<const V*>(carry), tile_row, n_tiles, a);
+  }
+  return launch_status();
+}
+
+}  // namespace b2s
+
+extern "C" int b2s_spmm_tile_items(int val_type, int idx_type) {
+  (void)val_type;
+  (void)idx_type;
+  return b2s::SpmmCfg<float, int32_t>::ITEMS;
+}
+
+extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                            const void* indices_dev, const void* indptr_dev, int64_t n_rows,
+                            int64_t n_cols, int64_t nnz, const void* B_dev, int64_t ldb,
+                            int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
+                            const void* alpha, const void* beta, const int64_t* tile_row_dev,
+                            void* carry_dev, int32_t* status_dev, b2s_stream stream) {
+  if (n_rows < 0 || n_cols < 0 || nnz < 0 || n_dense < 0 || !alpha || !beta) return B2S_ERR_ARG;
+  if (n_rows == 0 || n_dense == 0) return B2S_OK;
+  if (ldb < n_dense || ldc < n_dense) return B2S_ERR_ARG;
+  if (!indptr_dev || !C_dev || !tile_row_dev || !carry_dev) return B2S_ERR_ARG;
+  if (nnz > 0 && (!data_dev || !indices_dev || !B_dev)) return B2S_ERR_ARG;
+  const size_t vs = b2s::vsize(val_type);
+  if (vs == 0) return B2S_ERR_DTYPE;
+  const uintptr_t m = vs - 1;
+  if ((reinterpret_cast<uintptr_t>(data_dev) & m) || (reinterpret_cast<uintptr_t>(B_dev) & m) ||
+      (reinterpret_cast<uintptr_t>(C_dev) & m) || (reinterpret_cast<uintptr_t>(C_in_dev) & m) ||
+      (reinterpret_cast<uintptr_t>(carry_dev) & m))
+    return B2S_ERR_ALIGNMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
+    return (b2s::spmm_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, nnz, B_dev, ldb,
+                                      n_dense, C_in_dev, C_dev, ldc, alpha, beta, tile_row_dev,
+                                      carry_dev, status_dev, s));
+  })));
+  return B2S_ERR_DTYPE;
+}

@@ -1,0 +1,408 @@
+"""CSR SpMV with FlagSparse's call signature, computed by libb200sparse.so.
+
+Mirrors ``flagsparse.sparse_operations.spmv_csr`` (spmv_csr.py): ``flagsparse_spmv_csr``
+(:813-913), ``prepare_spmv_csr`` (:591-664), ``PreparedCsrSpmv`` (:55-130), the input contract
+(:518-588) and the int64 -> int32 retry (:726-810).  Two keyword arguments are added at the end
+of the signature, ``alpha=1.0, beta=0.0``: y = alpha * op(A) x + beta * out.
+
+Differences that do not change results beyond rounding:
+  * float32 is accumulated in float32 with short fixed trees instead of float64
+    (spmv_csr.py:124-129 upcasts); the difference is ~1e-7 relative;
+  * ``block_nnz`` / ``max_segments`` / ``use_opt`` are validated and recorded but do not steer
+    the kernel: one kernel covers every row length;
+  * CPU tensors are rejected exactly like the reference does; there is no CPU path.
+"""
+
+from __future__ import annotations
+
+import time
+
+import torch
+
+from . import _lib
+from ._contract import (
+    INDEX_LIMIT_INT32,
+    OP_CONJ_TRANS,
+    OP_NON,
+    REFERENCE_VALUE_DTYPE_NAMES,
+    SUPPORTED_INDEX_DTYPES,
+    SUPPORTED_VALUE_DTYPES,
+    check_scalar,
+    is_complex,
+    normalize_op,
+    op_name,
+    op_transposes,
+)
+from ._plan import (
+    ST_DECREASING,
+    ST_MAXCOL,
+    ST_MAXLEN,
+    ST_MINCOL,
+    ST_PTR0,
+    ST_PTRN,
+    CsrPlan,
+    cache_get,
+    cache_put,
+    inspect_csr,
+    plan_key,
+)
+
+SUPPORTED_SPMV_VALUE_DTYPES = SUPPORTED_VALUE_DTYPES
+SPMV_OP_NON, SPMV_OP_TRANS, SPMV_OP_CONJ_TRANS = 0, 1, 2
+SPMV_OP_NAMES = {0: "non", 1: "trans", 2: "conj"}
+_INDEX_LIMIT_INT32 = INDEX_LIMIT_INT32
+
+_normalize_spmv_op = normalize_op
+_spmv_op_to_name = op_name
+_spmv_op_transposes = op_transposes
+
+
+def _spmv_dtype_error_message():
+    return "data dtype must be one of: " + REFERENCE_VALUE_DTYPE_NAMES
+
+
+def _normalize_spmv_index_fallback_policy(index_fallback_policy):
+    policy = str(index_fallback_policy).lower()
+    if policy not in ("auto", "strict"):
+        raise ValueError("index_fallback_policy must be 'auto' or 'strict'")
+    return policy
+
+
+# -------------------------------------------------------------------------------------------------
+# input contract  (spmv_csr.py:518-572)
+# -------------------------------------------------------------------------------------------------
+def _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy="auto"):
+    """Validate the CSR triple and return its CsrPlan (cached by tensor identity)."""
+    _normalize_spmv_index_fallback_policy(index_fallback_policy)
+    if not all(torch.is_tensor(t) for t in (data, indices, indptr)):
+        raise TypeError("data, indices, indptr must all be torch.Tensor")
+    if data.ndim != 1 or indices.ndim != 1 or indptr.ndim != 1:
+        raise ValueError("data, indices, indptr must be 1D tensors")
+    n_rows, n_cols = int(shape[0]), int(shape[1])
+    if indptr.numel() != n_rows + 1:
+        raise ValueError(f"indptr length must be n_rows+1={n_rows + 1}, got {indptr.numel()}")
+    if data.numel() != indices.numel():
+        raise ValueError("data and indices must have the same length (nnz)")
+    if not all(t.is_cuda for t in (data, indices, indptr)):
+        raise ValueError("data, indices, indptr must be CUDA tensors")
+    if not all(t.device == data.device for t in (indices, indptr)):
+        raise ValueError("data, indices, indptr must be on the same CUDA device")
+    if data.dtype not in SUPPORTED_SPMV_VALUE_DTYPES:
+        raise TypeError(_spmv_dtype_error_message())
+    if indices.dtype not in SUPPORTED_INDEX_DTYPES:
+        raise TypeError("indices dtype must be torch.int32 or torch.int64")
+    if indptr.dtype not in SUPPORTED_INDEX_DTYPES:
+        raise TypeError("indptr dtype must be torch.int32 or torch.int64")
+
+    key = plan_key("spmv", data, indices, indptr, (n_rows, n_cols))
+    plan = cache_get(key)
+    if plan is not None:
+        return plan
+
+    d, i, p = data.contiguous(), indices.contiguous(), indptr.contiguous()
+    if d.data_ptr() % d.element_size():
+        d = d.clone()
+    nnz = d.numel()
+    stats = inspect_csr(i, p, n_rows, nnz)
+    if stats[ST_PTR0] != 0:
+        raise ValueError("indptr must start at zero")
+    if stats[ST_PTRN] != nnz:
+        raise ValueError("indptr[-1] must equal nnz")
+    if stats[ST_DECREASING] != 0:
+        raise ValueError("indptr must be non-decreasing")
+    if nnz > 0 and (stats[ST_MINCOL] < 0 or stats[ST_MAXCOL] >= n_cols):
+        raise IndexError("indices out of range for n_cols")
+    plan = CsrPlan(d, i, p, (n_rows, n_cols), stats[ST_MAXLEN],
+                   keepalive=(data, indices, indptr))
+    cache_put(key, plan)
+    return plan
+
+
+class PreparedCsrSpmv:
+    """Cached CSR metadata for repeated SpMV calls on the same sparse matrix.
+
+    Attribute names follow spmv_csr.py:58-79.  ``data`` / ``kernel_indices`` / ``kernel_indptr``
+    are the arrays the kernel reads (those of the transpose when ``transpose`` is set);
+    ``shape`` / ``n_rows`` / ``n_cols`` describe op(A).
+    """
+
+    def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, block_nnz,
+                 max_segments, max_row_nnz, opt_buckets=None, opt_max_segments=None,
+                 row_lengths=None, transpose=False, op=None, index_fallback_policy="auto",
+                 index_fallback_applied=False, index_fallback_reason=None, _plan=None):
+        self.data = data
+        self.kernel_indices = kernel_indices
+        self.kernel_indptr = kernel_indptr
+        self.shape = (int(shape[0]), int(shape[1]))
+        self.n_rows = n_rows
+        self.n_cols = n_cols
+        self.block_nnz = block_nnz
+        self.max_segments = max_segments
+        self.opt_max_segments = opt_max_segments
+        self._row_lengths = row_lengths
+        self.max_row_nnz = max_row_nnz
+        self.opt_buckets = [] if opt_buckets is None else opt_buckets
+        self.supports_opt = (
+            data.dtype in (torch.float32, torch.float64) and kernel_indices.dtype == torch.int32
+        )
+        self.op = normalize_op(op, transpose=transpose)
+        self.transpose = op_transposes(self.op)
+        self.index_fallback_policy = str(index_fallback_policy).lower()
+        self.index_fallback_applied = bool(index_fallback_applied)
+        self.index_fallback_reason = index_fallback_reason
+        self._plan = _plan
+
+    @property
+    def row_lengths(self):
+        if self._row_lengths is None:
+            self._row_lengths = self.kernel_indptr[1:] - self.kernel_indptr[:-1]
+        return self._row_lengths
+
+    def plan(self):
+        """The CsrPlan of the arrays the kernel reads (built on first use when this object was
+        constructed by hand rather than by prepare_spmv_csr)."""
+        if self._plan is None:
+            self._plan = _checked_spmv_plan(self.data, self.kernel_indices, self.kernel_indptr,
+                                            self.shape, self.index_fallback_policy)
+        return self._plan
+
+
+def _transpose_csr_for_spmv(data, indices, indptr, shape):
+    """CSR(A) -> CSR(A^T) as four values like spmv_csr.py:477-515, computed by b2s_csr2csc."""
+    plan = _checked_spmv_plan(data, indices, indptr, shape)
+    t = plan.transposed(conj=False)
+    return t.data, t.indices, t.indptr, (t.n_rows, t.n_cols)
+
+
+def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=None,
+                     transpose=False, op=None, index_fallback_policy="auto"):
+    index_fallback_policy = _normalize_spmv_index_fallback_policy(index_fallback_policy)
+    op_code = normalize_op(op, transpose=transpose)
+    if op is not None and bool(transpose) and op_code == OP_NON:
+        raise ValueError("transpose=True conflicts with op=non")
+    plan = _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy)
+    if op_transposes(op_code):
+        plan = plan.transposed(conj=(op_code == OP_CONJ_TRANS))
+        if plan.max_row_nnz < 0:
+            # the transpose came from our own kernel; only its longest row is still unknown
+            plan.max_row_nnz = inspect_csr(plan.indices, plan.indptr, plan.n_rows,
+                                           plan.nnz)[ST_MAXLEN]
+    max_row_nnz = plan.max_row_nnz
+    # segment bookkeeping kept for callers that read it (spmv_csr.py:637-647)
+    block_nnz_use = block_nnz
+    if max_segments is None:
+        max_segments_use = max((max_row_nnz + block_nnz_use - 1) // block_nnz_use, 1)
+        while max_segments_use > 2048 and block_nnz_use < 65536:
+            block_nnz_use *= 2
+            max_segments_use = max((max_row_nnz + block_nnz_use - 1) // block_nnz_use, 1)
+    else:
+        max_segments_use = max_segments
+    return PreparedCsrSpmv(
+        data=plan.data, kernel_indices=plan.indices, kernel_indptr=plan.indptr, shape=plan.shape,
+        n_rows=plan.n_rows, n_cols=plan.n_cols, block_nnz=block_nnz_use,
+        max_segments=max_segments_use, opt_max_segments=max_segments, max_row_nnz=max_row_nnz,
+        transpose=op_transposes(op_code), op=op_code,
+        index_fallback_policy=index_fallback_policy, _plan=plan)
+
+
+def _validate_spmv_x(x, prepared):
+    if x is None or not torch.is_tensor(x):
+        raise TypeError("x must be a torch.Tensor")
+    if x.ndim != 1:
+        raise ValueError("x must be a 1D tensor")
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor")
+    if x.dtype != prepared.data.dtype:
+        raise TypeError("x dtype must match sparse matrix dtype")
+    if x.numel() != prepared.n_cols:
+        raise ValueError(f"x length must be n_cols={prepared.n_cols}, got {x.numel()}")
+    if x.device != prepared.data.device:
+        raise ValueError("x must be on the same device as sparse matrix data")
+    x = x.contiguous()
+    if x.data_ptr() % x.element_size():
+        x = x.clone()
+    return x
+
+
+# -------------------------------------------------------------------------------------------------
+# launch
+# -------------------------------------------------------------------------------------------------
+def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
+    """Enqueue y = alpha * A x + beta * y_in on the current stream (no synchronisation)."""
+    lib = _lib.load()
+    items = lib.b2s_spmv_tile_items(plan.vcode, plan.icode)
+    n_tiles, tile_row = plan.tiles(items)
+    carry = plan.scratch("spmv_carry", n_tiles)
+    dtype = plan.data.dtype
+    a = _lib.scalar_buffer(alpha, dtype)
+    b = _lib.scalar_buffer(beta, dtype)
+    with torch.cuda.device(plan.device):
+        st = lib.b2s_spmv_csr(
+            plan.vcode, plan.icode, plan.pcode,
+            _lib.ptr(plan.data), _lib.ptr(plan.indices), _lib.ptr(plan.indptr),
+            plan.n_rows, plan.n_cols, plan.nnz,
+            _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b,
+            _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status),
+            _lib.stream_handle(plan.device))
+    _lib.check(st, "b2s_spmv_csr")
+    if not plan.status_checked:
+        plan.check_status()
+
+
+def _b200_spmv_csr_impl_prepared(prepared, x, out=None, alpha=1.0, beta=0.0):
+    plan = prepared.plan()
+    dtype = plan.data.dtype
+    direct = (out is not None and out.is_contiguous()
+              and out.data_ptr() % out.element_size() == 0)
+    y = out if direct else torch.empty(plan.n_rows, dtype=dtype, device=plan.device)
+    if plan.n_rows == 0:
+        return y
+    y_in = None
+    if beta != 0:
+        y_in = out if direct else out.contiguous()
+    _launch_spmv(plan, x, y, y_in, alpha, beta)
+    if out is not None and not direct:
+        out.copy_(y)
+        y = out
+    return y
+
+
+def _spmv_uses_int64_indices(prepared):
+    return (prepared.kernel_indices.dtype == torch.int64
+            or prepared.kernel_indptr.dtype == torch.int64)
+
+
+def _spmv_int32_fallback_blocker(prepared):
+    """Why an int64 matrix cannot be re-run with int32 copies, or None (spmv_csr.py:733-750)."""
+    if prepared.kernel_indices.dtype == torch.int64 and prepared.kernel_indices.numel() > 0:
+        min_index = int(prepared.kernel_indices.min().item())
+        max_index = int(prepared.kernel_indices.max().item())
+        if min_index < 0 or max_index > _INDEX_LIMIT_INT32:
+            return (f"column index range [{min_index}, {max_index}] cannot fit int32 "
+                    f"for shape={prepared.shape}")
+    if prepared.kernel_indptr.dtype == torch.int64 and prepared.kernel_indptr.numel() > 0:
+        max_offset = int(prepared.kernel_indptr[-1].item())
+        if max_offset > _INDEX_LIMIT_INT32:
+            return f"CSR nnz offset {max_offset} cannot fit int32 for shape={prepared.shape}"
+    if prepared.n_rows > _INDEX_LIMIT_INT32:
+        return f"row count {prepared.n_rows} cannot fit int32 row metadata"
+    return None
+
+
+def _spmv_prepared_with_int32_indices(prepared, reason):
+    blocker = _spmv_int32_fallback_blocker(prepared)
+    if blocker is not None:
+        raise RuntimeError(
+            f"native int64 CSR SpMV failed and int32 fallback is unsafe: {blocker}")
+    return PreparedCsrSpmv(
+        data=prepared.data,
+        kernel_indices=prepared.kernel_indices.to(torch.int32),
+        kernel_indptr=prepared.kernel_indptr.to(torch.int32),
+        shape=prepared.shape, n_rows=prepared.n_rows, n_cols=prepared.n_cols,
+        block_nnz=prepared.block_nnz, max_segments=prepared.max_segments,
+        opt_max_segments=prepared.opt_max_segments, max_row_nnz=prepared.max_row_nnz,
+        transpose=prepared.transpose, op=prepared.op,
+        index_fallback_policy=prepared.index_fallback_policy,
+        index_fallback_applied=True, index_fallback_reason=str(reason))
+
+
+def _run_spmv_prepared(prepared, x, use_opt=False, opt_buckets=None, out=None, alpha=1.0,
+                       beta=0.0):
+    return _b200_spmv_csr_impl_prepared(prepared, x, out=out, alpha=alpha, beta=beta)
+
+
+def _run_spmv_prepared_with_fallback(prepared, x, use_opt=False, opt_buckets=None, out=None,
+                                     alpha=1.0, beta=0.0):
+    """Run; if the launch raises and the matrix has int64 indices and the policy is 'auto',
+    run once more on int32 copies of the index arrays (spmv_csr.py:790-810)."""
+    try:
+        return _run_spmv_prepared(prepared, x, use_opt=use_opt, opt_buckets=opt_buckets, out=out,
+                                  alpha=alpha, beta=beta)
+    except Exception as exc:
+        if (prepared.index_fallback_policy != "auto"
+                or not _spmv_uses_int64_indices(prepared)):
+            raise
+        fallback = _spmv_prepared_with_int32_indices(prepared, exc)
+        return _run_spmv_prepared(fallback, x, use_opt=use_opt, opt_buckets=None, out=out,
+                                  alpha=alpha, beta=beta)
+
+
+def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None, block_nnz=256,
+                        max_segments=None, out=None, return_time=False, return_meta=False,
+                        use_opt=False, prepared=None, transpose=None, op=None,
+                        index_fallback_policy="auto", alpha=1.0, beta=0.0):
+    """CSR SpMV on B200: y = alpha * op(A) @ x + beta * out.
+
+    data, indices, indptr: CSR arrays (CUDA tensors); x: dense vector; shape: (n_rows, n_cols).
+    prepared: handle from prepare_spmv_csr for steady-state runs (an implicit cache keyed on the
+    tensors gives the same effect when it is omitted).
+    op: 0/'non' for A @ x, 1/'trans' for A.T @ x, 2/'conj' for A.conj().T @ x.
+    alpha, beta: scalars (default 1, 0 -- the reference's behaviour); beta != 0 needs ``out``,
+    whose prior contents are read.
+    """
+    op_explicit = op is not None
+    op_code = normalize_op(op, transpose=False if transpose is None else bool(transpose))
+    if op_explicit and transpose is not None and bool(transpose) != op_transposes(op_code):
+        raise ValueError("transpose conflicts with op")
+    if prepared is None:
+        if any(arg is None for arg in (data, indices, indptr, shape)):
+            raise ValueError(
+                "data, indices, indptr, and shape are required when prepared is not provided")
+        prepared = prepare_spmv_csr(data, indices, indptr, shape, block_nnz=block_nnz,
+                                    max_segments=max_segments, op=op_code,
+                                    index_fallback_policy=index_fallback_policy)
+    else:
+        if op_explicit and op_code != prepared.op:
+            raise ValueError(
+                f"op={op_name(op_code)} does not match prepared.op={op_name(prepared.op)}")
+        if not op_explicit and transpose is not None and bool(transpose) != prepared.transpose:
+            raise ValueError(
+                f"transpose={bool(transpose)} does not match "
+                f"prepared.transpose={prepared.transpose}")
+    x = _validate_spmv_x(x, prepared)
+    dtype = prepared.data.dtype
+    alpha = check_scalar(alpha, dtype, "alpha")
+    beta = check_scalar(beta, dtype, "beta")
+    if out is not None:
+        if not torch.is_tensor(out) or not out.is_cuda:
+            raise ValueError("out must be a CUDA tensor")
+        if out.device != prepared.data.device:
+            raise ValueError("out must be on the same CUDA device as the result")
+        if out.shape != (prepared.n_rows,) or out.dtype != dtype:
+            raise ValueError("out shape/dtype must match result")
+    elif beta != 0:
+        raise ValueError("beta != 0 requires out= holding the vector to scale")
+
+    do_timing = bool(return_time or return_meta)
+    symbolic_ms = 0.0 if do_timing else None
+    compute_ms = None
+    op_total_ms = None
+    opt_active = bool(use_opt and prepared.supports_opt)
+    if do_timing:
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+    y = _run_spmv_prepared_with_fallback(prepared, x, use_opt=use_opt, out=out, alpha=alpha,
+                                         beta=beta)
+    if do_timing:
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        compute_ms = (t2 - t1) * 1000.0
+        op_total_ms = symbolic_ms + compute_ms
+    if return_meta:
+        meta = {
+            "symbolic_ms": symbolic_ms,
+            "compute_ms": compute_ms,
+            "op_total_ms": op_total_ms,
+            # the reference counts its row-length buckets when use_opt is active; the tile
+            # kernel always has three row-length strategies
+            "bucket_count": 3 if opt_active else 0,
+        }
+        if return_time:
+            return y, op_total_ms, meta
+        return y, meta
+    if return_time:
+        return y, op_total_ms
+    return y
+
+
+spmv_csr = flagsparse_spmv_csr

@@ -1,0 +1,131 @@
+/*
+ * b200sparse.h -- C ABI of libb200sparse.so: CSR SpMV / SpMM for NVIDIA B200 (sm_100a).
+ *
+ * The library is the device side of the Python functions flagsparse_spmv_csr and
+ * flagsparse_spmm_csr.  FlagSparse itself has no native interface (its kernels are Triton
+ * functions launched from Python), so every entry point below cites the Python function or
+ * Triton kernel of FlagSparse whose work it takes over
+ * (paths are relative to the FlagSparse source tree).
+ *
+ * Conventions
+ *   - every pointer argument named *_dev is a CUDA device pointer on the current device;
+ *     alpha / beta are HOST pointers to one scalar of the value dtype;
+ *   - nothing here allocates, frees or synchronises: scratch memory is passed in by the caller,
+ *     kernels are enqueued on `stream` and the call returns at once;
+ *   - every function returns a b2s_status (0 = ok); none throws, aborts or traps;
+ *   - value pointers must be aligned to the value size (16 bytes for complex128).
+ */
+#ifndef B200SPARSE_H_
+#define B200SPARSE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2S_VERSION 100
+
+typedef enum {
+  B2S_OK = 0,
+  B2S_ERR_DTYPE = 1,      /* unknown value / index dtype code                     */
+  B2S_ERR_ARG = 2,        /* null pointer, negative size, inconsistent sizes      */
+  B2S_ERR_ALIGNMENT = 3,  /* a pointer is not aligned to its element size         */
+  B2S_ERR_LAUNCH = 4,     /* cudaGetLastError() reported a launch failure         */
+  B2S_ERR_TIMEOUT = 5,    /* (device status word) a bounded wait in a kernel ran out */
+  B2S_ERR_WORKSPACE = 6,  /* scratch buffer smaller than *_bytes() asked for      */
+  B2S_ERR_RANGE = 7       /* a size does not fit the requested index dtype        */
+} b2s_status;
+
+/* value dtypes (order follows FlagSparse's SUPPORTED_VALUE_DTYPES, _common.py:21-29) */
+typedef enum { B2S_F32 = 0, B2S_F64 = 1, B2S_C64 = 2, B2S_C128 = 3 } b2s_vtype;
+/* index dtypes (SUPPORTED_INDEX_DTYPES, _common.py:30) */
+typedef enum { B2S_I32 = 0, B2S_I64 = 1 } b2s_itype;
+
+/* Opaque CUDA stream handle (cudaStream_t); 0 is the legacy default stream. */
+typedef void* b2s_stream;
+
+int b2s_version(void);
+const char* b2s_status_string(int status);
+
+/* ---- input contract ------------------------------------------------------------------------
+ * Replaces the device reductions behind the `.item()` checks of _prepare_spmv_csr_matrix
+ * (spmv_csr.py:546-563) and _prepare_spmm_csr_matrix (spmm_csr.py:268-296).  One pass over
+ * indptr and indices fills eight int64 words at stats_dev:
+ *   [0] indptr[0]   [1] indptr[n_rows]   [2] number of i with indptr[i+1] < indptr[i]
+ *   [3] min column  [4] max column       [5] max row length   [6] number of empty rows
+ *   [7] reserved (0)
+ * The caller zero-initialises nothing: the first kernel does.  min/max are INT64_MAX/INT64_MIN
+ * when nnz == 0.
+ */
+int b2s_csr_inspect(const void* indptr_dev, int ptr_type, const void* indices_dev, int idx_type,
+                    int64_t n_rows, int64_t nnz, int64_t* stats_dev, b2s_stream stream);
+
+/* ---- tile plan -----------------------------------------------------------------------------
+ * A plan cuts the merged sequence "row ends + non-zeros" of a CSR matrix into tiles of
+ * `tile_items` entries (merge-path).  It replaces the per-call bucket construction of
+ * _build_spmv_opt_buckets (spmv_csr.py:353-399) and the split-row bookkeeping of
+ * _spmm_csr_split_part / _split_reduce (spmm_csr.py:2368-2402, 2969-3109).
+ * b2s_tile_count gives the number of tiles T; the plan is (T+1) int64 words (first row of
+ * each tile) written to tile_row_dev.
+ */
+int64_t b2s_tile_count(int64_t n_rows, int64_t nnz, int tile_items);
+int b2s_tile_plan(const void* indptr_dev, int ptr_type, int64_t n_rows, int64_t nnz,
+                  int tile_items, int64_t* tile_row_dev, b2s_stream stream);
+
+/* Tile size (merge items per CTA) the SpMV / SpMM kernels of this build were compiled for. */
+int b2s_spmv_tile_items(int val_type, int idx_type);
+int b2s_spmm_tile_items(int val_type, int idx_type);
+
+/* ---- SpMV ----------------------------------------------------------------------------------
+ * y = alpha * A x + beta * y_in.  Replaces _spmv_csr_real_kernel (spmv_csr.py:167-192),
+ * _spmv_csr_complex_kernel (:196-227) and the bucketed kernels (:234-351) with their launchers
+ * (:412-461, :679-723).  One launch of the tile kernel plus one launch of the carry fix-up.
+ *   y_in_dev  may be NULL when *beta == 0, and may equal y_dev;
+ *   carry_dev scratch of T values (T = b2s_tile_count(..., b2s_spmv_tile_items(...)));
+ *   status_dev one int32 the kernels OR error bits into (B2S_ERR_TIMEOUT); may be NULL.
+ * The result is bit-identical from run to run: no floating-point atomics, fixed reduction trees.
+ */
+int b2s_spmv_csr(int val_type, int idx_type, int ptr_type,
+                 const void* data_dev, const void* indices_dev, const void* indptr_dev,
+                 int64_t n_rows, int64_t n_cols, int64_t nnz,
+                 const void* x_dev, const void* y_in_dev, void* y_dev,
+                 const void* alpha, const void* beta,
+                 const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
+                 b2s_stream stream);
+
+/* ---- SpMM ----------------------------------------------------------------------------------
+ * C = alpha * A B + beta * C_in, B (n_cols x n_dense, leading dimension ldb) and
+ * C (n_rows x n_dense, leading dimension ldc) row-major.  Replaces _spmm_csr_real_kernel
+ * (spmm_csr.py:135-176), _spmm_csr_complex_kernel (:181-237) and _triton_spmm_csr_impl
+ * (:2684-2789).  carry_dev: scratch of T * n_dense values with
+ * T = b2s_tile_count(..., b2s_spmm_tile_items(...)).
+ */
+int b2s_spmm_csr(int val_type, int idx_type, int ptr_type,
+                 const void* data_dev, const void* indices_dev, const void* indptr_dev,
+                 int64_t n_rows, int64_t n_cols, int64_t nnz,
+                 const void* B_dev, int64_t ldb, int64_t n_dense,
+                 const void* C_in_dev, void* C_dev, int64_t ldc,
+                 const void* alpha, const void* beta,
+                 const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
+                 b2s_stream stream);
+
+/* ---- CSR -> CSC (the transpose behind op = trans / conj) -----------------------------------
+ * Replaces _transpose_csr_for_spmv (spmv_csr.py:477-515) and _transpose_csr_for_spmm
+ * (spmm_csr.py:300-338): a stable sort of the non-zeros by column, so that inside one output
+ * row the entries keep ascending source-row order, exactly like the stable argsort there.
+ * conj != 0 conjugates complex values on the way (spmv_csr.py:615-618, spmm_csr.py:345-348).
+ * Output arrays use the input dtypes: t_indices (idx_type, source row ids), t_indptr (ptr_type,
+ * n_cols + 1 entries).  scratch_dev needs b2s_csr2csc_bytes() bytes.
+ */
+int64_t b2s_csr2csc_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz);
+int b2s_csr2csc(int val_type, int idx_type, int ptr_type,
+                const void* data_dev, const void* indices_dev, const void* indptr_dev,
+                int64_t n_rows, int64_t n_cols, int64_t nnz, int conj,
+                void* t_data_dev, void* t_indices_dev, void* t_indptr_dev,
+                void* scratch_dev, int64_t scratch_bytes, b2s_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200SPARSE_H_ */

@@ -1,0 +1,173 @@
+"""The C ABI called directly (ctypes, raw device pointers): tile plan invariants, the CSR -> CSC
+kernel against the reference fixtures bit for bit, the status codes."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import load_golden
+from gpu_util import assert_parity, csr_from_lengths, dev, host, random_values
+
+pytestmark = pytest.mark.gpu
+
+TRANS_CASES = sorted(c for c in load_golden("spmv_reference.npz") if not c.endswith("_non"))
+
+
+def _lib():
+    from flagsparse_b200 import _lib
+    return _lib.load(), _lib
+
+
+def _merge_path_rows(ptr, n_rows, nnz, items):
+    """numpy restatement of the merge-path search the plan kernel performs."""
+    total = n_rows + nnz
+    n_tiles = -(-total // items)
+    out = np.empty(n_tiles + 1, dtype=np.int64)
+    ends = ptr[1:]
+    for t in range(n_tiles + 1):
+        d = min(t * items, total)
+        lo, hi = max(d - nnz, 0), min(d, n_rows)
+        while lo < hi:
+            mid = (lo + hi) // 2
+            if ends[mid] <= d - mid - 1:
+                lo = mid + 1
+            else:
+                hi = mid
+        out[t] = lo
+    return out
+
+
+@pytest.mark.parametrize("items", [64, 1024, 2048])
+def test_tile_plan_matches_merge_path(items):
+    lib, L = _lib()
+    rng = np.random.default_rng(2)
+    lengths = np.concatenate([rng.integers(0, 4, 5000), [9000, 0, 0, 1], np.zeros(3000, int),
+                              rng.integers(0, 300, 200)])
+    ptr = np.zeros(lengths.size + 1, dtype=np.int64)
+    np.cumsum(lengths, out=ptr[1:])
+    n_rows, nnz = lengths.size, int(ptr[-1])
+    for tdt, code in ((torch.int32, L.B2S_I32), (torch.int64, L.B2S_I64)):
+        p = dev(ptr, tdt)
+        T = lib.b2s_tile_count(n_rows, nnz, items)
+        assert T == -(-(n_rows + nnz) // items)
+        tile_row = torch.empty(T + 1, dtype=torch.int64, device="cuda")
+        st = lib.b2s_tile_plan(L.ptr(p), code, n_rows, nnz, items, L.ptr(tile_row),
+                               L.stream_handle(p.device))
+        assert st == 0
+        got = host(tile_row)
+        assert np.array_equal(got, _merge_path_rows(ptr, n_rows, nnz, items))
+        # invariants the kernels rely on
+        d = np.minimum(np.arange(T + 1) * items, n_rows + nnz)
+        j = d - got
+        assert got[0] == 0 and got[-1] == n_rows and j[-1] == nnz
+        assert np.all(np.diff(got) >= 0) and np.all(np.diff(j) >= 0)
+        assert np.all(ptr[got] <= j) and np.all(j <= ptr[np.minimum(got + 1, n_rows)])
+
+
+@pytest.mark.parametrize("case", TRANS_CASES)
+def test_csr2csc_bit_identical_to_reference_transpose(case, spmv_golden):
+    """b2s_csr2csc against the output of the reference's _transpose_csr_for_spmv
+    (spmv_csr.py:477-515) on the same input: same permutation, same bits."""
+    lib, L = _lib()
+    c = spmv_golden[case]
+    n_rows = c["indptr"].shape[0] - 1
+    n_cols = int(case.split("_")[1].split("x")[1])
+    conj = case.endswith("_conj")
+    data, idx, ptr = dev(c["data"]), dev(c["indices"]), dev(c["indptr"])
+    nnz = data.numel()
+    t_data, t_idx = torch.empty_like(data), torch.empty_like(idx)
+    t_ptr = torch.empty(n_cols + 1, dtype=torch.int64, device="cuda")
+    nbytes = lib.b2s_csr2csc_bytes(n_rows, n_cols, nnz)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    st = lib.b2s_csr2csc(L.VALUE_CODE[data.dtype], L.B2S_I64, L.B2S_I64, L.ptr(data), L.ptr(idx),
+                         L.ptr(ptr), n_rows, n_cols, nnz, int(conj), L.ptr(t_data), L.ptr(t_idx),
+                         L.ptr(t_ptr), L.ptr(ws), nbytes, L.stream_handle(data.device))
+    assert st == 0
+    assert np.array_equal(host(t_ptr), c["t_indptr"])
+    assert np.array_equal(host(t_idx), c["t_indices"])
+    assert np.array_equal(host(t_data).view(np.uint8), c["t_data"].view(np.uint8))
+    too_small = lib.b2s_csr2csc(L.VALUE_CODE[data.dtype], L.B2S_I64, L.B2S_I64, L.ptr(data),
+                                L.ptr(idx), L.ptr(ptr), n_rows, n_cols, nnz, int(conj),
+                                L.ptr(t_data), L.ptr(t_idx), L.ptr(t_ptr), L.ptr(ws), 16,
+                                L.stream_handle(data.device))
+    assert too_small == 6 and b"scratch" in lib.b2s_status_string(too_small)
+
+
+@pytest.mark.parametrize("n_cols", [1, 255, 257, 70000, 17_000_000])
+def test_csr2csc_large_random_vs_oracle(n_cols):
+    """1, 2 and 3+ radix passes; several thousand CTAs; unsorted columns with duplicates."""
+    from flagsparse_b200._plan import CsrPlan
+    rng = np.random.default_rng(n_cols)
+    n_rows = 20000
+    data, idx, ptr = csr_from_lengths(rng, rng.integers(0, 60, n_rows), n_cols, np.complex64,
+                                      sort=False)
+    plan = CsrPlan(dev(data), dev(idx, torch.int32), dev(ptr), (n_rows, n_cols), -1)
+    t = plan.transposed(conj=True)
+    e_data, e_idx, e_ptr, _ = oracle.transpose_csr(data, idx, ptr, (n_rows, n_cols), conj=True)
+    assert np.array_equal(host(t.indptr), e_ptr)
+    assert np.array_equal(host(t.indices), e_idx)
+    assert np.array_equal(host(t.data).view(np.uint8), e_data.view(np.uint8))
+
+
+def test_raw_spmv_spmm_calls_and_status_codes():
+    lib, L = _lib()
+    rng = np.random.default_rng(9)
+    n_rows, n_cols = 3000, 2000
+    data, idx, ptr = csr_from_lengths(rng, rng.integers(0, 50, n_rows), n_cols, np.float64)
+    x = random_values(rng, n_cols, np.float64)
+    d, i, p, xd = dev(data), dev(idx, torch.int32), dev(ptr, torch.int32), dev(x)
+    nnz = d.numel()
+    items = lib.b2s_spmv_tile_items(L.B2S_F64, L.B2S_I32)
+    T = lib.b2s_tile_count(n_rows, nnz, items)
+    tile_row = torch.empty(T + 1, dtype=torch.int64, device="cuda")
+    s = L.stream_handle(d.device)
+    assert lib.b2s_tile_plan(L.ptr(p), L.B2S_I32, n_rows, nnz, items, L.ptr(tile_row), s) == 0
+    carry = torch.empty(T, dtype=torch.float64, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.empty(n_rows, dtype=torch.float64, device="cuda")
+    one, zero = (ctypes.c_double * 1)(1.0), (ctypes.c_double * 1)(0.0)
+    st = lib.b2s_spmv_csr(L.B2S_F64, L.B2S_I32, L.B2S_I32, L.ptr(d), L.ptr(i), L.ptr(p), n_rows,
+                          n_cols, nnz, L.ptr(xd), None, L.ptr(y), one, zero, L.ptr(tile_row),
+                          L.ptr(carry), L.ptr(status), s)
+    assert st == 0
+    assert_parity(host(y), oracle.spmv(data, idx, ptr, x, (n_rows, n_cols)), np.float64)
+    assert int(status.item()) == 0
+    # status codes: bad dtype, beta != 0 without y_in, misaligned pointer
+    args = [L.B2S_F64, L.B2S_I32, L.B2S_I32, L.ptr(d), L.ptr(i), L.ptr(p), n_rows, n_cols, nnz,
+            L.ptr(xd), None, L.ptr(y), one, zero, L.ptr(tile_row), L.ptr(carry), L.ptr(status), s]
+    bad = list(args); bad[0] = 9
+    assert lib.b2s_spmv_csr(*bad) == 1
+    bad = list(args); bad[13] = one
+    assert lib.b2s_spmv_csr(*bad) == 2
+    bad = list(args); bad[11] = ctypes.c_void_p(y.data_ptr() + 4)
+    assert lib.b2s_spmv_csr(*bad) == 3
+    assert lib.b2s_version() == 100
+
+    n_dense = 8
+    B = random_values(rng, n_cols * n_dense, np.float64).reshape(n_cols, n_dense)
+    Bd = dev(B)
+    items = lib.b2s_spmm_tile_items(L.B2S_F64, L.B2S_I32)
+    T = lib.b2s_tile_count(n_rows, nnz, items)
+    tile_row = torch.empty(T + 1, dtype=torch.int64, device="cuda")
+    assert lib.b2s_tile_plan(L.ptr(p), L.B2S_I32, n_rows, nnz, items, L.ptr(tile_row), s) == 0
+    carry = torch.empty(T * n_dense, dtype=torch.float64, device="cuda")
+    C = torch.empty((n_rows, n_dense), dtype=torch.float64, device="cuda")
+    st = lib.b2s_spmm_csr(L.B2S_F64, L.B2S_I32, L.B2S_I32, L.ptr(d), L.ptr(i), L.ptr(p), n_rows,
+                          n_cols, nnz, L.ptr(Bd), n_dense, n_dense, None, L.ptr(C), n_dense, one,
+                          zero, L.ptr(tile_row), L.ptr(carry), L.ptr(status), s)
+    assert st == 0
+    assert_parity(host(C), oracle.spmm(data, idx, ptr, B, (n_rows, n_cols)), np.float64)
+
+
+def test_inspect_reports_contract_violations():
+    lib, L = _lib()
+    ptr = torch.tensor([0, 3, 2, 2, 7], dtype=torch.int64, device="cuda")
+    idx = torch.tensor([5, -2, 9, 1, 1, 1, 4], dtype=torch.int32, device="cuda")
+    stats = torch.empty(8, dtype=torch.int64, device="cuda")
+    st = lib.b2s_csr_inspect(L.ptr(ptr), L.B2S_I64, L.ptr(idx), L.B2S_I32, 4, 7, L.ptr(stats),
+                             L.stream_handle(ptr.device))
+    assert st == 0
+    assert stats.tolist()[:7] == [0, 7, 1, -2, 9, 5, 1]

@@ -1,0 +1,123 @@
+"""Host-side logic that needs no GPU: op codes, scalar handling, the checks that fire before any
+device work, and that CPU tensors are refused (there is no CPU path)."""
+
+import pytest
+import torch
+
+from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr, prepare_spmv_csr
+from flagsparse_b200._contract import (check_scalar, normalize_op, op_name, op_transposes,
+                                       resolve_op)
+from flagsparse_b200.spmm import (_resolve_spmm_alg1_launch_config,
+                                  _select_spmm_alg1_warp_and_factor)
+
+
+def test_op_codes_follow_reference():
+    # spmv_csr.py:29-43 / spmm_csr.py:22-36
+    assert [normalize_op(v) for v in (0, 1, 2, "non", " Trans ", "CONJ")] == [0, 1, 2, 0, 1, 2]
+    assert normalize_op(None, transpose=True) == 1 and normalize_op(None) == 0
+    for bad in ("bad", 3, -1, object()):
+        with pytest.raises(ValueError, match="op must be one of: 0=non, 1=trans, 2=conj"):
+            normalize_op(bad)
+    assert op_name(2) == "conj" and op_transposes("trans") and not op_transposes(0)
+    assert resolve_op("trans", True) == 1 and resolve_op(None, None) == 0
+    with pytest.raises(ValueError, match="transpose conflicts with op"):
+        resolve_op("non", True)
+    with pytest.raises(ValueError, match="transpose conflicts with op"):
+        resolve_op("conj", False)
+
+
+def test_scalars():
+    assert check_scalar(torch.tensor(2.0), torch.float32, "alpha") == 2.0
+    assert check_scalar(1 + 0j, torch.float64, "alpha") == 1.0
+    with pytest.raises(TypeError):
+        check_scalar(1 + 1j, torch.float64, "alpha")
+    assert check_scalar(1 + 1j, torch.complex64, "alpha") == 1 + 1j
+
+
+def test_dense_tile_heuristic_matches_reference_table():
+    # _alpha_spmm_alg1_common.py:6-23
+    table = {1: (4, 1), 4: (4, 1), 5: (8, 1), 8: (8, 1), 9: (16, 1), 16: (16, 1), 17: (32, 1),
+             32: (32, 1), 33: (32, 2), 64: (32, 2), 65: (32, 4), 128: (32, 4)}
+    for n, want in table.items():
+        assert _select_spmm_alg1_warp_and_factor(n) == want
+    cfg = _resolve_spmm_alg1_launch_config(48, 1536)
+    assert (cfg["block_n"], cfg["block_nnz"], cfg["required_segments"]) == (64, 32, 48)
+    with pytest.raises(ValueError, match="more CSR segments"):
+        _resolve_spmm_alg1_launch_config(48, 1536, block_nnz=128, max_segments=4)
+    with pytest.raises(ValueError, match="must be positive"):
+        _resolve_spmm_alg1_launch_config(48, 10, block_n=0)
+
+
+def _cpu_csr():
+    data = torch.tensor([1.0, 2.0, 3.0])
+    indices = torch.tensor([0, 1, 1], dtype=torch.int32)
+    indptr = torch.tensor([0, 2, 3], dtype=torch.int64)
+    return data, indices, indptr
+
+
+def test_spmv_checks_before_device_work():
+    data, indices, indptr = _cpu_csr()
+    x = torch.ones(2)
+    with pytest.raises(ValueError, match="must be CUDA tensors"):  # spmv_csr.py:531-532
+        flagsparse_spmv_csr(data, indices, indptr, x, (2, 2))
+    with pytest.raises(ValueError, match="are required when prepared is not provided"):
+        flagsparse_spmv_csr(data, indices, indptr, x)
+    with pytest.raises(TypeError, match="must all be torch.Tensor"):
+        flagsparse_spmv_csr([1.0], indices, indptr, x, (2, 2))
+    with pytest.raises(ValueError, match="must be 1D tensors"):
+        flagsparse_spmv_csr(data.view(1, 3), indices, indptr, x, (2, 2))
+    with pytest.raises(ValueError, match=r"indptr length must be n_rows\+1=4, got 3"):
+        flagsparse_spmv_csr(data, indices, indptr, x, (3, 2))
+    with pytest.raises(ValueError, match="same length"):
+        flagsparse_spmv_csr(data[:2], indices, indptr, x, (2, 2))
+    with pytest.raises(ValueError, match="index_fallback_policy must be"):
+        flagsparse_spmv_csr(data, indices, indptr, x, (2, 2), index_fallback_policy="maybe")
+    with pytest.raises(ValueError, match="transpose conflicts with op"):
+        flagsparse_spmv_csr(data, indices, indptr, x, (2, 2), op="non", transpose=True)
+    with pytest.raises(ValueError, match="transpose=True conflicts with op=non"):
+        prepare_spmv_csr(data, indices, indptr, (2, 2), transpose=True, op="non")
+
+
+def test_spmm_checks_before_device_work():
+    data, indices, indptr = _cpu_csr()
+    B = torch.ones(2, 4)
+    with pytest.raises(ValueError, match="must be CUDA tensors"):  # spmm_csr.py:255-256
+        flagsparse_spmm_csr(data, indices, indptr, B, (2, 2))
+    with pytest.raises(ValueError, match="shape must be a 2-tuple"):
+        flagsparse_spmm_csr(data, indices, indptr, B, (2,))
+    with pytest.raises(ValueError, match="non-negative"):
+        flagsparse_spmm_csr(data, indices, indptr, B, (-1, 2))
+    with pytest.raises(ValueError, match="block_n must be positive"):
+        flagsparse_spmm_csr(data, indices, indptr, B, (2, 2), block_n=0)
+    with pytest.raises(ValueError, match="op must be one of"):
+        flagsparse_spmm_csr(data, indices, indptr, B, (2, 2), op="bad")
+
+
+def test_install_rebinds_a_flagsparse_like_package():
+    """install() on a stand-in module tree with the reference's layout
+    (src/flagsparse/__init__.py:247-254, sparse_operations/__init__.py:36-72)."""
+    import sys
+    import types
+
+    import flagsparse_b200
+
+    root = types.ModuleType("fake_flagsparse")
+    ops = types.ModuleType("fake_flagsparse.sparse_operations")
+    spmv = types.ModuleType("fake_flagsparse.sparse_operations.spmv_csr")
+    spmm = types.ModuleType("fake_flagsparse.sparse_operations.spmm_csr")
+    sentinel = object()
+    ops.flagsparse_spmv_csr = spmv.flagsparse_spmv_csr = sentinel
+    ops.flagsparse_spmm_csr = spmm.flagsparse_spmm_csr = sentinel
+    root.sparse_operations, ops.spmv_csr, ops.spmm_csr = ops, spmv, spmm
+    for m in (root, ops, spmv, spmm):
+        sys.modules[m.__name__] = m
+    try:
+        replaced = flagsparse_b200.install(root)
+        assert root.flagsparse_spmv_csr is flagsparse_b200.flagsparse_spmv_csr
+        assert ops.flagsparse_spmm_csr is flagsparse_b200.flagsparse_spmm_csr
+        assert spmv.flagsparse_spmv_csr is flagsparse_b200.flagsparse_spmv_csr
+        flagsparse_b200.uninstall(replaced)
+        assert ops.flagsparse_spmv_csr is sentinel and not hasattr(root, "flagsparse_spmv_csr")
+    finally:
+        for m in (root, ops, spmv, spmm):
+            sys.modules.pop(m.__name__, None)

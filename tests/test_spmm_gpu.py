@@ -1,0 +1,210 @@
+"""GPU parity of flagsparse_spmm_csr (CUDA path) against the CPU oracle and the reference
+fixtures.  Tolerance: rel-L2 <= 1e-5 (float32 / complex64), <= 1e-12 (float64 / complex128)."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import ALLCLOSE_TOL, load_golden
+from gpu_util import TORCH_OF, assert_parity, csr_from_lengths, dev, host, random_values
+
+pytestmark = pytest.mark.gpu
+
+SPMM_CASES = sorted(load_golden("spmm_reference.npz"))
+DTYPES = [np.float32, np.float64, np.complex64, np.complex128]
+
+
+def _shape_of(case, c):
+    n_rows = c["indptr"].shape[0] - 1
+    if case.startswith("spmm_longrow"):
+        return n_rows, 2048
+    M, K, _ = (int(v) for v in case.split("_")[1].split("x"))
+    return M, K
+
+
+@pytest.mark.parametrize("index_dtype", [torch.int32, torch.int64], ids=["int32", "int64"])
+@pytest.mark.parametrize("case", SPMM_CASES)
+def test_spmm_matches_reference_fixture(case, index_dtype, spmm_golden):
+    from flagsparse_b200 import flagsparse_spmm_csr
+    c = spmm_golden[case]
+    op = case.rsplit("_", 1)[1]
+    C = flagsparse_spmm_csr(dev(c["data"]), dev(c["indices"], index_dtype),
+                            dev(c["indptr"], index_dtype), dev(c["B"]), _shape_of(case, c), op=op)
+    assert_parity(host(C), c["C"], c["C"].dtype, case)
+    tol = ALLCLOSE_TOL[c["C"].dtype]
+    assert np.allclose(host(C), c["C"], rtol=max(tol, 1e-5 if tol > 1e-7 else tol), atol=tol * 8)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("n_dense", [1, 3, 4, 5, 16, 31, 32, 33, 64, 130])
+@pytest.mark.parametrize("op", ["non", "trans"])
+def test_spmm_dense_widths_vs_oracle(dtype, n_dense, op):
+    """Every dense-column tile (1 .. 32 lanes per B row, and more than one column tile), widths
+    that are not a multiple of 16 bytes, ragged rows including one longer than several tiles."""
+    from flagsparse_b200 import flagsparse_spmm_csr
+    rng = np.random.default_rng(100 + n_dense)
+    lengths = np.concatenate([[0, 1, 31, 32, 33, 0, 3000, 2, 600, 513, 0],
+                              rng.integers(0, 5, 700), np.zeros(1200, dtype=np.int64),
+                              rng.integers(0, 80, 300), [0]])
+    n_rows, n_cols = lengths.size, 1500
+    data, idx, ptr = csr_from_lengths(rng, lengths, n_cols, dtype)
+    k = n_rows if op != "non" else n_cols
+    B = random_values(rng, k * n_dense, dtype).reshape(k, n_dense)
+    expect = oracle.spmm(data, idx, ptr, B, (n_rows, n_cols), op=op)
+    args = (dev(data), dev(idx, torch.int32), dev(ptr, torch.int64), dev(B), (n_rows, n_cols))
+    C = flagsparse_spmm_csr(*args, op=op)
+    assert_parity(host(C), expect, dtype)
+    C2 = flagsparse_spmm_csr(*args, op=op)
+    assert torch.equal(C.view(torch.uint8), C2.view(torch.uint8)), "not bit-identical run to run"
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128], ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64], ids=["i32", "i64"])
+def test_spmm_conj_vs_oracle(dtype, idx_dtype):
+    from flagsparse_b200 import flagsparse_spmm_csr
+    rng = np.random.default_rng(21)
+    data, idx, ptr = csr_from_lengths(rng, rng.integers(0, 30, 900), 400, dtype, sort=False)
+    B = random_values(rng, 900 * 8, dtype).reshape(900, 8)
+    C = flagsparse_spmm_csr(dev(data), dev(idx, idx_dtype), dev(ptr, idx_dtype), dev(B),
+                            (900, 400), op="conj")
+    assert_parity(host(C), oracle.spmm(data, idx, ptr, B, (900, 400), op="conj"), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: np.dtype(d).name)
+def test_spmm_alpha_beta_out_and_strides(dtype):
+    from flagsparse_b200 import flagsparse_spmm_csr
+    rng = np.random.default_rng(8)
+    lengths = rng.integers(0, 30, 1000)
+    lengths[5] = 5000
+    data, idx, ptr = csr_from_lengths(rng, lengths, 800, dtype)
+    B = random_values(rng, 800 * 12, dtype).reshape(800, 12)
+    C0 = random_values(rng, 1000 * 12, dtype).reshape(1000, 12)
+    alpha, beta = (1.5, 0.5) if np.dtype(dtype).kind != "c" else (1.5 - 0.25j, 0.5 + 2j)
+    expect = oracle.spmm(data, idx, ptr, B, (1000, 800), alpha=alpha, beta=beta, C0=C0)
+    out = dev(C0)
+    C = flagsparse_spmm_csr(dev(data), dev(idx), dev(ptr), dev(B), (1000, 800), out=out,
+                            alpha=alpha, beta=beta)
+    assert C is out
+    assert_parity(host(C), expect, dtype)
+    # B as a column slice of a wider matrix (row-major, leading dimension 20) and a transposed B
+    wide = torch.zeros((800, 20), dtype=TORCH_OF[np.dtype(dtype)], device="cuda")
+    wide[:, 3:15] = dev(B)
+    C = flagsparse_spmm_csr(dev(data), dev(idx), dev(ptr), wide[:, 3:15], (1000, 800))
+    assert_parity(host(C), oracle.spmm(data, idx, ptr, B, (1000, 800)), dtype)
+    Bt = dev(np.ascontiguousarray(B.T)).t()
+    assert not Bt.is_contiguous()
+    C = flagsparse_spmm_csr(dev(data), dev(idx), dev(ptr), Bt, (1000, 800))
+    assert_parity(host(C), oracle.spmm(data, idx, ptr, B, (1000, 800)), dtype)
+
+
+def test_spmm_cfg3_and_cfg4_scaled_vs_oracle():
+    """Banded float32/int32 N=32 and Poisson(24) op=trans float32 / op=conj complex64 N=64, at
+    1/16 and 1/32 of the benchmark's row counts."""
+    from flagsparse_b200 import flagsparse_spmm_csr, workloads
+    p = workloads.cfg3_banded_spmm(device="cuda", scale=16)
+    C = flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape)
+    expect = oracle.spmm(host(p.data), host(p.indices), host(p.indptr), host(p.B), p.shape)
+    assert_parity(host(C), expect, np.float32, "cfg3")
+    for dtype in (torch.float32, torch.complex64):
+        p = workloads.cfg4_poisson_spmm(device="cuda", scale=32, dtype=dtype)
+        C = flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape, op=p.op)
+        assert C.shape == (p.shape[1], 64)
+        expect = oracle.spmm(host(p.data), host(p.indices), host(p.indptr), host(p.B), p.shape,
+                             op=p.op)
+        assert_parity(host(C), expect, host(p.data).dtype, f"cfg4 {p.op}")
+
+
+def test_spmm_powerlaw_scaled_vs_oracle():
+    """float64/int64 power-law matrix (1/256 of 2^24 rows) with N=32, and float32/int64 N=16."""
+    from flagsparse_b200 import flagsparse_spmm_csr, workloads
+    p = workloads.cfg2_powerlaw_spmv(device="cuda", scale=256, n_dense=32)
+    C = flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape)
+    expect = oracle.spmm(host(p.data), host(p.indices), host(p.indptr), host(p.B), p.shape)
+    assert_parity(host(C), expect, np.float64, "cfg2-MM")
+    p = workloads.cfg5_scaling(device="cuda", scale=1024)
+    C = flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape)
+    expect = oracle.spmm(host(p.data), host(p.indices), host(p.indptr), host(p.B), p.shape)
+    assert_parity(host(C), expect, np.float32, "cfg5 SpMM")
+
+
+def test_spmm_full_size_banded_properties():
+    """Full-size banded config (2^22 rows, N=32): compared with torch's CSR product, and repeats
+    bit for bit."""
+    from flagsparse_b200 import flagsparse_spmm_csr, workloads
+    p = workloads.cfg3_banded_spmm(device="cuda")
+    C = flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape)
+    A = torch.sparse_csr_tensor(p.indptr.long(), p.indices.long(), p.data.double(), size=p.shape)
+    ref = A @ p.B.double()
+    err = float(torch.linalg.matrix_norm(C.double() - ref) / torch.linalg.matrix_norm(ref))
+    assert err <= 1e-5, err
+    assert torch.equal(C, flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape))
+
+
+def test_spmm_api_contract():
+    """The negative / positive cases of the reference's CLI checks (tests/test_spmm.py:766-898)
+    and of tests/pytest/test_spmm_csr_accuracy.py:135-215."""
+    from flagsparse_b200 import flagsparse_spmm_csr as f
+    cuda = "cuda"
+    data = torch.tensor([1.0, 2.0, 3.0], device=cuda)
+    indices = torch.tensor([0, 1, 1], dtype=torch.int32, device=cuda)
+    indptr = torch.tensor([0, 2, 3], dtype=torch.int64, device=cuda)
+    B = torch.randn((2, 4), device=cuda)
+    t64 = lambda v: torch.tensor(v, dtype=torch.int64, device=cuda)  # noqa: E731
+    negative = [
+        (lambda: f(data, indices, indptr, B, (2,)), ValueError),
+        (lambda: f(data, indices, indptr, B[0], (2, 2)), ValueError),
+        (lambda: f(data, indices, indptr, B.double(), (2, 2)), TypeError),
+        (lambda: f(data, indices, indptr, torch.randn((3, 4), device=cuda), (2, 2)), ValueError),
+        (lambda: f(data, indices, indptr[:-1], B, (2, 2)), ValueError),
+        (lambda: f(data, indices, t64([1, 2, 3]), B, (2, 2)), ValueError),
+        (lambda: f(data, indices, t64([0, 2, 2]), B, (2, 2)), ValueError),
+        (lambda: f(data, indices, t64([0, 3, 2]), B, (2, 2)), ValueError),
+        (lambda: f(data, torch.tensor([0, 3, 1], dtype=torch.int32, device=cuda), indptr, B,
+                   (2, 2)), IndexError),
+        (lambda: f(data, indices, indptr, B, (2, 2), block_n=0), ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), block_nnz=0), ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), max_segments=0), ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), out=torch.empty((3, 4), device=cuda)),
+         ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), out=torch.empty((2, 4))), ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), op="bad"), ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), op="non", transpose=True), ValueError),
+        (lambda: f(data, indices, indptr, torch.randn((3, 4), device=cuda), (2, 2), op="trans"),
+         ValueError),
+        (lambda: f(data, indices, indptr, B, (2, 2), op="trans",
+                   out=torch.empty((2, 3), device=cuda)), ValueError),
+    ]
+    for fn, exc in negative:
+        with pytest.raises(exc):
+            fn()
+    # the explicit max_segments override that is too small for a 1536-entry row
+    idx = torch.cat([torch.arange(1536), torch.tensor([7, 129, 511, 1024])]).to(torch.int32).cuda()
+    ptr = t64([0, 1536, 1540])
+    vals = torch.randn(1540, device=cuda)
+    Bl = torch.randn((2048, 48), device=cuda)
+    with pytest.raises(ValueError, match="more CSR segments"):
+        f(vals, idx, ptr, Bl, (2, 2048), block_nnz=128, max_segments=4)
+    # messages pinned by the reference's pytest file
+    with pytest.raises(ValueError, match="B.shape\\[0\\] must be n_cols=2"):
+        f(data, indices, indptr, torch.randn((3, 4), device=cuda), (2, 2), op="trans")
+    with pytest.raises(ValueError, match="out shape/dtype must match result"):
+        f(data, indices, indptr, B, (2, 2), op="trans", out=torch.empty((2, 3), device=cuda))
+
+    dense = torch.tensor([[1.0, 2.0], [0.0, 3.0]], device=cuda)
+    out = torch.empty((2, 4), device=cuda)
+    C = f(data, indices, indptr, B, (2, 2), out=out)
+    assert C.data_ptr() == out.data_ptr()
+    assert torch.allclose(C, dense @ B, atol=1e-6)
+    assert torch.allclose(f(data, indices, indptr, B, (2, 2), op="trans"), dense.t() @ B, atol=1e-6)
+    empty = f(data[:0], indices[:0], torch.zeros(3, dtype=torch.int64, device=cuda), B, (2, 2))
+    assert empty.shape == (2, 4) and float(empty.abs().sum()) == 0.0
+    assert f(data, indices, indptr, torch.empty((2, 0), device=cuda), (2, 2)).shape == (2, 0)
+    # meta / timing
+    C, ms, meta = f(data, indices.long(), indptr, B, (2, 2), op="trans", return_time=True,
+                    return_meta=True)
+    assert meta["op"] == "trans" and meta["symbolic_ms"] >= 0.0 and meta["compute_ms"] >= 0.0
+    assert ms == pytest.approx(meta["op_total_ms"])
+    assert meta["op_total_ms"] == pytest.approx(meta["symbolic_ms"] + meta["compute_ms"])
+    C, meta = f(data, indices, indptr, B, (2, 2), op="non", return_meta=True)
+    assert meta["op"] == "non" and meta["symbolic_ms"] == 0.0
