@@ -368,6 +368,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the SpMM N=32 side measurement")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -401,7 +402,10 @@ def main():
     per_step = seconds / args.steps
     gbs = nbytes / per_step / 1e9
 
-    e2e_s, h2d, d2h = time_e2e(p, kind, max(3, min(args.steps, 10)), 3)
+    if args.no_e2e:
+        e2e_s, h2d, d2h = float("nan"), 0, 0
+    else:
+        e2e_s, h2d, d2h = time_e2e(p, kind, max(3, min(args.steps, 10)), 3)
 
     extra = {"gflops": flops / per_step / 1e9, "pct_of_8tbs_nominal": 100.0 * gbs / NOMINAL_HBM_GBS,
              "algorithmic_bytes_per_step": nbytes}

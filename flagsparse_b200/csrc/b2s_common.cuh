@@ -147,7 +147,7 @@ __device__ inline void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t b
 // Bounded wait for a barrier phase.  try_wait suspends the thread for a hardware-chosen slice
 // each time, so the limit below is generous in time yet finite: a lost copy ends the kernel
 // with an error bit instead of hanging the GPU.
-constexpr int kMbarSpinLimit = 1 << 22;
+constexpr int kMbarSpinLimit = 1 << 20;
 
 __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
   uint32_t a = smem_addr(bar);

@@ -55,6 +55,8 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
+  // an earlier CTA already gave up on a copy: do not queue more waits behind it
+  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
   const int64_t t = blockIdx.x;
   const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
   const int n_nz = static_cast<int>(tc.j1 - tc.j0);
