@@ -31,6 +31,7 @@ INDEX_CODE = {torch.int32: B2S_I32, torch.int64: B2S_I64}
 SIGNATURES = {
     "b2s_version": (c_int, []),
     "b2s_status_string": (c_char_p, [c_int]),
+    "b2s_tune": (c_int, [c_int, c_int64]),
     "b2s_csr_inspect": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p,
                                 c_void_p]),
     "b2s_tile_count": (c_int64, [c_int64, c_int64, c_int]),

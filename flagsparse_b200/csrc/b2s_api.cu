@@ -6,6 +6,8 @@
 
 namespace b2s {
 
+int64_t g_knobs[KNOB_COUNT] = {0};
+
 void ensure_dyn_smem(const void* kernel, size_t bytes) {
   struct Seen {
     const void* k;
@@ -130,6 +132,24 @@ __global__ void tile_plan_kernel(const P* __restrict__ ptr, int64_t n_rows, int6
 }  // namespace b2s
 
 extern "C" int b2s_version(void) { return B2S_VERSION; }
+
+extern "C" int b2s_tune(int knob, int64_t value) {
+  if (knob < 0 || knob >= b2s::KNOB_COUNT) return B2S_ERR_ARG;
+  b2s::g_knobs[knob] = value;
+  if (knob == b2s::KNOB_L2_FETCH && value > 0)
+    if (cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, static_cast<size_t>(value)) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return B2S_ERR_ARG;
+    }
+  if (knob == b2s::KNOB_PERSIST_BYTES)
+    if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, static_cast<size_t>(value)) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return B2S_ERR_ARG;
+    }
+  return B2S_OK;
+}
 
 extern "C" const char* b2s_status_string(int status) {
   switch (status) {

@@ -75,6 +75,88 @@ __device__ inline c128 ldg_val(const c128* p) {
   return {t.x, t.y};
 }
 
+// the same loads carrying an L2 eviction-priority descriptor
+__device__ inline float ldg_val(const float* p, uint64_t pol) {
+  float v;
+  asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ inline double ldg_val(const double* p, uint64_t pol) {
+  double v;
+  asm volatile("ld.global.nc.L2::cache_hint.f64 %0, [%1], %2;" : "=d"(v) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ inline c64 ldg_val(const c64* p, uint64_t pol) {
+  c64 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v2.f32 {%0,%1}, [%2], %3;"
+               : "=f"(v.re), "=f"(v.im)
+               : "l"(p), "l"(pol));
+  return v;
+}
+__device__ inline c128 ldg_val(const c128* p, uint64_t pol) {
+  c128 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v2.f64 {%0,%1}, [%2], %3;"
+               : "=d"(v.re), "=d"(v.im)
+               : "l"(p), "l"(pol));
+  return v;
+}
+
+// gather of one value with a selectable cache path:
+//   0 ld.global.nc (read-only path)   1 nc + L2 evict-last hint   2 ld.global.cg (L2 only)
+//   3 nc + L1::no_allocate            4 ld.global.ca
+template <class V>
+__device__ inline V gather_val(const V* p, int mode, uint64_t pol) {
+  if (mode == 0) return ldg_val(p);
+  if (mode == 1) return ldg_val(p, pol);
+  V v;
+  if constexpr (sizeof(V) == 4) {
+    uint32_t r;
+    if (mode == 2) asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(r) : "l"(p));
+    else if (mode == 3) asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(r) : "l"(p));
+    else asm volatile("ld.global.ca.b32 %0, [%1];" : "=r"(r) : "l"(p));
+    memcpy(&v, &r, 4);
+  } else if constexpr (sizeof(V) == 8) {
+    uint64_t r;
+    if (mode == 2) asm volatile("ld.global.cg.b64 %0, [%1];" : "=l"(r) : "l"(p));
+    else if (mode == 3) asm volatile("ld.global.nc.L1::no_allocate.b64 %0, [%1];" : "=l"(r) : "l"(p));
+    else asm volatile("ld.global.ca.b64 %0, [%1];" : "=l"(r) : "l"(p));
+    memcpy(&v, &r, 8);
+  } else {
+    uint64_t a, b;
+    if (mode == 2) asm volatile("ld.global.cg.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
+    else if (mode == 3) asm volatile("ld.global.nc.L1::no_allocate.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
+    else asm volatile("ld.global.ca.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
+    uint64_t t[2] = {a, b};
+    memcpy(&v, t, 16);
+  }
+  return v;
+}
+
+// load of one element of a stream that is read exactly once: read-only path, no L1 allocation,
+// L2 eviction priority given by `pol` (evict-first keeps the stream from displacing x)
+template <class T>
+__device__ inline T stream_val(const T* p, uint64_t pol) {
+  T v;
+  if constexpr (sizeof(T) == 4) {
+    uint32_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;"
+                 : "=r"(r) : "l"(p), "l"(pol));
+    memcpy(&v, &r, 4);
+  } else if constexpr (sizeof(T) == 8) {
+    uint64_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b64 %0, [%1], %2;"
+                 : "=l"(r) : "l"(p), "l"(pol));
+    memcpy(&v, &r, 8);
+  } else {
+    uint64_t a, b;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.b64 {%0,%1}, [%2], %3;"
+                 : "=l"(a), "=l"(b) : "l"(p), "l"(pol));
+    uint64_t t[2] = {a, b};
+    memcpy(&v, t, 16);
+  }
+  return v;
+}
+
 // epilogue: alpha * s (+ beta * y0 when beta != 0; y0 is not touched otherwise)
 template <class V>
 __device__ inline V axpby(V alpha, V s, bool has_beta, V beta, const V* y0) {
@@ -144,20 +226,21 @@ __device__ inline void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t b
       : "memory");
 }
 
-// Bounded wait for a barrier phase.  try_wait suspends the thread for a hardware-chosen slice
-// each time, so the limit below is generous in time yet finite: a lost copy ends the kernel
-// with an error bit instead of hanging the GPU.
-constexpr int kMbarSpinLimit = 1 << 20;
+// Bounded wait for a barrier phase.  Each try_wait lets the hardware suspend the warp for up to
+// the hinted time, so a waiting warp costs almost no issue slots; the iteration limit keeps the
+// total wait finite (a lost copy ends the kernel with an error bit instead of hanging the GPU).
+constexpr int kMbarSpinLimit = 1 << 18;
+constexpr uint32_t kMbarSuspendNs = 2000;
 
 __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
   uint32_t a = smem_addr(bar);
   for (int it = 0; it < kMbarSpinLimit; ++it) {
     uint32_t ok;
     asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; "
         "selp.u32 %0, 1, 0, p; }"
         : "=r"(ok)
-        : "r"(a), "r"(parity)
+        : "r"(a), "r"(parity), "r"(kMbarSuspendNs)
         : "memory");
     if (ok) return true;
   }
@@ -201,6 +284,10 @@ inline size_t isize(int itype) { return itype == B2S_I32 ? 4 : (itype == B2S_I64
     case B2S_I64: { using NAME = int64_t; __VA_ARGS__; } break; \
     default: return B2S_ERR_DTYPE;                             \
   }
+
+// run-time tuning knobs (b2s_tune)
+enum { KNOB_GATHER_POLICY = 0, KNOB_L2_FETCH = 1, KNOB_PERSIST_BYTES = 2, KNOB_COUNT = 16 };
+extern int64_t g_knobs[KNOB_COUNT];
 
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();

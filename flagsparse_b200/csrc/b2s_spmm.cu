@@ -191,10 +191,11 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   for (int k = tid; k < n_end; k += THREADS)
     row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
   if (tid == 0) row_end[n_end] = n_nz;
-  if (tx) {
+  // one warp waits for the copies; the CTA barrier that follows releases everybody else
+  if (tx && warp == 0) {
     if (!mbar_wait(bar, 0)) {
-      if (status) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
-      mbar_wait(bar, 0);
+      if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
+      mbar_wait(bar, 0);  // second bounded wait: do not leave with a copy in flight
     }
   }
   __syncthreads();

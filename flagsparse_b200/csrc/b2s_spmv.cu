@@ -16,23 +16,56 @@
 
 namespace b2s {
 
+#ifndef B2S_SPMV_THREADS
+#define B2S_SPMV_THREADS 128
+#endif
+#ifndef B2S_SPMV_ITEMS
+#define B2S_SPMV_ITEMS 1024
+#endif
+#ifndef B2S_SPMV_DIRECT
+#define B2S_SPMV_DIRECT 1  // 1: col / val straight from global memory; 0: staged by bulk copies
+#endif
+#ifndef B2S_SPMV_UNROLL
+#define B2S_SPMV_UNROLL 8
+#endif
+
 template <class V, class I>
 struct SpmvCfg {
-  static constexpr int THREADS = 256;
-  static constexpr int ITEMS = 2048;
+  static constexpr int THREADS = B2S_SPMV_THREADS;
+  static constexpr int ITEMS = B2S_SPMV_ITEMS;
 };
 
-constexpr int kWarpRowMax = 1024;   // longest in-tile row piece a single warp takes
-constexpr int kQueue2Cap = 512;     // queue of warp-per-row pieces (each longer than 8)
-constexpr int kQueue3Cap = 8;       // queue of CTA-per-row pieces (each longer than 1024)
+#ifdef B2S_PHASES
+__device__ unsigned long long g_phase_cycles[8];
+__device__ unsigned long long g_s1_by_T[16];
+#define B2S_TICK(n)                                                             \
+  do {                                                                          \
+    if (threadIdx.x == 0) {                                                     \
+      const long long now_ = clock64();                                         \
+      atomicAdd(&g_phase_cycles[n], static_cast<unsigned long long>(now_ - tick_)); \
+      tick_ = now_;                                                             \
+    }                                                                           \
+  } while (0)
+#else
+#define B2S_TICK(n)
+#endif
+
+static_assert(B2S_SPMV_ITEMS <= 4096, "queue capacities below assume at most 4096 items per tile");
+constexpr int kSpmvUnroll = B2S_SPMV_UNROLL;  // gathers in flight per thread
+constexpr int kThreadRowMax = 8;    // longest in-tile row piece one thread sums serially
+constexpr int kGroupRowMax = 64;    // longest piece a group of 8 lanes takes
+constexpr int kWarpRowMax = 1024;   // longest piece a single warp takes
+constexpr int kQueueACap = 512;     // pieces of 9..64 entries (at most ITEMS / 9)
+constexpr int kQueueBCap = 64;      // pieces of 65..1024 entries (at most ITEMS / 65)
+constexpr int kQueueCCap = 8;       // longer pieces (at most ITEMS / 1025 + 1)
 
 template <int THREADS, int ITEMS, class V, class I>
 constexpr size_t spmv_smem_bytes() {
   return 16                                   // mbarrier
          + sizeof(int) * (ITEMS + 4)          // row_end (+ padding to keep 16-byte alignment)
-         + sizeof(I) * ITEMS + 16             // staged columns
-         + sizeof(V) * ITEMS + 16             // staged values -> products
-         + sizeof(int) * (kQueue2Cap + kQueue3Cap + 4)  // queues + counters
+         + (B2S_SPMV_DIRECT ? 0 : sizeof(I) * ITEMS + 16)  // staged columns
+         + sizeof(V) * ITEMS + 32             // staged values -> products, then row sums
+         + sizeof(int) * (kQueueACap + kQueueBCap + kQueueCCap + 4)  // queues + counters
          + sizeof(V) * (THREADS / 32);        // per-warp partials
 }
 
@@ -41,15 +74,16 @@ __global__ void __launch_bounds__(THREADS)
 spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ x, const V* y_in, V* y, V* __restrict__ carry,
                  const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t nnz, V alpha,
-                 V beta, int has_beta, int32_t* status) {
+                 V beta, int has_beta, int gather_policy, int32_t* status) {
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
   int* row_end = reinterpret_cast<int*>(smem + 16);
   unsigned char* col_buf = smem + 16 + sizeof(int) * (ITEMS + 4);
-  unsigned char* val_buf = col_buf + sizeof(I) * ITEMS + 16;
-  int* queue2 = reinterpret_cast<int*>(val_buf + sizeof(V) * ITEMS + 16);
-  int* queue3 = queue2 + kQueue2Cap;
-  int* qcount = queue3 + kQueue3Cap;  // [0] = n2, [1] = n3
+  unsigned char* val_buf = col_buf + (B2S_SPMV_DIRECT ? 0 : sizeof(I) * ITEMS + 16);
+  int* queueA = reinterpret_cast<int*>(val_buf + sizeof(V) * ITEMS + 32);
+  int* queueB = queueA + kQueueACap;
+  int* queueC = queueB + kQueueBCap;
+  int* qcount = queueC + kQueueCCap;  // number of entries in queues A, B, C
   V* wpart = reinterpret_cast<V*>(qcount + 4);
 
   const int tid = threadIdx.x;
@@ -57,6 +91,9 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int warp = tid >> 5;
   // an earlier CTA already gave up on a copy: do not queue more waits behind it
   if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+#ifdef B2S_PHASES
+  long long tick_ = clock64();
+#endif
   const int64_t t = blockIdx.x;
   const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
   const int n_nz = static_cast<int>(tc.j1 - tc.j0);
@@ -64,141 +101,207 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
 
   const I* gcol = col + tc.j0;
   const V* gval = val + tc.j0;
-  const Staged<I> sc = stage_layout<I>(col_buf, gcol, n_nz);
-  const Staged<V> sv = stage_layout<V>(val_buf, gval, n_nz);
-  const uint32_t tx = stage_bytes(sc) + stage_bytes(sv);
-
+  V* prod_w;  // products of the tile, in shared memory
   if (tid == 0) {
     qcount[0] = 0;
     qcount[1] = 0;
-    if (tx) mbar_init(bar, 1);
+    qcount[2] = 0;
   }
-  __syncthreads();
-  if (tid == 0 && tx) {
-    const uint64_t pol = policy_evict_first();  // col / val are read once
-    mbar_expect_tx(bar, tx);
-    stage_issue(sc, gcol, bar, pol);
-    stage_issue(sv, gval, bar, pol);
-  }
-  // while the copies fly: ragged edges and the row ends of this tile
-  stage_edges(sc, gcol, n_nz, tid, THREADS);
-  stage_edges(sv, gval, n_nz, tid, THREADS);
-  for (int k = tid; k < n_end; k += THREADS)
-    row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
-  if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
-  if (tx) {
-    if (!mbar_wait(bar, 0)) {
-      if (status) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
-      mbar_wait(bar, 0);  // second bounded wait: do not leave with a copy in flight
+  if constexpr (B2S_SPMV_DIRECT) {
+    // col / val are read straight from global memory, coalesced, with all loads of a batch in
+    // flight before the gathers; measured cheaper for the load/store pipe than staging them
+    // (bulk-copy fills of shared memory and the re-reads count against the same data pipe)
+    prod_w = reinterpret_cast<V*>(val_buf);
+    for (int k = tid; k < n_end; k += THREADS)
+      row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
+    if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
+    const uint64_t once = policy_evict_first();
+    const uint64_t keep = policy_evict_last();
+    for (int base = tid; base < n_nz; base += kSpmvUnroll * THREADS) {
+      I c[kSpmvUnroll];
+      V a[kSpmvUnroll];
+#pragma unroll
+      for (int u = 0; u < kSpmvUnroll; ++u) {
+        const int i = base + u * THREADS;
+        if (i < n_nz) {
+          c[u] = stream_val(gcol + i, once);
+          a[u] = stream_val(gval + i, once);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kSpmvUnroll; ++u) {
+        const int i = base + u * THREADS;
+        if (i < n_nz) a[u] = a[u] * gather_val(x + static_cast<int64_t>(c[u]), gather_policy, keep);
+      }
+#pragma unroll
+      for (int u = 0; u < kSpmvUnroll; ++u) {
+        const int i = base + u * THREADS;
+        if (i < n_nz) prod_w[i] = a[u];
+      }
     }
-  }
-  __syncthreads();
-
-  // products, in place
-  {
+    __syncthreads();
+    B2S_TICK(1);
+  } else {
+    const Staged<I> sc = stage_layout<I>(col_buf, gcol, n_nz);
+    const Staged<V> sv = stage_layout<V>(val_buf, gval, n_nz);
+    const uint32_t tx = stage_bytes(sc) + stage_bytes(sv);
+    if (tid == 0 && tx) mbar_init(bar, 1);
+    __syncthreads();
+    if (tid == 0 && tx) {
+      const uint64_t pol = policy_evict_first();  // col / val are read once
+      mbar_expect_tx(bar, tx);
+      stage_issue(sc, gcol, bar, pol);
+      stage_issue(sv, gval, bar, pol);
+    }
+    // while the copies fly: ragged edges and the row ends of this tile
+    stage_edges(sc, gcol, n_nz, tid, THREADS);
+    stage_edges(sv, gval, n_nz, tid, THREADS);
+    for (int k = tid; k < n_end; k += THREADS)
+      row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
+    if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
+    // one warp waits for the copies; the CTA barrier that follows releases everybody else
+    if (tx && warp == 0) {
+      if (!mbar_wait(bar, 0)) {
+        if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
+        mbar_wait(bar, 0);  // second bounded wait: do not leave with a copy in flight
+      }
+    }
+    __syncthreads();
+    B2S_TICK(0);
     const I* scol = sc.s;
     V* sval = sv.s;
-#pragma unroll 4
-    for (int i = tid; i < n_nz; i += THREADS) {
-      const int64_t c = static_cast<int64_t>(scol[i]);
-      sval[i] = sval[i] * ldg_val(x + c);
+    prod_w = sv.s;
+    const uint64_t keep = policy_evict_last();
+    for (int base = tid; base < n_nz; base += kSpmvUnroll * THREADS) {
+      V xv[kSpmvUnroll];
+#pragma unroll
+      for (int u = 0; u < kSpmvUnroll; ++u) {
+        const int i = base + u * THREADS;
+        if (i < n_nz)
+          xv[u] = gather_val(x + static_cast<int64_t>(scol[i]), gather_policy, keep);
+      }
+#pragma unroll
+      for (int u = 0; u < kSpmvUnroll; ++u) {
+        const int i = base + u * THREADS;
+        if (i < n_nz) sval[i] = sval[i] * xv[u];
+      }
+    }
+    __syncthreads();
+    B2S_TICK(1);
+  }
+
+  const V* prod = prod_w;
+  V* rsum = prod_w + n_nz;  // row sums live behind the products (n_nz + n_end + 1 <= ITEMS + 1)
+  const bool open_row = tc.r1 < n_rows;
+  const int n_seg = n_end + 1;  // row pieces in the tile; the last one is the open row
+
+  // ---- bin the row pieces of the tile by length; the shortest are summed on the spot ----------
+  //   <= kThreadRowMax : one thread per piece, serial sum
+  //   <= kGroupRowMax  : queue A, a group of 8 lanes per piece (vector-per-row)
+  //   <= kWarpRowMax   : queue B, a warp per piece
+  //   longer           : queue C, the whole CTA per piece
+  for (int k = tid; k < n_seg; k += THREADS) {
+    const int s = k ? row_end[k - 1] : 0;
+    const int e = row_end[k];
+    const int len = e - s;
+    if (len <= kThreadRowMax) {
+      V acc = vt<V>::zero();
+      for (int i = s; i < e; ++i) acc = acc + prod[i];
+      rsum[k] = acc;
+    } else if (len <= kGroupRowMax) {
+      const int q = atomicAdd(&qcount[0], 1);
+      if (q < kQueueACap) queueA[q] = k;
+    } else if (len <= kWarpRowMax) {
+      const int q = atomicAdd(&qcount[1], 1);
+      if (q < kQueueBCap) queueB[q] = k;
+    } else {
+      const int q = atomicAdd(&qcount[2], 1);
+      if (q < kQueueCCap) queueC[q] = k;
     }
   }
   __syncthreads();
+  B2S_TICK(2);
 
-  const V* prod = sv.s;
-  const bool open_row = tc.r1 < n_rows;
-  const int n_seg = n_end + 1;  // row pieces in the tile; the last one is the open row
-  // lanes per row: power of two covering the mean piece length
-  int T = 1;
+  // ---- queue A: vector-per-row, 8 lanes per piece, butterfly reduction ------------------------
   {
-    const int mean = (n_nz + n_seg - 1) / n_seg;
-    while (T < mean && T < 32) T <<= 1;
-  }
-  const int p1max = (T == 32) ? kWarpRowMax : 8 * T;
-
-  // ---- strategy 1: vector-per-row ---------------------------------------------------------
-  {
-    const int sub = tid & (T - 1);
-    const int grp = tid / T;
-    const int n_grp = THREADS / T;
-    for (int kb = 0; kb < n_seg; kb += n_grp) {  // uniform trip count: shuffles stay converged
-      const int k = kb + grp;
-      const bool live = k < n_seg;
-      int s = 0, e = 0;
+    const int nA = min(qcount[0], kQueueACap);
+    const int sub = tid & 7;
+    const int grp = tid >> 3;
+    for (int qb = 0; qb < nA; qb += THREADS / 8) {  // uniform trip count: shuffles stay converged
+      const int q = qb + grp;
+      const bool live = q < nA;
+      int k = 0, s = 0, e = 0;
       if (live) {
+        k = queueA[q];
         s = k ? row_end[k - 1] : 0;
         e = row_end[k];
       }
-      const int len = e - s;
       V acc = vt<V>::zero();
-      if (len <= p1max) {
-        for (int i = s + sub; i < e; i += T) acc = acc + prod[i];
-      } else if (sub == 0) {
-        if (len <= kWarpRowMax) {
-          const int q = atomicAdd(&qcount[0], 1);
-          if (q < kQueue2Cap) queue2[q] = k;
-        } else {
-          const int q = atomicAdd(&qcount[1], 1);
-          if (q < kQueue3Cap) queue3[q] = k;
-        }
+      for (int i = s + sub; i < e; i += 8) acc = acc + prod[i];
+      acc = group_sum(acc, 8);
+      if (live && sub == 0) rsum[k] = acc;
+    }
+  }
+
+  // ---- queue B: warp-per-row -------------------------------------------------------------------
+  {
+    const int nB = min(qcount[1], kQueueBCap);
+    for (int q = warp; q < nB; q += THREADS / 32) {
+      const int k = queueB[q];
+      const int s = k ? row_end[k - 1] : 0;
+      const int e = row_end[k];
+      V acc = vt<V>::zero();
+      for (int i = s + lane; i < e; i += 32) acc = acc + prod[i];
+      acc = group_sum(acc, 32);
+      if (lane == 0) rsum[k] = acc;
+    }
+  }
+
+  // ---- queue C: CTA-per-row --------------------------------------------------------------------
+  {
+    const int nC = min(qcount[2], kQueueCCap);
+    for (int q = 0; q < nC; ++q) {
+      const int k = queueC[q];
+      const int s = k ? row_end[k - 1] : 0;
+      const int e = row_end[k];
+      V acc = vt<V>::zero();
+      for (int i = s + tid; i < e; i += THREADS) acc = acc + prod[i];
+      acc = group_sum(acc, 32);
+      if (lane == 0) wpart[warp] = acc;
+      __syncthreads();
+      if (tid == 0) {
+        V tot = wpart[0];
+#pragma unroll
+        for (int w = 1; w < THREADS / 32; ++w) tot = tot + wpart[w];
+        rsum[k] = tot;
       }
-      acc = group_sum(acc, T);
-      if (live && sub == 0 && len <= p1max) {
-        if (k < n_end) {
-          const int64_t r = tc.r0 + k;
-          y[r] = axpby(alpha, acc, has_beta != 0, beta, y_in + r);
-        } else if (open_row) {
-          carry[t] = acc;
-        }
-      }
+      __syncthreads();
     }
   }
   __syncthreads();
+  B2S_TICK(3);
 
-  // ---- strategy 2: warp-per-row -----------------------------------------------------------
-  const int n2 = min(qcount[0], kQueue2Cap);
-  for (int q = warp; q < n2; q += THREADS / 32) {
-    const int k = queue2[q];
-    const int s = k ? row_end[k - 1] : 0;
-    const int e = row_end[k];
-    V acc = vt<V>::zero();
-    for (int i = s + lane; i < e; i += 32) acc = acc + prod[i];
-    acc = group_sum(acc, 32);
-    if (lane == 0) {
-      if (k < n_end) {
-        const int64_t r = tc.r0 + k;
-        y[r] = axpby(alpha, acc, has_beta != 0, beta, y_in + r);
-      } else if (open_row) {
-        carry[t] = acc;
-      }
-    }
-  }
-
-  // ---- strategy 3: CTA-per-row ------------------------------------------------------------
-  const int n3 = min(qcount[1], kQueue3Cap);
-  for (int q = 0; q < n3; ++q) {
-    const int k = queue3[q];
-    const int s = k ? row_end[k - 1] : 0;
-    const int e = row_end[k];
-    V acc = vt<V>::zero();
-    for (int i = s + tid; i < e; i += THREADS) acc = acc + prod[i];
-    acc = group_sum(acc, 32);
-    if (lane == 0) wpart[warp] = acc;
-    __syncthreads();
-    if (tid == 0) {
-      V tot = wpart[0];
+  // ---- epilogue: the rows that end in this tile are consecutive, so y is read and written
+  // coalesced, with every load of a batch issued before the first store
+  for (int kb = 0; kb < n_end; kb += 4 * THREADS) {
+    V old[4];
 #pragma unroll
-      for (int w = 1; w < THREADS / 32; ++w) tot = tot + wpart[w];
+    for (int u = 0; u < 4; ++u) {
+      const int k = kb + u * THREADS + tid;
+      old[u] = (has_beta && k < n_end) ? y_in[tc.r0 + k] : vt<V>::zero();
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = kb + u * THREADS + tid;
       if (k < n_end) {
-        const int64_t r = tc.r0 + k;
-        y[r] = axpby(alpha, tot, has_beta != 0, beta, y_in + r);
-      } else if (open_row) {
-        carry[t] = tot;
+        V r = alpha * rsum[k];
+        if (has_beta) r = r + beta * old[u];
+        y[tc.r0 + k] = r;
       }
     }
-    __syncthreads();
   }
+  if (tid == 0 && open_row) carry[t] = rsum[n_end];
+  B2S_TICK(4);
 }
 
 // Adds to each row that began in an earlier tile the partial sums those tiles left behind,
@@ -220,7 +323,7 @@ __global__ void spmv_fixup_kernel(V* y, const V* __restrict__ carry,
 
 template <class V, class I, class P>
 int spmv_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
-                int64_t nnz, const void* x, const void* y_in, void* y, const void* alpha,
+                int64_t n_cols, int64_t nnz, const void* x, const void* y_in, void* y, const void* alpha,
                 const void* beta, const int64_t* tile_row, void* carry, int32_t* status,
                 cudaStream_t stream) {
   using Cfg = SpmvCfg<V, I>;
@@ -235,10 +338,30 @@ int spmv_launch(const void* data, const void* indices, const void* indptr, int64
   auto kern = spmv_tile_kernel<V, I, P, THREADS, ITEMS>;
   constexpr size_t smem = spmv_smem_bytes<THREADS, ITEMS, V, I>();
   ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
-  kern<<<static_cast<unsigned>(n_tiles), THREADS, smem, stream>>>(
-      static_cast<const V*>(data), static_cast<const I*>(indices),
-      static_cast<const P*>(indptr), static_cast<const V*>(x), static_cast<const V*>(y_in),
-      static_cast<V*>(y), static_cast<V*>(carry), tile_row, n_rows, nnz, a, b, has_beta, status);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(n_tiles));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (g_knobs[KNOB_PERSIST_BYTES] > 0 && n_cols > 0) {
+    // keep as much of x as the persisting carve-out holds; the rest is treated as streaming
+    const double x_bytes = static_cast<double>(n_cols) * sizeof(V);
+    attr[0].id = cudaLaunchAttributeAccessPolicyWindow;
+    attr[0].val.accessPolicyWindow.base_ptr = const_cast<void*>(x);
+    attr[0].val.accessPolicyWindow.num_bytes = static_cast<size_t>(x_bytes);
+    double ratio = static_cast<double>(g_knobs[KNOB_PERSIST_BYTES]) / x_bytes;
+    attr[0].val.accessPolicyWindow.hitRatio = static_cast<float>(ratio > 1.0 ? 1.0 : ratio);
+    attr[0].val.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+    attr[0].val.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, kern, static_cast<const V*>(data), static_cast<const I*>(indices),
+                     static_cast<const P*>(indptr), static_cast<const V*>(x),
+                     static_cast<const V*>(y_in), static_cast<V*>(y), static_cast<V*>(carry),
+                     tile_row, n_rows, nnz, a, b, has_beta,
+                     static_cast<int>(g_knobs[KNOB_GATHER_POLICY]), status);
   if (n_tiles > 1) {
     const int fb = 256;
     spmv_fixup_kernel<V><<<static_cast<unsigned>((n_tiles + fb - 1) / fb), fb, 0, stream>>>(
@@ -248,6 +371,21 @@ int spmv_launch(const void* data, const void* indices, const void* indptr, int64
 }
 
 }  // namespace b2s
+
+#ifdef B2S_PHASES
+extern "C" int b2s_debug_phases(unsigned long long* out8, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out8, b2s::g_phase_cycles, sizeof(unsigned long long) * 8);
+  cudaMemcpyFromSymbol(out8 + 8, b2s::g_s1_by_T, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[8] = {0};
+    cudaMemcpyToSymbol(b2s::g_phase_cycles, z, sizeof(z));
+    unsigned long long z2[16] = {0};
+    cudaMemcpyToSymbol(b2s::g_s1_by_T, z2, sizeof(z2));
+  }
+  return 0;
+}
+#endif
 
 extern "C" int b2s_spmv_tile_items(int val_type, int idx_type) {
   (void)val_type;
@@ -274,7 +412,7 @@ extern "C" int b2s_spmv_csr(int val_type, int idx_type, int ptr_type, const void
     return B2S_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
-    return (b2s::spmv_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, nnz, x_dev,
+    return (b2s::spmv_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, x_dev,
                                       y_in_dev, y_dev, alpha, beta, tile_row_dev, carry_dev,
                                       status_dev, s));
   })));

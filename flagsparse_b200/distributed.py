@@ -1,0 +1,129 @@
+"""Row-partitioned CSR SpMV / SpMM over several GPUs of one node (one process per GPU).
+
+FlagSparse has no distributed code (no NCCL, no torch.distributed anywhere in its tree); its only
+multi-GPU feature is the test runner spreading operators over devices.  This module is therefore
+new: output rows are independent, so the matrix is cut into contiguous row blocks holding equal
+shares of the non-zeros, x / B is replicated (broadcast from one rank), every rank multiplies its
+block with the single-GPU kernels, and the row blocks of y / C are all-gathered.
+
+The collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs; gloo on CPU for the
+tests of the host logic, where ``local_spmv`` / ``local_spmm`` are injected because the product
+kernels have no CPU path).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def partition_rows_by_nnz(indptr, parts):
+    """Row boundaries r_0=0 <= r_1 <= ... <= r_parts=n_rows such that block p holds about
+    nnz/parts non-zeros: r_p is the first row whose start offset reaches p*nnz/parts."""
+    n_rows = int(indptr.numel()) - 1
+    nnz = int(indptr[-1].item()) if n_rows >= 0 else 0
+    targets = torch.tensor([(p * nnz) // parts for p in range(1, parts)], dtype=indptr.dtype,
+                           device=indptr.device)
+    inner = torch.searchsorted(indptr[:-1].contiguous(), targets, right=False)
+    bounds = [0] + [min(int(v), n_rows) for v in inner.tolist()] + [n_rows]
+    for i in range(1, len(bounds)):  # monotone even for degenerate inputs
+        bounds[i] = max(bounds[i], bounds[i - 1])
+    return bounds
+
+
+def slice_rows(data, indices, indptr, r0, r1):
+    """CSR arrays of rows r0..r1-1 with indptr re-based to zero."""
+    j0, j1 = int(indptr[r0].item()), int(indptr[r1].item())
+    return data[j0:j1], indices[j0:j1], (indptr[r0:r1 + 1] - indptr[r0])
+
+
+def _default_local_spmv(data, indices, indptr, x, shape, **kw):
+    from .spmv import flagsparse_spmv_csr
+    return flagsparse_spmv_csr(data, indices, indptr, x, shape, **kw)
+
+
+def _default_local_spmm(data, indices, indptr, B, shape, **kw):
+    from .spmm import flagsparse_spmm_csr
+    return flagsparse_spmm_csr(data, indices, indptr, B, shape, **kw)
+
+
+class RowPartitionedCsr:
+    """This rank's row block of a CSR matrix whose rows are spread over the process group."""
+
+    def __init__(self, data, indices, indptr, n_cols, group=None, local_spmv=None,
+                 local_spmm=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.data, self.indices, self.indptr = data, indices, indptr
+        self.n_local = int(indptr.numel()) - 1
+        self.n_cols = int(n_cols)
+        self.local_spmv = local_spmv or _default_local_spmv
+        self.local_spmm = local_spmm or _default_local_spmm
+        counts = [None] * self.world
+        dist.all_gather_object(counts, self.n_local, group=group)
+        self.rows_per_rank = [int(c) for c in counts]
+        self.max_rows = max(self.rows_per_rank) if self.rows_per_rank else 0
+        self.n_rows = sum(self.rows_per_rank)
+        self.row_offset = sum(self.rows_per_rank[: self.rank])
+        self._pads = {}
+
+    @classmethod
+    def from_global(cls, data, indices, indptr, shape, group=None, **kw):
+        """Every rank passes the same full matrix (or a view of it) and keeps its own block."""
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        bounds = partition_rows_by_nnz(indptr, world)
+        d, i, p = slice_rows(data, indices, indptr, bounds[rank], bounds[rank + 1])
+        return cls(d.contiguous(), i.contiguous(), p.contiguous(), shape[1], group=group, **kw)
+
+    # -- collectives ---------------------------------------------------------------------------
+    def broadcast_dense(self, dense, src=0):
+        """Replicate x / B: `dense` holds the data on `src` and is overwritten elsewhere."""
+        dist.broadcast(dense, src=src, group=self.group)
+        return dense
+
+    def _padded(self, trailing, dtype, device):
+        key = (tuple(trailing), dtype, device)
+        bufs = self._pads.get(key)
+        if bufs is None:
+            mine = torch.zeros((self.max_rows, *trailing), dtype=dtype, device=device)
+            everyone = torch.empty((self.world * self.max_rows, *trailing), dtype=dtype,
+                                   device=device)
+            bufs = self._pads[key] = (mine, everyone)
+        return bufs
+
+    def gather_rows(self, local, out=None):
+        """All-gather the row blocks (unequal heights are padded to the tallest block for the
+        collective and cut back afterwards).  Returns the full y / C on every rank."""
+        trailing = tuple(local.shape[1:])
+        mine, everyone = self._padded(trailing, local.dtype, local.device)
+        mine[: self.n_local].copy_(local)
+        dist.all_gather_into_tensor(everyone, mine, group=self.group)
+        if out is None:
+            out = torch.empty((self.n_rows, *trailing), dtype=local.dtype, device=local.device)
+        off = 0
+        for p, rows in enumerate(self.rows_per_rank):
+            out[off:off + rows].copy_(everyone[p * self.max_rows: p * self.max_rows + rows])
+            off += rows
+        return out
+
+    # -- products ------------------------------------------------------------------------------
+    def spmv_local(self, x, out=None, alpha=1.0, beta=0.0):
+        return self.local_spmv(self.data, self.indices, self.indptr, x,
+                               (self.n_local, self.n_cols), out=out, alpha=alpha, beta=beta)
+
+    def spmm_local(self, B, out=None, alpha=1.0, beta=0.0):
+        return self.local_spmm(self.data, self.indices, self.indptr, B,
+                               (self.n_local, self.n_cols), out=out, alpha=alpha, beta=beta)
+
+    def spmv(self, x, src=0, out_local=None, out=None, alpha=1.0, beta=0.0):
+        """y = alpha * A x + beta * y0 with x taken from rank `src`; y0 is this rank's block in
+        out_local.  Returns the assembled y on every rank."""
+        self.broadcast_dense(x, src)
+        y_local = self.spmv_local(x, out=out_local, alpha=alpha, beta=beta)
+        return self.gather_rows(y_local, out=out)
+
+    def spmm(self, B, src=0, out_local=None, out=None, alpha=1.0, beta=0.0):
+        self.broadcast_dense(B, src)
+        C_local = self.spmm_local(B, out=out_local, alpha=alpha, beta=beta)
+        return self.gather_rows(C_local, out=out)

@@ -48,6 +48,12 @@ typedef void* b2s_stream;
 int b2s_version(void);
 const char* b2s_status_string(int status);
 
+/* Run-time tuning knobs of the kernels (no counterpart in the reference, whose tuning lives in
+ * Python keyword arguments such as block_nnz, spmv_csr.py:819-820).  Knob 0: L2 eviction hint on
+ * the x gather (0 none, 1 evict-last).  Knob 1: L2 fetch granularity in bytes for this context.
+ * Knob 2: bytes of x kept in the persisting part of L2 (0 = off). */
+int b2s_tune(int knob, int64_t value);
+
 /* ---- input contract ------------------------------------------------------------------------
  * Replaces the device reductions behind the `.item()` checks of _prepare_spmv_csr_matrix
  * (spmv_csr.py:546-563) and _prepare_spmm_csr_matrix (spmm_csr.py:268-296).  One pass over
