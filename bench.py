@@ -191,7 +191,19 @@ def make_step(p, kind):
         def step():
             flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape, out=out, op=op,
                                 alpha=alpha, beta=beta)
-    return step, out, 2  # tile kernel + carry fix-up kernel
+    return step, out, 2  # tile kernel + carry fix-up kernel (+ panel combine, see main)
+
+
+def uses_panels(p, kind):
+    """True when the SpMV of this problem runs on the column-panel layout (one more launch)."""
+    if kind != "spmv":
+        return False
+    from flagsparse_b200 import _plan
+    key = _plan.plan_key("spmv", p.data, p.indices, p.indptr, p.shape)
+    plan = _plan.cache_get(key)
+    if plan is not None and p.extra.get("op", "non") != "non":
+        plan = plan.transposed(conj=p.extra.get("op") == "conj")
+    return bool(plan is not None and plan.panels() is not None)
 
 
 def time_device(step, steps, warmup, sampler=None):
@@ -443,7 +455,7 @@ def main():
                      "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind},
         "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": (launches_per_step + (1 if uses_panels(p, kind) else 0)) * args.steps,
         "clocks": sampler.summary(),
         "extra": extra,
     }

@@ -41,6 +41,32 @@ def inspect_csr(indices, indptr, n_rows, nnz):
     return [int(v) for v in stats.tolist()]
 
 
+# Column-panel layout for SpMV (b2s_panel_build).  "auto": used when x does not fit the part of L2
+# that survives the col / val stream; "off": never.
+PANEL_POLICY = "auto"
+PANEL_TRIGGER_BYTES = 48 << 20   # x larger than this is split into panels
+PANEL_TARGET_BYTES = 40 << 20    # largest x slice of one panel
+PANEL_MIN_NNZ = 1 << 22          # below this the conversion is not worth its memory
+
+
+def set_panel_policy(policy):
+    """'auto' (default) or 'off': whether SpMV may keep a column-panel copy of large matrices."""
+    global PANEL_POLICY
+    if policy not in ("auto", "off"):
+        raise ValueError("panel policy must be 'auto' or 'off'")
+    PANEL_POLICY = policy
+
+
+class PanelLayout:
+    """The matrix as a stack of column panels (see include/b200sparse.h, b2s_panel_build)."""
+
+    def __init__(self, data, cols, ptr, panel_start, n_panels, shift):
+        self.data, self.cols, self.ptr, self.panel_start = data, cols, ptr, panel_start
+        self.n_panels, self.shift = n_panels, shift
+        self.pcode = _lib.INDEX_CODE[ptr.dtype]
+        self.tiles = {}
+
+
 class CsrPlan:
     """Device arrays of one CSR matrix plus everything derived from them."""
 
@@ -61,6 +87,7 @@ class CsrPlan:
         self._tiles = {}                     # tile_items -> (T, int64[T+1])
         self._scratch = {}                   # (tag, width, stream) -> tensor
         self._transposed = {}                # conj flag -> CsrPlan of the transpose
+        self._panels = False                 # False: not decided yet; None: not used
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.status_checked = False
 
@@ -91,6 +118,58 @@ class CsrPlan:
                               device=self.device)
             self._scratch[key] = buf
         return buf
+
+    # -- column panels ------------------------------------------------------------------------
+    def panels(self):
+        """PanelLayout when the policy asks for one for this matrix, else None (built once)."""
+        if self._panels is not False:
+            return self._panels
+        self._panels = None
+        vbytes = self.data.element_size()
+        if (PANEL_POLICY != "auto" or self.n_cols * vbytes <= PANEL_TRIGGER_BYTES
+                or self.nnz < PANEL_MIN_NNZ or self.n_rows == 0):
+            return None
+        shift = 1
+        while (2 << shift) * vbytes <= PANEL_TARGET_BYTES:
+            shift += 1
+        n_panels = ((self.n_cols - 1) >> shift) + 1
+        if n_panels < 2 or n_panels > 256 or shift > 31:
+            return None
+        lib = _lib.load()
+        ptr_dtype = torch.int32 if self.nnz <= INDEX_LIMIT_INT32 else torch.int64
+        p_data = torch.empty_like(self.data)
+        p_cols = torch.empty(self.nnz, dtype=torch.int32, device=self.device)
+        p_ptr = torch.empty(n_panels * self.n_rows + 1, dtype=ptr_dtype, device=self.device)
+        panel_start = torch.empty(n_panels + 1, dtype=torch.int64, device=self.device)
+        nbytes = int(lib.b2s_panel_bytes(self.n_cols, self.nnz))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            st = lib.b2s_panel_build(
+                self.vcode, self.icode, self.pcode, _lib.ptr(self.data), _lib.ptr(self.indices),
+                _lib.ptr(self.indptr), self.n_rows, self.n_cols, self.nnz, n_panels, shift,
+                _lib.ptr(p_data), _lib.ptr(p_cols), _lib.ptr(p_ptr),
+                _lib.INDEX_CODE[ptr_dtype], _lib.ptr(panel_start), _lib.ptr(ws), nbytes,
+                _lib.stream_handle(self.device))
+        _lib.check(st, "b2s_panel_build")
+        del ws
+        self._panels = PanelLayout(p_data, p_cols, p_ptr, panel_start, n_panels, shift)
+        return self._panels
+
+    def panel_tiles(self, items):
+        lay = self._panels
+        hit = lay.tiles.get(items)
+        if hit is not None:
+            return hit
+        lib = _lib.load()
+        rows = lay.n_panels * self.n_rows
+        n_tiles = int(lib.b2s_tile_count(rows, self.nnz, items))
+        tile_row = torch.empty(n_tiles + 1, dtype=torch.int64, device=self.device)
+        with torch.cuda.device(self.device):
+            st = lib.b2s_tile_plan(_lib.ptr(lay.ptr), lay.pcode, rows, self.nnz, items,
+                                   _lib.ptr(tile_row), _lib.stream_handle(self.device))
+        _lib.check(st, "b2s_tile_plan")
+        lay.tiles[items] = (n_tiles, tile_row)
+        return lay.tiles[items]
 
     # -- transpose ----------------------------------------------------------------------------
     def transposed(self, conj):

@@ -28,21 +28,25 @@ __host__ __device__ inline c128 operator*(c128 a, c128 b) {
 template <class V> struct vt;
 template <> struct vt<float> {
   __host__ __device__ static float zero() { return 0.f; }
+  __host__ __device__ static float one() { return 1.f; }
   __host__ __device__ static bool is_zero(float a) { return a == 0.f; }
   __host__ __device__ static float conj(float a) { return a; }
 };
 template <> struct vt<double> {
   __host__ __device__ static double zero() { return 0.0; }
+  __host__ __device__ static double one() { return 1.0; }
   __host__ __device__ static bool is_zero(double a) { return a == 0.0; }
   __host__ __device__ static double conj(double a) { return a; }
 };
 template <> struct vt<c64> {
   __host__ __device__ static c64 zero() { return {0.f, 0.f}; }
+  __host__ __device__ static c64 one() { return {1.f, 0.f}; }
   __host__ __device__ static bool is_zero(c64 a) { return a.re == 0.f && a.im == 0.f; }
   __host__ __device__ static c64 conj(c64 a) { return {a.re, -a.im}; }
 };
 template <> struct vt<c128> {
   __host__ __device__ static c128 zero() { return {0.0, 0.0}; }
+  __host__ __device__ static c128 one() { return {1.0, 0.0}; }
   __host__ __device__ static bool is_zero(c128 a) { return a.re == 0.0 && a.im == 0.0; }
   __host__ __device__ static c128 conj(c128 a) { return {a.re, -a.im}; }
 };

@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(THREADS)
 spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ x, const V* y_in, V* y, V* __restrict__ carry,
                  const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t nnz, V alpha,
-                 V beta, int has_beta, int gather_policy, int32_t* status) {
+                 V beta, int has_beta, int gather_policy, int32_t* status,
+                 const int64_t* __restrict__ panel_start, int n_panels, int panel_shift) {
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
   int* row_end = reinterpret_cast<int*>(smem + 16);
@@ -117,6 +118,19 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
     const uint64_t once = policy_evict_first();
     const uint64_t keep = policy_evict_last();
+    // column-panel layout: the matrix is a stack of panels, columns are panel-local and the
+    // non-zeros of panel p start at panel_start[p]; find the panel of the tile's first entry
+    int p_lo = 0;
+    int64_t p_next = INT64_MAX;  // first non-zero (global index) of the panel after p_lo
+    if (panel_start != nullptr && n_nz > 0) {
+      int lo = 0, hi = n_panels - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (panel_start[mid] <= tc.j0) lo = mid; else hi = mid - 1;
+      }
+      p_lo = lo;
+      p_next = panel_start[p_lo + 1];
+    }
     for (int base = tid; base < n_nz; base += kSpmvUnroll * THREADS) {
       I c[kSpmvUnroll];
       V a[kSpmvUnroll];
@@ -131,7 +145,18 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
 #pragma unroll
       for (int u = 0; u < kSpmvUnroll; ++u) {
         const int i = base + u * THREADS;
-        if (i < n_nz) a[u] = a[u] * gather_val(x + static_cast<int64_t>(c[u]), gather_policy, keep);
+        if (i < n_nz) {
+          int64_t xc = static_cast<int64_t>(c[u]);
+          if (panel_start != nullptr) {
+            int pp = p_lo;
+            if (tc.j0 + i >= p_next) {  // rare: the tile straddles a panel border
+              ++pp;
+              while (pp + 1 < n_panels && tc.j0 + i >= panel_start[pp + 1]) ++pp;
+            }
+            xc += static_cast<int64_t>(pp) << panel_shift;
+          }
+          a[u] = a[u] * gather_val(x + xc, gather_policy, keep);
+        }
       }
 #pragma unroll
       for (int u = 0; u < kSpmvUnroll; ++u) {
@@ -325,7 +350,8 @@ template <class V, class I, class P>
 int spmv_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* x, const void* y_in, void* y, const void* alpha,
                 const void* beta, const int64_t* tile_row, void* carry, int32_t* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, const int64_t* panel_start = nullptr, int n_panels = 0,
+                int panel_shift = 0) {
   using Cfg = SpmvCfg<V, I>;
   constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
   const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
@@ -361,12 +387,53 @@ int spmv_launch(const void* data, const void* indices, const void* indptr, int64
                      static_cast<const P*>(indptr), static_cast<const V*>(x),
                      static_cast<const V*>(y_in), static_cast<V*>(y), static_cast<V*>(carry),
                      tile_row, n_rows, nnz, a, b, has_beta,
-                     static_cast<int>(g_knobs[KNOB_GATHER_POLICY]), status);
+                     static_cast<int>(g_knobs[KNOB_GATHER_POLICY]), status, panel_start, n_panels,
+                     panel_shift);
   if (n_tiles > 1) {
     const int fb = 256;
     spmv_fixup_kernel<V><<<static_cast<unsigned>((n_tiles + fb - 1) / fb), fb, 0, stream>>>(
         static_cast<V*>(y), static_cast<const V*>(carry), tile_row, n_tiles, a);
   }
+  return launch_status();
+}
+
+// y[r] = alpha * (ypart[0][r] + ypart[1][r] + ...) + beta * y_in[r]; panels are added in
+// ascending order, so the result does not depend on scheduling.
+template <class V>
+__global__ void panel_combine_kernel(const V* __restrict__ ypart, int64_t n_rows, int n_panels,
+                                     const V* y_in, V* y, V alpha, V beta, int has_beta) {
+  const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (r >= n_rows) return;
+  V s = ypart[r];
+  for (int p = 1; p < n_panels; ++p) s = s + ypart[p * n_rows + r];
+  V out = alpha * s;
+  if (has_beta) out = out + beta * y_in[r];
+  y[r] = out;
+}
+
+template <class V, class P>
+int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_ptr,
+                       int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                       const int64_t* panel_start, const void* x, const void* y_in, void* y,
+                       const void* alpha, const void* beta, const int64_t* tile_row, void* carry,
+                       void* ypart, int32_t* status, cudaStream_t stream) {
+  // 1) the stacked matrix (n_panels * n_rows rows, panel-local int32 columns) times x with
+  //    alpha = 1, beta = 0 -> one partial result per (panel, row)
+  const V one = vt<V>::one(), zero = vt<V>::zero();
+  int st = spmv_launch<V, int32_t, P>(p_data, p_cols, p_ptr, n_rows * n_panels, n_cols, nnz, x,
+                                      nullptr, ypart, &one, &zero, tile_row, carry, status,
+                                      stream, panel_start, n_panels, panel_shift);
+  if (st != B2S_OK) return st;
+  // 2) add the panels of each row and apply alpha / beta
+  const V a = *static_cast<const V*>(alpha);
+  const V b = *static_cast<const V*>(beta);
+  const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
+  if (has_beta && y_in == nullptr) return B2S_ERR_ARG;
+  const int threads = 256;
+  panel_combine_kernel<V><<<static_cast<unsigned>((n_rows + threads - 1) / threads), threads, 0,
+                            stream>>>(static_cast<const V*>(ypart), n_rows, n_panels,
+                                      static_cast<const V*>(y_in), static_cast<V*>(y), a, b,
+                                      has_beta);
   return launch_status();
 }
 
@@ -391,6 +458,36 @@ extern "C" int b2s_spmv_tile_items(int val_type, int idx_type) {
   (void)val_type;
   (void)idx_type;
   return b2s::SpmvCfg<float, int32_t>::ITEMS;
+}
+
+extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_dev,
+                               const int32_t* p_cols_dev, const void* p_ptr_dev, int64_t n_rows,
+                               int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                               const int64_t* panel_start_dev, const void* x_dev,
+                               const void* y_in_dev, void* y_dev, const void* alpha,
+                               const void* beta, const int64_t* tile_row_dev, void* carry_dev,
+                               void* ypart_dev, int32_t* status_dev, b2s_stream stream) {
+  if (n_rows < 0 || n_cols < 0 || nnz < 0 || !alpha || !beta) return B2S_ERR_ARG;
+  if (n_panels < 1 || n_panels > 256 || panel_shift < 0 || panel_shift > 40) return B2S_ERR_ARG;
+  if (n_rows == 0) return B2S_OK;
+  if (!p_ptr_dev || !y_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
+    return B2S_ERR_ARG;
+  if (nnz > 0 && (!p_data_dev || !p_cols_dev || !x_dev)) return B2S_ERR_ARG;
+  const size_t vs = b2s::vsize(val_type);
+  if (vs == 0) return B2S_ERR_DTYPE;
+  const uintptr_t m = vs - 1;
+  if ((reinterpret_cast<uintptr_t>(p_data_dev) & m) || (reinterpret_cast<uintptr_t>(x_dev) & m) ||
+      (reinterpret_cast<uintptr_t>(y_dev) & m) || (reinterpret_cast<uintptr_t>(y_in_dev) & m) ||
+      (reinterpret_cast<uintptr_t>(carry_dev) & m) || (reinterpret_cast<uintptr_t>(ypart_dev) & m))
+    return B2S_ERR_ALIGNMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(ptr_type, P, {
+    return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
+                                          n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
+                                          y_dev, alpha, beta, tile_row_dev, carry_dev, ypart_dev,
+                                          status_dev, s));
+  }));
+  return B2S_ERR_DTYPE;
 }
 
 extern "C" int b2s_spmv_csr(int val_type, int idx_type, int ptr_type, const void* data_dev,

@@ -260,7 +260,115 @@ int csr2csc_run(const void* data, const void* indices, const void* indptr, int64
   return launch_status();
 }
 
+// ---- column-panel layout ------------------------------------------------------------------------
+// The non-zeros are stably sorted by panel id = col >> panel_shift (one radix pass), so the result
+// is a stack of n_panels CSR matrices over the same rows, each touching only its own slice of x.
+// Columns become panel-local int32; stacked row p * n_rows + r holds the entries of row r that
+// fall into panel p, in their original order.
+template <class V, class P, class W>
+__global__ void panel_gather_kernel(const V* __restrict__ data, const P* __restrict__ ptr,
+                                    int64_t n_rows, const W* __restrict__ sorted_cols,
+                                    const W* __restrict__ src_pos, int64_t nnz, int panel_shift,
+                                    V* __restrict__ p_data, int32_t* __restrict__ p_cols,
+                                    int64_t* __restrict__ stacked_row) {
+  const int64_t k = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (k >= nnz) return;
+  const int64_t j = static_cast<int64_t>(src_pos[k]);
+  const int64_t c = static_cast<int64_t>(sorted_cols[k]);
+  int64_t lo = 0, hi = n_rows;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (static_cast<int64_t>(ptr[mid + 1]) <= j)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  p_data[k] = data[j];
+  p_cols[k] = static_cast<int32_t>(c & ((int64_t{1} << panel_shift) - 1));
+  stacked_row[k] = (c >> panel_shift) * n_rows + lo;
+}
+
+template <class PP>
+__global__ void panel_start_kernel(const PP* __restrict__ p_ptr, int64_t n_rows, int n_panels,
+                                   int64_t* __restrict__ panel_start) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p <= n_panels) panel_start[p] = static_cast<int64_t>(p_ptr[p * n_rows]);
+}
+
+template <class W>
+int64_t panel_scratch_bytes(int64_t nnz) {
+  const int64_t n_blocks = (nnz + kRxChunk - 1) / kRxChunk;
+  const int64_t hist = 256 * n_blocks;
+  return 2 * align256(nnz * sizeof(W)) + align256(hist * sizeof(W)) +
+         align256(scan_scratch_elems(hist) * sizeof(W)) + align256(nnz * sizeof(int64_t));
+}
+
+template <class V, class I, class P, class PP, class W>
+int panel_build_run(const void* data, const void* indices, const void* indptr, int64_t n_rows,
+                    int64_t nnz, int n_panels, int panel_shift, void* p_data, int32_t* p_cols,
+                    void* p_ptr, int64_t* panel_start, void* scratch, int64_t scratch_bytes,
+                    cudaStream_t s) {
+  if (panel_scratch_bytes<W>(nnz) > scratch_bytes) return B2S_ERR_WORKSPACE;
+  unsigned char* p = static_cast<unsigned char*>(scratch);
+  W* keys = reinterpret_cast<W*>(p); p += align256(nnz * sizeof(W));
+  W* vals = reinterpret_cast<W*>(p); p += align256(nnz * sizeof(W));
+  const int64_t n_blocks = (nnz + kRxChunk - 1) / kRxChunk;
+  const int64_t hist_n = 256 * n_blocks;
+  W* hist = reinterpret_cast<W*>(p); p += align256(hist_n * sizeof(W));
+  W* scan_ws = reinterpret_cast<W*>(p); p += align256(scan_scratch_elems(hist_n) * sizeof(W));
+  int64_t* stacked = reinterpret_cast<int64_t*>(p);
+  const unsigned grid = static_cast<unsigned>(n_blocks);
+  radix_hist_kernel<W, I><<<grid, kRxThreads, 0, s>>>(static_cast<const I*>(indices), nnz,
+                                                      panel_shift, hist, n_blocks);
+  exclusive_scan<W>(hist, hist_n, scan_ws, s);
+  radix_scatter_kernel<W, I><<<grid, kRxThreads, 0, s>>>(static_cast<const I*>(indices), nullptr,
+                                                         keys, vals, nnz, panel_shift, hist,
+                                                         n_blocks);
+  panel_gather_kernel<V, P, W><<<static_cast<unsigned>((nnz + 255) / 256), 256, 0, s>>>(
+      static_cast<const V*>(data), static_cast<const P*>(indptr), n_rows, keys, vals, nnz,
+      panel_shift, static_cast<V*>(p_data), p_cols, stacked);
+  csc_ptr_kernel<int64_t, PP><<<static_cast<unsigned>((nnz + 1 + 255) / 256), 256, 0, s>>>(
+      stacked, nnz, n_rows * n_panels, static_cast<PP*>(p_ptr));
+  panel_start_kernel<PP><<<(n_panels + 1 + 63) / 64, 64, 0, s>>>(static_cast<const PP*>(p_ptr),
+                                                                 n_rows, n_panels, panel_start);
+  return launch_status();
+}
+
 }  // namespace b2s
+
+extern "C" int64_t b2s_panel_bytes(int64_t n_cols, int64_t nnz) {
+  if (nnz <= 0) return 256;
+  return b2s::wide_needed(n_cols, nnz) ? b2s::panel_scratch_bytes<uint64_t>(nnz)
+                                       : b2s::panel_scratch_bytes<uint32_t>(nnz);
+}
+
+extern "C" int b2s_panel_build(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                               const void* indices_dev, const void* indptr_dev, int64_t n_rows,
+                               int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                               void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev,
+                               int p_ptr_type, int64_t* panel_start_dev, void* scratch_dev,
+                               int64_t scratch_bytes, b2s_stream stream) {
+  if (n_rows <= 0 || n_cols <= 0 || nnz <= 0) return B2S_ERR_ARG;
+  if (n_panels < 1 || n_panels > 256 || panel_shift < 1 || panel_shift > 31) return B2S_ERR_ARG;
+  if (((n_cols - 1) >> panel_shift) >= n_panels) return B2S_ERR_ARG;
+  if (p_ptr_type == B2S_I32 && nnz > 0x7fffffffLL) return B2S_ERR_RANGE;
+  if (!data_dev || !indices_dev || !indptr_dev || !p_data_dev || !p_cols_dev || !p_ptr_dev ||
+      !panel_start_dev || !scratch_dev)
+    return B2S_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool wide = b2s::wide_needed(n_cols, nnz);
+  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P,
+      B2S_DISPATCH_I(p_ptr_type, PP, {
+    if (wide)
+      return (b2s::panel_build_run<V, I, P, PP, uint64_t>(
+          data_dev, indices_dev, indptr_dev, n_rows, nnz, n_panels, panel_shift, p_data_dev,
+          p_cols_dev, p_ptr_dev, panel_start_dev, scratch_dev, scratch_bytes, s));
+    return (b2s::panel_build_run<V, I, P, PP, uint32_t>(
+        data_dev, indices_dev, indptr_dev, n_rows, nnz, n_panels, panel_shift, p_data_dev,
+        p_cols_dev, p_ptr_dev, panel_start_dev, scratch_dev, scratch_bytes, s));
+  }))));
+  return B2S_ERR_DTYPE;
+}
 
 extern "C" int64_t b2s_csr2csc_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz) {
   (void)n_rows;

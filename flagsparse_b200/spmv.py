@@ -231,20 +231,32 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
     """Enqueue y = alpha * A x + beta * y_in on the current stream (no synchronisation)."""
     lib = _lib.load()
     items = lib.b2s_spmv_tile_items(plan.vcode, plan.icode)
-    n_tiles, tile_row = plan.tiles(items)
-    carry = plan.scratch("spmv_carry", n_tiles)
     dtype = plan.data.dtype
     a = _lib.scalar_buffer(alpha, dtype)
     b = _lib.scalar_buffer(beta, dtype)
+    lay = plan.panels()
     with torch.cuda.device(plan.device):
-        st = lib.b2s_spmv_csr(
-            plan.vcode, plan.icode, plan.pcode,
-            _lib.ptr(plan.data), _lib.ptr(plan.indices), _lib.ptr(plan.indptr),
-            plan.n_rows, plan.n_cols, plan.nnz,
-            _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b,
-            _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status),
-            _lib.stream_handle(plan.device))
-    _lib.check(st, "b2s_spmv_csr")
+        if lay is None:
+            n_tiles, tile_row = plan.tiles(items)
+            carry = plan.scratch("spmv_carry", n_tiles)
+            st = lib.b2s_spmv_csr(
+                plan.vcode, plan.icode, plan.pcode,
+                _lib.ptr(plan.data), _lib.ptr(plan.indices), _lib.ptr(plan.indptr),
+                plan.n_rows, plan.n_cols, plan.nnz,
+                _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b,
+                _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status),
+                _lib.stream_handle(plan.device))
+        else:
+            n_tiles, tile_row = plan.panel_tiles(items)
+            carry = plan.scratch("spmv_panel_carry", n_tiles)
+            ypart = plan.scratch("spmv_panel_part", lay.n_panels * plan.n_rows)
+            st = lib.b2s_spmv_panels(
+                plan.vcode, lay.pcode, _lib.ptr(lay.data), _lib.ptr(lay.cols), _lib.ptr(lay.ptr),
+                plan.n_rows, plan.n_cols, plan.nnz, lay.n_panels, lay.shift,
+                _lib.ptr(lay.panel_start), _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b,
+                _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(ypart), _lib.ptr(plan.status),
+                _lib.stream_handle(plan.device))
+    _lib.check(st, "b2s_spmv")
     if not plan.status_checked:
         plan.check_status()
 

@@ -100,6 +100,34 @@ int b2s_spmv_csr(int val_type, int idx_type, int ptr_type,
                  const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
                  b2s_stream stream);
 
+/* ---- column-panel layout for SpMV -------------------------------------------------------------
+ * No counterpart in the reference.  When x is larger than the L2 cache, gathers of x miss and
+ * each miss moves a 64-byte DRAM burst for 8 useful bytes.  b2s_panel_build re-lays the matrix
+ * out once as a stack of n_panels CSR matrices over the same rows, panel p holding the entries
+ * with col >> panel_shift == p (stable, so the order inside a row is kept), columns stored
+ * panel-local as int32.  b2s_spmv_panels multiplies the stack (the x slice of the panels in
+ * flight stays L2-resident), leaves one partial per (panel, row) in ypart_dev
+ * (n_panels * n_rows values) and adds them in ascending panel order with the alpha / beta
+ * epilogue.  p_ptr has n_panels * n_rows + 1 entries of p_ptr_type; panel_start_dev has
+ * n_panels + 1 int64 entries; tile_row / carry are sized for the stacked matrix
+ * (b2s_tile_count(n_panels * n_rows, nnz, b2s_spmv_tile_items(...))).
+ */
+int64_t b2s_panel_bytes(int64_t n_cols, int64_t nnz);
+int b2s_panel_build(int val_type, int idx_type, int ptr_type,
+                    const void* data_dev, const void* indices_dev, const void* indptr_dev,
+                    int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                    void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev, int p_ptr_type,
+                    int64_t* panel_start_dev, void* scratch_dev, int64_t scratch_bytes,
+                    b2s_stream stream);
+int b2s_spmv_panels(int val_type, int ptr_type,
+                    const void* p_data_dev, const int32_t* p_cols_dev, const void* p_ptr_dev,
+                    int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                    const int64_t* panel_start_dev,
+                    const void* x_dev, const void* y_in_dev, void* y_dev,
+                    const void* alpha, const void* beta,
+                    const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
+                    int32_t* status_dev, b2s_stream stream);
+
 /* ---- SpMM ----------------------------------------------------------------------------------
  * C = alpha * A B + beta * C_in, B (n_cols x n_dense, leading dimension ldb) and
  * C (n_rows x n_dense, leading dimension ldc) row-major.  Replaces _spmm_csr_real_kernel

@@ -244,3 +244,39 @@ def test_spmv_int64_fallback_policy(monkeypatch):
     prepared.n_rows = mod._INDEX_LIMIT_INT32 + 1
     with pytest.raises(RuntimeError, match="int32 fallback is unsafe"):
         mod._run_spmv_prepared_with_fallback(prepared, x)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64], ids=["i32", "i64"])
+@pytest.mark.parametrize("target_elems", [32, 512, 2048])
+def test_spmv_column_panel_layout_vs_oracle(monkeypatch, dtype, idx_dtype, target_elems):
+    """The column-panel layout (normally used only when x outgrows L2) forced onto a small
+    matrix: 2 .. 200 panels, panels with no entries, tiles that straddle several panels, rows
+    longer than a tile, alpha / beta, bit-identical repeats."""
+    import flagsparse_b200._plan as plan_mod
+    from flagsparse_b200 import clear_plan_cache, flagsparse_spmv_csr
+    monkeypatch.setattr(plan_mod, "PANEL_TRIGGER_BYTES", 0)
+    monkeypatch.setattr(plan_mod, "PANEL_TARGET_BYTES", target_elems * np.dtype(dtype).itemsize)
+    monkeypatch.setattr(plan_mod, "PANEL_MIN_NNZ", 0)
+    clear_plan_cache()
+    rng = np.random.default_rng(target_elems)
+    lengths = np.concatenate([[0, 1, 5000, 0, 33], rng.integers(0, 12, 3000), [2500, 0]])
+    n_rows, n_cols = lengths.size, 6000
+    data, idx, ptr = csr_from_lengths(rng, lengths, n_cols, dtype, sort=False)
+    idx[idx >= 5000] //= 7      # leave the last panels (almost) empty
+    x = random_values(rng, n_cols, dtype)
+    y0 = random_values(rng, n_rows, dtype)
+    alpha, beta = (1.5, 0.5) if np.dtype(dtype).kind != "c" else (1.5 - 0.25j, 0.5 + 2j)
+    expect = oracle.spmv(data, idx, ptr, x, (n_rows, n_cols), alpha=alpha, beta=beta, y0=y0)
+    args = (dev(data), dev(idx, idx_dtype), dev(ptr, idx_dtype), dev(x), (n_rows, n_cols))
+    out = dev(y0)
+    y = flagsparse_spmv_csr(*args, out=out, alpha=alpha, beta=beta)
+    plan = plan_mod.cache_get(plan_mod.plan_key("spmv", args[0], args[1], args[2], args[4]))
+    assert plan is not None and plan.panels() is not None and plan.panels().n_panels >= 2
+    assert_parity(host(y), expect, dtype)
+    out2 = dev(y0)
+    flagsparse_spmv_csr(*args, out=out2, alpha=alpha, beta=beta)
+    assert torch.equal(out.view(torch.uint8), out2.view(torch.uint8))
+    yt = flagsparse_spmv_csr(*args[:3], dev(random_values(rng, n_rows, dtype)), args[4], op="trans")
+    assert yt.shape == (n_cols,)
+    clear_plan_cache()
