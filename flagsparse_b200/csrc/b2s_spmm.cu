@@ -114,34 +114,58 @@ constexpr size_t spmm_smem_bytes() {
 
 // Accumulate A[piece] * B over non-zeros s + first, s + first + step, ... < e of the staged tile.
 // Four gathers of B are in flight per lane before the first multiply.
-template <class V, class I>
+// VEC: every lane that owns columns owns a full, 16-byte aligned pack, so a B row slice is one
+// 128-bit read-only load at Bv + col * stride16 (Bv already points at the lane's columns).
+template <class V, class I, bool VEC>
 __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
                                   const V* __restrict__ sval, int s, int e, int first, int step,
                                   const V* __restrict__ B, int64_t ldb, int64_t e0,
-                                  int64_t n_dense, bool vec_ok) {
+                                  int64_t n_dense, const uint4* __restrict__ Bv,
+                                  int64_t stride16) {
   int i = s + first;
-  for (; i + 3 * step < e; i += 4 * step) {
-    const int64_t c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step],
-                  c3 = scol[i + 3 * step];
-    const Pack<V> b0 = load_pack(B + c0 * ldb, e0, n_dense, vec_ok);
-    const Pack<V> b1 = load_pack(B + c1 * ldb, e0, n_dense, vec_ok);
-    const Pack<V> b2 = load_pack(B + c2 * ldb, e0, n_dense, vec_ok);
-    const Pack<V> b3 = load_pack(B + c3 * ldb, e0, n_dense, vec_ok);
-    fma_pack(acc, sval[i], b0);
-    fma_pack(acc, sval[i + step], b1);
-    fma_pack(acc, sval[i + 2 * step], b2);
-    fma_pack(acc, sval[i + 3 * step], b3);
-  }
-  for (; i < e; i += step) {
-    const int64_t c = scol[i];
-    const Pack<V> b = load_pack(B + c * ldb, e0, n_dense, vec_ok);
-    fma_pack(acc, sval[i], b);
+  if constexpr (VEC) {
+    if (e0 >= n_dense) return;  // lane beyond the last column: nothing to add
+    for (; i + 3 * step < e; i += 4 * step) {
+      const I c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step], c3 = scol[i + 3 * step];
+      Pack<V> b0, b1, b2, b3;
+      *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + static_cast<int64_t>(c0) * stride16);
+      *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + static_cast<int64_t>(c1) * stride16);
+      *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + static_cast<int64_t>(c2) * stride16);
+      *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + static_cast<int64_t>(c3) * stride16);
+      fma_pack(acc, sval[i], b0);
+      fma_pack(acc, sval[i + step], b1);
+      fma_pack(acc, sval[i + 2 * step], b2);
+      fma_pack(acc, sval[i + 3 * step], b3);
+    }
+    for (; i < e; i += step) {
+      Pack<V> b;
+      *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<int64_t>(scol[i]) * stride16);
+      fma_pack(acc, sval[i], b);
+    }
+  } else {
+    for (; i + 3 * step < e; i += 4 * step) {
+      const int64_t c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step],
+                    c3 = scol[i + 3 * step];
+      const Pack<V> b0 = load_pack(B + c0 * ldb, e0, n_dense, false);
+      const Pack<V> b1 = load_pack(B + c1 * ldb, e0, n_dense, false);
+      const Pack<V> b2 = load_pack(B + c2 * ldb, e0, n_dense, false);
+      const Pack<V> b3 = load_pack(B + c3 * ldb, e0, n_dense, false);
+      fma_pack(acc, sval[i], b0);
+      fma_pack(acc, sval[i + step], b1);
+      fma_pack(acc, sval[i + 2 * step], b2);
+      fma_pack(acc, sval[i + 3 * step], b3);
+    }
+    for (; i < e; i += step) {
+      const int64_t c = scol[i];
+      const Pack<V> b = load_pack(B + c * ldb, e0, n_dense, false);
+      fma_pack(acc, sval[i], b);
+    }
   }
 }
 
 // G = lanes per B row (power of two, 1..32); blockIdx.y selects the dense-column tile of
 // G * Pack::N columns when N is wider than one tile.
-template <class V, class I, class P, int THREADS, int ITEMS>
+template <class V, class I, class P, int THREADS, int ITEMS, bool VEC>
 __global__ void __launch_bounds__(THREADS)
 spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
@@ -206,18 +230,21 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int n_seg = n_end + 1;
   const int64_t e0 =
       (static_cast<int64_t>(blockIdx.y) * G + (tid & (G - 1))) * Pack<V>::N;  // lane's columns
-  const bool vb = vec_b != 0, vc = vec_c != 0;
+  const bool vc = VEC || vec_c != 0;
+  (void)vec_b;
+  const uint4* Bv = reinterpret_cast<const uint4*>(B + (VEC && e0 < n_dense ? e0 : 0));
+  const int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(V)) / 16 : 0;
   V* carry_row = carry + t * n_dense;
 
-  // groups per row piece: power of two so that each group sees about four non-zeros
+  // groups per row piece: power of two so that each group sees at most about 16 non-zeros
   const int groups_per_warp = 32 / G;
   int S = 1;
   {
     const int mean = (n_nz + n_seg - 1) / n_seg;
-    while (S * 4 < mean && S < groups_per_warp) S <<= 1;
+    while (S * 16 < mean && S < groups_per_warp) S <<= 1;
   }
   const int team = S * G;  // lanes per row piece
-  const int p1max = (S == groups_per_warp) ? kSpmmWarpRowMax : 16 * S;
+  const int p1max = (S == groups_per_warp) ? kSpmmWarpRowMax : 64 * S;
 
   // ---- strategy 1: one team of S groups per row piece ---------------------------------------
   {
@@ -235,7 +262,7 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
       const int len = e - s;
       Pack<V> acc = pack_zero<V>();
       if (len <= p1max) {
-        accumulate<V, I>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, vb);
+        accumulate<V, I, VEC>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, Bv, stride16);
       } else if ((tid % team) == 0) {
         if (len <= kSpmmWarpRowMax) {
           const int q = atomicAdd(&qcount[0], 1);
@@ -265,7 +292,8 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     const int s = k ? row_end[k - 1] : 0;
     const int e = row_end[k];
     Pack<V> acc = pack_zero<V>();
-    accumulate<V, I>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0, n_dense, vb);
+    accumulate<V, I, VEC>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0, n_dense, Bv,
+                          stride16);
     for (int m = 16; m >= G; m >>= 1) acc = add_pack(acc, shfl_xor_pack(acc, m));
     if (lane < G) {
       if (k < n_end) {
@@ -285,7 +313,7 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     const int s = k ? row_end[k - 1] : 0;
     const int e = row_end[k];
     Pack<V> acc = pack_zero<V>();
-    accumulate<V, I>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, vb);
+    accumulate<V, I, VEC>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, Bv, stride16);
     part[tid] = acc;
     __syncthreads();
     if (tid < G) {
@@ -344,15 +372,22 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   const int vec_b = (reinterpret_cast<uintptr_t>(B) % 16 == 0) && ((ldb * sizeof(V)) % 16 == 0);
   const int vec_c = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * sizeof(V)) % 16 == 0) &&
                     (!has_beta || reinterpret_cast<uintptr_t>(C_in) % 16 == 0);
-  auto kern = spmm_tile_kernel<V, I, P, THREADS, ITEMS>;
   constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
-  ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
   dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(col_tiles));
-  kern<<<grid, THREADS, smem, stream>>>(
-      static_cast<const V*>(data), static_cast<const I*>(indices),
-      static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
-      static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-      n_rows, nnz, a, b, has_beta, G, vec_b, vec_c, status);
+  // fast path: every pack is whole and 16-byte aligned in B, C and C_in
+  const bool vec = vec_b && vec_c && (n_dense % PN == 0);
+  auto launch = [&](auto kern) {
+    ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
+    kern<<<grid, THREADS, smem, stream>>>(
+        static_cast<const V*>(data), static_cast<const I*>(indices),
+        static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
+        static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
+        n_rows, nnz, a, b, has_beta, G, vec_b, vec_c, status);
+  };
+  if (vec)
+    launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true>);
+  else
+    launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, false>);
   if (n_tiles > 1) {
     const int fb = 256;
     const int64_t work = n_tiles * n_dense;
