@@ -369,6 +369,128 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_multi_gpu(args, rank, world, local_rank, device):
+    """Weak scaling over the GPUs of one node: rank r owns the r-th row block, a matrix of the
+    single-GPU workload's size drawn with seed + r; the global matrix is (world * rows) x cols.
+    A step is: broadcast x (or B) from rank 0, multiply the local block, all-gather y (or C)."""
+    import torch.distributed as dist
+
+    from flagsparse_b200.distributed import RowPartitionedCsr
+
+    dist.init_process_group("nccl", device_id=device)
+    peak, peak_kind = measured_peaks()
+    p, kind = make_problem(args.workload, device, args.scale, args.seed + rank)
+    nbytes, flops = problem_bytes_flops(p, kind)
+    if p.extra.get("op", "non") != "non":
+        raise SystemExit("multi-GPU bench covers op=non workloads")
+    part = RowPartitionedCsr(p.data, p.indices, p.indptr, p.shape[1])
+    alpha, beta = p.extra.get("alpha", 1.0), p.extra.get("beta", 0.0)
+    dense = p.x if kind == "spmv" else p.B
+    trailing = () if kind == "spmv" else (int(p.B.shape[1]),)
+    out_local = (p.extra["y0"].clone() if beta != 0.0 else
+                 torch.empty((part.n_local, *trailing), dtype=p.data.dtype, device=device))
+    out_full = torch.empty((part.n_rows, *trailing), dtype=p.data.dtype, device=device)
+    local = part.spmv_local if kind == "spmv" else part.spmm_local
+
+    def bcast():
+        part.broadcast_dense(dense, 0)
+
+    def kernel():
+        local(dense, out=out_local, alpha=alpha, beta=beta)
+
+    def gather():
+        part.gather_rows(out_local, out=out_full)
+
+    def step():
+        bcast()
+        kernel()
+        gather()
+
+    def timed(fn, steps, warmup, sampler=None):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with (sampler if sampler is not None else _Null()):
+            start.record()
+            for _ in range(steps):
+                fn()
+            stop.record()
+            torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([start.elapsed_time(stop) / 1000.0], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    step()  # plans, NCCL communicators
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    seconds = timed(step, args.steps, args.warmup, sampler)
+    per_step = seconds / args.steps
+    phase_steps = max(3, args.steps // 3)
+    phases = {name: timed(fn, phase_steps, 2) / phase_steps * 1e3
+              for name, fn in (("broadcast_ms", bcast), ("kernel_ms", kernel),
+                               ("allgather_ms", gather))}
+    tot = torch.tensor([float(nbytes), float(flops), float(p.nnz)], dtype=torch.float64,
+                       device=device)
+    dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    job_bytes, job_flops, job_nnz = (float(v) for v in tot.tolist())
+
+    # end to end: x from pinned host memory on rank 0, y0 blocks from host, full y back to host
+    dense_host = dense.cpu().pin_memory() if rank == 0 else None
+    y0_host = p.extra["y0"].cpu().pin_memory() if beta != 0.0 else None
+    full_host = torch.empty(out_full.shape, dtype=out_full.dtype).pin_memory()
+
+    def e2e_step():
+        if rank == 0:
+            dense.copy_(dense_host, non_blocking=True)
+        if y0_host is not None:
+            out_local.copy_(y0_host, non_blocking=True)
+        step()
+        full_host.copy_(out_full, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_s = timed(e2e_step, e2e_steps, 2) / e2e_steps
+    h2d = (dense.numel() * dense.element_size()
+           + world * (out_local.numel() * out_local.element_size() if y0_host is not None else 0))
+    d2h = world * out_full.numel() * out_full.element_size()
+
+    if rank == 0:
+        gbs = job_bytes / per_step / 1e9
+        kernel_gbs = job_bytes / (phases["kernel_ms"] / 1e3) / 1e9
+        line = {
+            "metric": "effective HBM GB/s (algorithmic bytes / time)",
+            "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype],
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD_TEXT[args.workload] + f"; one such row block per GPU "
+                       f"({world} blocks, global matrix {part.n_rows} x {p.shape[1]})",
+                       "rows": part.n_rows, "nnz": int(job_nnz),
+                       "l2": "inputs_exceed_l2" if nbytes > 2 * 126e6 else "l2_resident_inputs",
+                       "seed": args.seed, "scale": args.scale,
+                       "exchange": "NCCL broadcast of x/B from rank 0 + NCCL all-gather of y/C, "
+                                   "both inside the timed step"},
+            "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
+                         "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
+                         "peak_kind": peak_kind,
+                         "note": "per-GPU rate of the local kernel phase alone"},
+            "e2e": {"value": job_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": world * args.steps * (2 + (1 if uses_panels(p, kind) else 0)),
+            "clocks": sampler.summary(),
+            "extra": {"gflops": job_flops / per_step / 1e9,
+                      "pct_of_8tbs_nominal_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS,
+                      "phases": phases, "kernel_phase_gbs_all_gpus": kernel_gbs,
+                      "algorithmic_bytes_per_step": job_bytes},
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -398,8 +520,7 @@ def main():
     device = torch.device("cuda", local_rank)
 
     if world > 1:
-        from flagsparse_b200 import distributed as D
-        D.bench_multi_gpu(args, rank, world, local_rank, WORKLOAD_TEXT, DTYPE_TEXT)
+        run_multi_gpu(args, rank, world, local_rank, device)
         return
 
     peak, peak_kind = measured_peaks()

@@ -96,11 +96,16 @@ class RowPartitionedCsr:
         """All-gather the row blocks (unequal heights are padded to the tallest block for the
         collective and cut back afterwards).  Returns the full y / C on every rank."""
         trailing = tuple(local.shape[1:])
+        if out is None:
+            out = torch.empty((self.n_rows, *trailing), dtype=local.dtype, device=local.device)
+        if all(r == self.max_rows for r in self.rows_per_rank) and local.is_contiguous() \
+                and out.is_contiguous():
+            # equal blocks: gather straight into the result, no padding or repacking
+            dist.all_gather_into_tensor(out, local, group=self.group)
+            return out
         mine, everyone = self._padded(trailing, local.dtype, local.device)
         mine[: self.n_local].copy_(local)
         dist.all_gather_into_tensor(everyone, mine, group=self.group)
-        if out is None:
-            out = torch.empty((self.n_rows, *trailing), dtype=local.dtype, device=local.device)
         off = 0
         for p, rows in enumerate(self.rows_per_rank):
             out[off:off + rows].copy_(everyone[p * self.max_rows: p * self.max_rows + rows])
