@@ -41,6 +41,10 @@ SIGNATURES = {
     "b2s_spmv_csr": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                              c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p]),
+    "b2s_spmv_csr_fixed_max_items": (c_int64, []),
+    "b2s_spmv_csr_fixed": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                   c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p]),
     "b2s_panel_bytes": (c_int64, [c_int64, c_int64]),
     "b2s_panel_build": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,

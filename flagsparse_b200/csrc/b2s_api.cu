@@ -161,6 +161,7 @@ extern "C" const char* b2s_status_string(int status) {
     case B2S_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case B2S_ERR_WORKSPACE: return "scratch buffer too small";
     case B2S_ERR_RANGE: return "size does not fit the index dtype";
+    case B2S_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of b2s_spmv_csr_fixed";
   }
   return "unknown status";
 }

@@ -12,6 +12,8 @@
 //                       borders leaves one partial sum per tile in `carry`, and a second kernel
 //                       adds those partials to the row in ascending tile order.
 // No floating-point atomics: every sum has a fixed shape, so results repeat bit for bit.
+#include <mutex>
+
 #include "b2s_tile.cuh"
 
 namespace b2s {
@@ -514,4 +516,67 @@ extern "C" int b2s_spmv_csr(int val_type, int idx_type, int ptr_type, const void
                                       status_dev, s));
   })));
   return B2S_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SpMV without any allocation: tile plan and carries live in a fixed device array
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int64_t kFixedMaxTiles = 1 << 16;  // 65,536 tiles = 67,108,864 rows + non-zeros
+
+struct FixedScratch {
+  int64_t tile_row[kFixedMaxTiles + 1];
+  alignas(16) unsigned char carry[kFixedMaxTiles * 16];  // one value of the widest dtype per tile
+};
+
+// About 1.5 MB of device memory on every GPU that loads the library, held until exit.
+static __device__ __align__(256) unsigned char g_fixed_scratch[sizeof(FixedScratch)];
+
+// In host code the name g_fixed_scratch is only a stand-in for the device array, not its
+// address; the address is looked up once per device and kept here.
+FixedScratch* g_fixed_ptr[64] = {};
+std::mutex g_fixed_mu;
+
+int fixed_scratch_for_current_device(FixedScratch** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2S_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_fixed_mu);
+  if (g_fixed_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_fixed_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return B2S_ERR_LAUNCH;
+    }
+    g_fixed_ptr[dev] = static_cast<FixedScratch*>(p);
+  }
+  *out = g_fixed_ptr[dev];
+  return B2S_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t b2s_spmv_csr_fixed_max_items(void) {
+  return kFixedMaxTiles * static_cast<int64_t>(b2s::SpmvCfg<float, int32_t>::ITEMS);
+}
+
+extern "C" int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                                  const void* indices_dev, const void* indptr_dev,
+                                  int64_t n_rows, int64_t n_cols, int64_t nnz, const void* x_dev,
+                                  const void* y_in_dev, void* y_dev, const void* alpha,
+                                  const void* beta, b2s_stream stream) {
+  if (n_rows < 0 || n_cols < 0 || nnz < 0) return B2S_ERR_ARG;
+  const int items = b2s_spmv_tile_items(val_type, idx_type);
+  if (b2s_tile_count(n_rows, nnz, items) > kFixedMaxTiles) return B2S_ERR_TOO_LARGE;
+  if (n_rows == 0) return B2S_OK;
+  FixedScratch* fs = nullptr;
+  int st = fixed_scratch_for_current_device(&fs);
+  if (st != B2S_OK) return st;
+  // Nothing in the array has to start at zero: the plan is rewritten in full here, and every
+  // carry the fix-up reads was written by the tile kernel of this same call.
+  st = b2s_tile_plan(indptr_dev, ptr_type, n_rows, nnz, items, fs->tile_row, stream);
+  if (st != B2S_OK) return st;
+  return b2s_spmv_csr(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
+                      n_cols, nnz, x_dev, y_in_dev, y_dev, alpha, beta, fs->tile_row, fs->carry,
+                      nullptr, stream);
 }

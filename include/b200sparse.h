@@ -34,7 +34,8 @@ typedef enum {
   B2S_ERR_LAUNCH = 4,     /* cudaGetLastError() reported a launch failure         */
   B2S_ERR_TIMEOUT = 5,    /* (device status word) a bounded wait in a kernel ran out */
   B2S_ERR_WORKSPACE = 6,  /* scratch buffer smaller than *_bytes() asked for      */
-  B2S_ERR_RANGE = 7       /* a size does not fit the requested index dtype        */
+  B2S_ERR_RANGE = 7,      /* a size does not fit the requested index dtype        */
+  B2S_ERR_TOO_LARGE = 8   /* problem exceeds the fixed scratch of b2s_spmv_csr_fixed */
 } b2s_status;
 
 /* value dtypes (order follows FlagSparse's SUPPORTED_VALUE_DTYPES, _common.py:21-29) */
@@ -99,6 +100,31 @@ int b2s_spmv_csr(int val_type, int idx_type, int ptr_type,
                  const void* alpha, const void* beta,
                  const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
                  b2s_stream stream);
+
+/* ---- SpMV for callers that may not allocate ----------------------------------------------------
+ * No counterpart in the reference.  b2s_spmv_csr needs a tile plan and a carry buffer that the
+ * caller allocates.  Some callers cannot: a service that handed all device memory to its own
+ * arena at start-up, a solver loop under a no-allocation-after-initialisation rule, a plug-in
+ * whose host owns the allocator.  b2s_spmv_csr_fixed computes the same y = alpha * A x +
+ * beta * y_in with the same kernels and takes both scratch areas from one fixed array inside the
+ * library (about 1.5 MB per GPU, held from library load to process exit).  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine.
+ *   - Limit: n_rows + nnz <= b2s_spmv_csr_fixed_max_items() (67,108,864); larger problems return
+ *     B2S_ERR_TOO_LARGE and launch nothing.
+ *   - The tile plan is rebuilt on every call (one extra small kernel), so the call costs a few
+ *     microseconds more than b2s_spmv_csr with a cached plan.
+ *   - The first call on each device looks up the array's device address (current device must be
+ *     the one the pointers live on); make that first call before any stream capture begins.
+ *   - All calls on a device share the array, which keeps the last call's contents.  Nothing in
+ *     it needs clearing between calls, but two calls whose kernels overlap on the GPU (different
+ *     streams, no ordering) race on it: order them.
+ */
+int64_t b2s_spmv_csr_fixed_max_items(void);
+int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type,
+                       const void* data_dev, const void* indices_dev, const void* indptr_dev,
+                       int64_t n_rows, int64_t n_cols, int64_t nnz,
+                       const void* x_dev, const void* y_in_dev, void* y_dev,
+                       const void* alpha, const void* beta, b2s_stream stream);
 
 /* ---- column-panel layout for SpMV -------------------------------------------------------------
  * No counterpart in the reference.  When x is larger than the L2 cache, gathers of x miss and
