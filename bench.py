@@ -39,6 +39,10 @@ if str(ROOT) not in sys.path:
 
 NOMINAL_HBM_GBS = 8000.0
 
+# DRAM bytes (read + written) of one step from ncu (dram__bytes_read.sum + dram__bytes_write.sum
+# over the kernels of a step; profiles/spmv_cfg2_step_launches_dram.md), keyed by (workload, scale)
+NCU_TRAFFIC_BYTES = {("cfg2", 1): 5.02e9}
+
 
 def measured_peaks():
     f = ROOT / "MEASURED_PEAKS.json"
@@ -573,7 +577,9 @@ def main():
                    "l2": "inputs_exceed_l2" if nbytes > 2 * 126e6 else "l2_resident_inputs",
                    "seed": args.seed, "scale": args.scale},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
-                     "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind},
+                     "frac": gbs / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale)),
+                     "peak_kind": peak_kind},
         "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
         "gpu_launches": (launches_per_step + (1 if uses_panels(p, kind) else 0)) * args.steps,
