@@ -11,10 +11,20 @@
 
 namespace b2s {
 
+#ifndef B2S_SPMM_CHUNKED
+#define B2S_SPMM_CHUNKED 2  // 0: team-per-row kernel; 1: chunk kernel; 2: chunk kernel for narrow B rows
+#endif
+#ifndef B2S_SPMM_THREADS
+#define B2S_SPMM_THREADS 256
+#endif
+#ifndef B2S_SPMM_ITEMS
+#define B2S_SPMM_ITEMS 1024
+#endif
+
 template <class V, class I>
 struct SpmmCfg {
-  static constexpr int THREADS = 256;
-  static constexpr int ITEMS = 1024;
+  static constexpr int THREADS = B2S_SPMM_THREADS;
+  static constexpr int ITEMS = B2S_SPMM_ITEMS;
 };
 
 constexpr int kSpmmWarpRowMax = 512;
@@ -125,6 +135,32 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
   int i = s + first;
   if constexpr (VEC) {
     if (e0 >= n_dense) return;  // lane beyond the last column: nothing to add
+    if (stride16 < 0) {
+      // all of B lies within 2^32 sixteen-byte units: 32-bit row offsets (one multiply, one
+      // widening add per gather instead of a 64-bit multiply)
+      const uint32_t s32 = static_cast<uint32_t>(-stride16);
+      for (; i + 3 * step < e; i += 4 * step) {
+        const uint32_t o0 = static_cast<uint32_t>(scol[i]) * s32;
+        const uint32_t o1 = static_cast<uint32_t>(scol[i + step]) * s32;
+        const uint32_t o2 = static_cast<uint32_t>(scol[i + 2 * step]) * s32;
+        const uint32_t o3 = static_cast<uint32_t>(scol[i + 3 * step]) * s32;
+        Pack<V> b0, b1, b2, b3;
+        *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + o0);
+        *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + o1);
+        *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + o2);
+        *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + o3);
+        fma_pack(acc, sval[i], b0);
+        fma_pack(acc, sval[i + step], b1);
+        fma_pack(acc, sval[i + 2 * step], b2);
+        fma_pack(acc, sval[i + 3 * step], b3);
+      }
+      for (; i < e; i += step) {
+        Pack<V> b;
+        *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<uint32_t>(scol[i]) * s32);
+        fma_pack(acc, sval[i], b);
+      }
+      return;
+    }
     for (; i + 3 * step < e; i += 4 * step) {
       const I c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step], c3 = scol[i + 3 * step];
       Pack<V> b0, b1, b2, b3;
@@ -170,7 +206,7 @@ __global__ void __launch_bounds__(THREADS)
 spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
                  int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,
-                 int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int vec_b,
+                 int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int small_b,
                  int vec_c, int32_t* status) {
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
@@ -231,9 +267,9 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int64_t e0 =
       (static_cast<int64_t>(blockIdx.y) * G + (tid & (G - 1))) * Pack<V>::N;  // lane's columns
   const bool vc = VEC || vec_c != 0;
-  (void)vec_b;
   const uint4* Bv = reinterpret_cast<const uint4*>(B + (VEC && e0 < n_dense ? e0 : 0));
-  const int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(V)) / 16 : 0;
+  int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(V)) / 16 : 0;
+  if (VEC && small_b) stride16 = -stride16;  // flag for 32-bit row offsets (see accumulate)
   V* carry_row = carry + t * n_dense;
 
   // groups per row piece: power of two so that each group sees at most about 16 non-zeros
@@ -330,6 +366,203 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Chunked SpMM tile kernel.  The staged non-zeros of a tile are cut into chunks of CH consecutive
+// entries; a team of G lanes takes a chunk, issues the B-row gathers of the chunk in batches of 8
+// (every lane has up to 8 independent 16-byte loads in flight whatever the row lengths are), and
+// walks the chunk in order, flushing a row whenever its end is passed.  A row that lies inside
+// one chunk is stored at once.  The first row that ends in a chunk may have begun in earlier
+// chunks: its partial goes to shared memory (`first`), as does the partial of the row still
+// open at the chunk's end (`carry`); a second pass adds, for every such first row, the carries
+// of the preceding chunks in ascending order.  Work per team is uniform (CH entries), sums have
+// a fixed order, nothing is atomic.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSpmmMaxChunks = 256;
+static_assert(B2S_SPMM_ITEMS <= 4 * kSpmmMaxChunks, "the shortest chunk has 4 entries");
+
+template <int ITEMS, class V, class I>
+constexpr size_t spmm_chunk_smem_base() {
+  return 16 + sizeof(int) * (ITEMS + 4) + sizeof(I) * ITEMS + 16 + sizeof(V) * ITEMS + 16 +
+         sizeof(int) * 2 * kSpmmMaxChunks;
+}
+
+template <class V, class I, class P, int THREADS, int ITEMS, bool VEC>
+__global__ void __launch_bounds__(THREADS)
+spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
+                  const P* __restrict__ ptr, const V* __restrict__ B, int64_t ldb,
+                  int64_t n_dense, const V* C_in, V* C, int64_t ldc, V* __restrict__ carry,
+                  const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t nnz, V alpha,
+                  V beta, int has_beta_i, int G, int CH, int vec_c, int32_t* status) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
+  int* row_end = reinterpret_cast<int*>(smem + 16);
+  unsigned char* col_buf = smem + 16 + sizeof(int) * (ITEMS + 4);
+  unsigned char* val_buf = col_buf + sizeof(I) * ITEMS + 16;
+  int* first_k = reinterpret_cast<int*>(val_buf + sizeof(V) * ITEMS + 16);
+  int* open_k = first_k + kSpmmMaxChunks;
+  Pack<V>* slots = reinterpret_cast<Pack<V>*>(open_k + kSpmmMaxChunks);  // [chunk][2][G]
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+  const bool has_beta = has_beta_i != 0;
+  const int64_t t = blockIdx.x;
+  const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
+  const int n_nz = static_cast<int>(tc.j1 - tc.j0);
+  const int n_end = static_cast<int>(tc.r1 - tc.r0);
+
+  const I* gcol = col + tc.j0;
+  const V* gval = val + tc.j0;
+  const Staged<I> sc = stage_layout<I>(col_buf, gcol, n_nz);
+  const Staged<V> sv = stage_layout<V>(val_buf, gval, n_nz);
+  const uint32_t tx = stage_bytes(sc) + stage_bytes(sv);
+  if (tid == 0 && tx) mbar_init(bar, 1);
+  __syncthreads();
+  if (tid == 0 && tx) {
+    const uint64_t pol = policy_evict_first();
+    mbar_expect_tx(bar, tx);
+    stage_issue(sc, gcol, bar, pol);
+    stage_issue(sv, gval, bar, pol);
+  }
+  stage_edges(sc, gcol, n_nz, tid, THREADS);
+  stage_edges(sv, gval, n_nz, tid, THREADS);
+  for (int k = tid; k < n_end; k += THREADS)
+    row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
+  if (tid == 0) row_end[n_end] = n_nz;
+  if (tx && warp == 0) {
+    if (!mbar_wait(bar, 0)) {
+      if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
+      mbar_wait(bar, 0);
+    }
+  }
+  __syncthreads();
+
+  const I* scol = sc.s;
+  const V* sval = sv.s;
+  const bool open_row = tc.r1 < n_rows;
+  const int sub = tid & (G - 1);
+  const int team = tid / G;
+  const int n_teams = THREADS / G;
+  const int64_t e0 = (static_cast<int64_t>(blockIdx.y) * G + sub) * Pack<V>::N;  // lane's columns
+  const bool lane_on = e0 < n_dense;
+  const bool vc = VEC || vec_c != 0;
+  const uint4* Bv = reinterpret_cast<const uint4*>(B + (VEC && lane_on ? e0 : 0));
+  const int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(V)) / 16 : 0;
+  V* carry_row = carry + t * n_dense;
+  const int n_chunks = n_nz > 0 ? (n_nz + CH - 1) / CH : 1;
+
+  auto load_b = [&](I c) -> Pack<V> {
+    Pack<V> b;
+    if constexpr (VEC) {
+      if (lane_on)
+        *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<int64_t>(c) * stride16);
+      else
+        b = pack_zero<V>();
+    } else {
+      b = load_pack(B + static_cast<int64_t>(c) * ldb, e0, n_dense, false);
+    }
+    return b;
+  };
+  auto store_row = [&](int k, const Pack<V>& acc) {
+    const int64_t r = tc.r0 + k;
+    store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc);
+  };
+
+  // rows without entries in this tile: alpha * 0 + beta * C_in, all teams in parallel
+  for (int k = team; k < n_end; k += n_teams) {
+    const int s = k ? row_end[k - 1] : 0;
+    if (row_end[k] == s) store_row(k, pack_zero<V>());
+  }
+
+  // ---- pass 1: one team per chunk ---------------------------------------------------------------
+  for (int c = team; c < n_chunks; c += n_teams) {
+    const int i0 = c * CH;
+    const int i1 = min(i0 + CH, n_nz);
+    int k = 0;
+    if (c > 0) {  // first piece whose end lies beyond i0
+      int lo = 0, hi = n_end;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (row_end[mid] <= i0) lo = mid + 1; else hi = mid;
+      }
+      k = lo;
+    }
+    int start = k ? row_end[k - 1] : 0;
+    int next_end = k < n_end ? row_end[k] : 0x7fffffff;
+    int fk = -1;
+    Pack<V> acc = pack_zero<V>();
+    Pack<V>* my_first = slots + (static_cast<size_t>(c) * 2 + 0) * G + sub;
+    Pack<V>* my_carry = slots + (static_cast<size_t>(c) * 2 + 1) * G + sub;
+
+    auto pass_ends = [&](int upto) {  // flush every piece that ends at or before `upto`
+      while (next_end <= upto) {
+        if (next_end > start) {  // pieces without entries were written above
+          if (fk < 0) {
+            fk = k;
+            *my_first = acc;
+          } else {
+            store_row(k, acc);
+          }
+          acc = pack_zero<V>();
+        }
+        start = next_end;
+        ++k;
+        next_end = k < n_end ? row_end[k] : 0x7fffffff;
+      }
+    };
+
+    for (int b0 = i0; b0 < i1; b0 += 8) {
+      Pack<V> bb[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (b0 + u < i1) bb[u] = load_b(scol[b0 + u]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = b0 + u;
+        if (i < i1) {
+          pass_ends(i);
+          fma_pack(acc, sval[i], bb[u]);
+        }
+      }
+    }
+    pass_ends(i1);
+    *my_carry = acc;  // partial of the piece still open at the end of the chunk
+    if (sub == 0) {
+      first_k[c] = fk;
+      open_k[c] = k;
+    }
+  }
+  __syncthreads();
+
+  // ---- pass 2: complete the first row of every chunk with the carries before it ----------------
+  for (int c = team; c < n_chunks; c += n_teams) {
+    const int fk = first_k[c];
+    if (fk < 0) continue;
+    int c_lo = c;
+    while (c_lo > 0 && open_k[c_lo - 1] == fk) --c_lo;
+    Pack<V> tot = slots[(static_cast<size_t>(c) * 2 + 0) * G + sub];
+    if (c_lo < c) {
+      Pack<V> run = slots[(static_cast<size_t>(c_lo) * 2 + 1) * G + sub];
+      for (int cc = c_lo + 1; cc < c; ++cc)
+        run = add_pack(run, slots[(static_cast<size_t>(cc) * 2 + 1) * G + sub]);
+      tot = add_pack(run, tot);
+    }
+    store_row(fk, tot);
+  }
+  if (team == 0 && open_row) {  // what this tile contributes to the row that continues after it
+    int c_lo = n_chunks;
+    while (c_lo > 0 && open_k[c_lo - 1] == n_end) --c_lo;
+    Pack<V> run = pack_zero<V>();
+    if (c_lo < n_chunks) {
+      run = slots[(static_cast<size_t>(c_lo) * 2 + 1) * G + sub];
+      for (int cc = c_lo + 1; cc < n_chunks; ++cc)
+        run = add_pack(run, slots[(static_cast<size_t>(cc) * 2 + 1) * G + sub]);
+    }
+    store_raw(carry_row, e0, n_dense, run);
+  }
+}
+
 template <class V>
 __global__ void spmm_fixup_kernel(V* C, int64_t ldc, int64_t n_dense,
                                   const V* __restrict__ carry,
@@ -350,7 +583,7 @@ __global__ void spmm_fixup_kernel(V* C, int64_t ldc, int64_t n_dense,
 
 template <class V, class I, class P>
 int spmm_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
-                int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
+                int64_t n_cols, int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
                 void* C, int64_t ldc, const void* alpha, const void* beta,
                 const int64_t* tile_row, void* carry, int32_t* status, cudaStream_t stream) {
   using Cfg = SpmmCfg<V, I>;
@@ -372,22 +605,50 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   const int vec_b = (reinterpret_cast<uintptr_t>(B) % 16 == 0) && ((ldb * sizeof(V)) % 16 == 0);
   const int vec_c = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * sizeof(V)) % 16 == 0) &&
                     (!has_beta || reinterpret_cast<uintptr_t>(C_in) % 16 == 0);
-  constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
   dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(col_tiles));
   // fast path: every pack is whole and 16-byte aligned in B, C and C_in
   const bool vec = vec_b && vec_c && (n_dense % PN == 0);
-  auto launch = [&](auto kern) {
-    ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
-    kern<<<grid, THREADS, smem, stream>>>(
-        static_cast<const V*>(data), static_cast<const I*>(indices),
-        static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
-        static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-        n_rows, nnz, a, b, has_beta, G, vec_b, vec_c, status);
-  };
-  if (vec)
-    launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true>);
-  else
-    launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, false>);
+  // B spans fewer than 2^32 sixteen-byte units (64 GB): row offsets fit 32 bits
+  const int small_b = (static_cast<double>(n_cols) * static_cast<double>(ldb) * sizeof(V) / 16.0) < 4.0e9;
+  // Two tile kernels.  Narrow rows of B (G <= 4 lanes, e.g. N = 16 float32): the chunk kernel,
+  // where every team has 8 gathers in flight whatever the row lengths (measured on the 2^26-row
+  // power-law matrix, N = 16: 30 ms against 40 ms).  Wider rows: the team-per-row kernel, whose
+  // smaller footprint keeps more CTAs resident (N = 32 float64 on the 2^24-row matrix: 18.5 ms
+  // against 35 ms; banded N = 32 float32: 1.4 ms against 3.1 ms).
+  const bool chunked = B2S_SPMM_CHUNKED == 1 || (B2S_SPMM_CHUNKED == 2 && G <= 4);
+  if (chunked) {
+    const int CH = G >= 4 ? 16 : 4 * G;  // shorter chunks for very narrow rows: all teams busy
+    const size_t smem = spmm_chunk_smem_base<ITEMS, V, I>() +
+                        static_cast<size_t>(ITEMS / CH) * 2 * G * sizeof(Pack<V>);
+    constexpr size_t smem_max = spmm_chunk_smem_base<ITEMS, V, I>() +
+                                static_cast<size_t>(ITEMS / 16) * 2 * 32 * sizeof(Pack<V>);
+    auto launch = [&](auto kern) {
+      ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem_max);
+      kern<<<grid, THREADS, smem, stream>>>(
+          static_cast<const V*>(data), static_cast<const I*>(indices),
+          static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
+          static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
+          n_rows, nnz, a, b, has_beta, G, CH, vec_c, status);
+    };
+    if (vec)
+      launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, true>);
+    else
+      launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, false>);
+  } else {
+    constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
+    auto launch = [&](auto kern) {
+      ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
+      kern<<<grid, THREADS, smem, stream>>>(
+          static_cast<const V*>(data), static_cast<const I*>(indices),
+          static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
+          static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
+          n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status);
+    };
+    if (vec)
+      launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true>);
+    else
+      launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, false>);
+  }
   if (n_tiles > 1) {
     const int fb = 256;
     const int64_t work = n_tiles * n_dense;
@@ -425,7 +686,7 @@ extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void
     return B2S_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
-    return (b2s::spmm_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, nnz, B_dev, ldb,
+    return (b2s::spmm_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, B_dev, ldb,
                                       n_dense, C_in_dev, C_dev, ldc, alpha, beta, tile_row_dev,
                                       carry_dev, status_dev, s));
   })));
