@@ -405,10 +405,16 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     def gather():
         part.gather_rows(out_local, out=out_full)
 
+    staged = part.split_stages(args.stages)
+    op = part.spmv if kind == "spmv" else part.spmm
+
     def step():
-        bcast()
-        kernel()
-        gather()
+        if staged:  # kernel of stage s+1 overlaps the all-gather of stage s
+            op(dense, src=0, out_local=out_local, out=out_full, alpha=alpha, beta=beta)
+        else:
+            bcast()
+            kernel()
+            gather()
 
     def timed(fn, steps, warmup, sampler=None):
         for _ in range(warmup):
@@ -442,10 +448,12 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     dist.all_reduce(tot, op=dist.ReduceOp.SUM)
     job_bytes, job_flops, job_nnz = (float(v) for v in tot.tolist())
 
-    # end to end: x from pinned host memory on rank 0, y0 blocks from host, full y back to host
+    # end to end: x from pinned host memory on rank 0, every rank's y0 block from its host
+    # buffer, the assembled y copied back to the host on rank 0 (where x came from)
     dense_host = dense.cpu().pin_memory() if rank == 0 else None
     y0_host = p.extra["y0"].cpu().pin_memory() if beta != 0.0 else None
-    full_host = torch.empty(out_full.shape, dtype=out_full.dtype).pin_memory()
+    full_host = torch.empty(out_full.shape, dtype=out_full.dtype).pin_memory() if rank == 0 \
+        else None
 
     def e2e_step():
         if rank == 0:
@@ -453,13 +461,14 @@ def run_multi_gpu(args, rank, world, local_rank, device):
         if y0_host is not None:
             out_local.copy_(y0_host, non_blocking=True)
         step()
-        full_host.copy_(out_full, non_blocking=True)
+        if rank == 0:
+            full_host.copy_(out_full, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
     e2e_s = timed(e2e_step, e2e_steps, 2) / e2e_steps
     h2d = (dense.numel() * dense.element_size()
            + world * (out_local.numel() * out_local.element_size() if y0_host is not None else 0))
-    d2h = world * out_full.numel() * out_full.element_size()
+    d2h = out_full.numel() * out_full.element_size()
 
     if rank == 0:
         gbs = job_bytes / per_step / 1e9
@@ -476,7 +485,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                        "l2": "inputs_exceed_l2" if nbytes > 2 * 126e6 else "l2_resident_inputs",
                        "seed": args.seed, "scale": args.scale,
                        "exchange": "NCCL broadcast of x/B from rank 0 + NCCL all-gather of y/C, "
-                                   "both inside the timed step"},
+                                   "both inside the timed step",
+                       "stages": args.stages if staged else 1},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
                          "peak_kind": peak_kind,
@@ -504,6 +514,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOAD_TEXT))
     ap.add_argument("--scale", type=int, default=1, help="divide the row count (debugging)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--stages", type=int, default=4,
+                    help="N > 1: row sub-blocks per rank; the all-gather of one overlaps the "
+                         "kernel of the next (1 = no overlap)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the SpMM N=32 side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")

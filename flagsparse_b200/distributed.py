@@ -67,6 +67,7 @@ class RowPartitionedCsr:
         self.n_rows = sum(self.rows_per_rank)
         self.row_offset = sum(self.rows_per_rank[: self.rank])
         self._pads = {}
+        self._stages = None
 
     @classmethod
     def from_global(cls, data, indices, indptr, shape, group=None, **kw):
@@ -112,6 +113,47 @@ class RowPartitionedCsr:
             off += rows
         return out
 
+    # -- pipelined variant: several row blocks per rank ------------------------------------------
+    def split_stages(self, stages):
+        """Cut this rank's block into `stages` consecutive sub-blocks of equal height so that
+        the all-gather of one sub-block can run while the next one is multiplied.  The global
+        row order becomes block-cyclic: sub-block s of rank p holds global rows
+        [(s*world + p)*h, (s*world + p + 1)*h), h = n_local / stages -- i.e. the all-gather of
+        stage s fills one contiguous slice of y / C and no repacking is needed.  Needs equal
+        n_local on all ranks and n_local divisible by stages; otherwise returns False and the
+        single-stage path stays in use."""
+        stages = int(stages)
+        if stages <= 1 or self.n_local % stages or len(set(self.rows_per_rank)) != 1:
+            self._stages = None
+            return False
+        h = self.n_local // stages
+        self._stages = []
+        for s in range(stages):
+            d, i, p = slice_rows(self.data, self.indices, self.indptr, s * h, (s + 1) * h)
+            self._stages.append((d.contiguous(), i.contiguous(), p.contiguous()))
+        self._stage_rows = h
+        return True
+
+    def _pipelined(self, local_op, dense, out_local, out, alpha, beta):
+        h, W = self._stage_rows, self.world
+        trailing = tuple(dense.shape[1:])
+        if out is None:
+            out = torch.empty((self.n_rows, *trailing), dtype=dense.dtype, device=dense.device)
+        if out_local is None:
+            out_local = torch.empty((self.n_local, *trailing), dtype=dense.dtype,
+                                    device=dense.device)
+        works = []
+        for s, (d, i, p) in enumerate(self._stages):
+            blk = out_local[s * h:(s + 1) * h]
+            local_op(d, i, p, dense, (h, self.n_cols), out=blk, alpha=alpha, beta=beta)
+            # asynchronous: the collective waits for the kernels enqueued so far and runs on
+            # NCCL's stream while the next stage is being multiplied
+            works.append(dist.all_gather_into_tensor(out[s * W * h:(s + 1) * W * h], blk,
+                                                     group=self.group, async_op=True))
+        for w in works:
+            w.wait()
+        return out
+
     # -- products ------------------------------------------------------------------------------
     def spmv_local(self, x, out=None, alpha=1.0, beta=0.0):
         return self.local_spmv(self.data, self.indices, self.indptr, x,
@@ -125,10 +167,14 @@ class RowPartitionedCsr:
         """y = alpha * A x + beta * y0 with x taken from rank `src`; y0 is this rank's block in
         out_local.  Returns the assembled y on every rank."""
         self.broadcast_dense(x, src)
+        if getattr(self, "_stages", None):
+            return self._pipelined(self.local_spmv, x, out_local, out, alpha, beta)
         y_local = self.spmv_local(x, out=out_local, alpha=alpha, beta=beta)
         return self.gather_rows(y_local, out=out)
 
     def spmm(self, B, src=0, out_local=None, out=None, alpha=1.0, beta=0.0):
         self.broadcast_dense(B, src)
+        if getattr(self, "_stages", None):
+            return self._pipelined(self.local_spmm, B, out_local, out, alpha, beta)
         C_local = self.spmm_local(B, out=out_local, alpha=alpha, beta=beta)
         return self.gather_rows(C_local, out=out)

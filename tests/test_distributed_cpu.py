@@ -85,6 +85,53 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
+def _staged_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from flagsparse_b200.distributed import RowPartitionedCsr
+        stages, h, n_cols = 3, 20, 64
+        # every rank owns `stages` blocks of h rows; block (s, p) holds global rows
+        # [(s*world + p)*h, ...): build all blocks, keep those of this rank
+        rng = np.random.default_rng(11)
+        blocks = {}
+        for s in range(stages):
+            for p in range(world):
+                lengths = rng.integers(0, 7, h)
+                ptr = np.zeros(h + 1, dtype=np.int64)
+                np.cumsum(lengths, out=ptr[1:])
+                blocks[(s, p)] = (rng.standard_normal(int(ptr[-1])),
+                                  rng.integers(0, n_cols, int(ptr[-1])), ptr)
+        mine = [blocks[(s, rank)] for s in range(stages)]
+        data = np.concatenate([b[0] for b in mine])
+        idx = np.concatenate([b[1] for b in mine])
+        ptr = np.zeros(stages * h + 1, dtype=np.int64)
+        off = 0
+        for s, b in enumerate(mine):
+            ptr[s * h + 1:(s + 1) * h + 1] = b[2][1:] + off
+            off += b[2][-1]
+        part = RowPartitionedCsr(torch.from_numpy(data), torch.from_numpy(idx),
+                                 torch.from_numpy(ptr), n_cols, local_spmv=_oracle_spmv)
+        assert part.split_stages(stages)
+        x = torch.from_numpy(np.random.default_rng(5).standard_normal(n_cols))
+        y = part.spmv(x.clone() if rank == 0 else torch.zeros_like(x), src=0)
+        expect = np.concatenate([oracle.spmv(*blocks[(s, p)], x.numpy(), (h, n_cols))
+                                 for s in range(stages) for p in range(world)])
+        results[rank] = bool(np.array_equal(y.numpy(), expect))
+        assert not part.split_stages(7)          # 60 rows do not split into 7 equal stages
+    finally:
+        dist.destroy_process_group()
+
+
+def test_staged_block_cyclic_gather_on_two_gloo_ranks():
+    world = 2
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_staged_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert results[0] and results[1]
+
+
 def _free_port():
     import socket
     with socket.socket() as s:
