@@ -88,6 +88,8 @@ class CsrPlan:
         self._scratch = {}                   # (tag, width, stream) -> tensor
         self._transposed = {}                # conj flag -> CsrPlan of the transpose
         self._panels = False                 # False: not decided yet; None: not used
+        self._spmv_record = None             # prebuilt launch arguments (spmv.py)
+        self._prepared = {}                  # memo of PreparedCsrSpmv handles (spmv.py)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.status_checked = False
 
@@ -110,7 +112,10 @@ class CsrPlan:
 
     def scratch(self, tag, n_values, dtype=None):
         """Scratch of n_values elements, one buffer per (purpose, size, stream)."""
-        stream = torch.cuda.current_stream(self.device).cuda_stream
+        return self.scratch_on(tag, n_values, torch.cuda.current_stream(self.device).cuda_stream,
+                               dtype)
+
+    def scratch_on(self, tag, n_values, stream, dtype=None):
         key = (tag, int(n_values), stream)
         buf = self._scratch.get(key)
         if buf is None:

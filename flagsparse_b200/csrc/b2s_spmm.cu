@@ -14,8 +14,11 @@ namespace b2s {
 #ifndef B2S_SPMM_CHUNKED
 #define B2S_SPMM_CHUNKED 2  // 0: team-per-row kernel; 1: chunk kernel; 2: chunk kernel for narrow B rows
 #endif
+#ifndef B2S_SPMM_GROUP_NNZ
+#define B2S_SPMM_GROUP_NNZ 16  // entries one group of lanes takes before a row is split over more groups
+#endif
 #ifndef B2S_SPMM_THREADS
-#define B2S_SPMM_THREADS 256
+#define B2S_SPMM_THREADS 128
 #endif
 #ifndef B2S_SPMM_ITEMS
 #define B2S_SPMM_ITEMS 1024
@@ -277,7 +280,7 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   int S = 1;
   {
     const int mean = (n_nz + n_seg - 1) / n_seg;
-    while (S * 16 < mean && S < groups_per_warp) S <<= 1;
+    while (S * B2S_SPMM_GROUP_NNZ < mean && S < groups_per_warp) S <<= 1;
   }
   const int team = S * G;  // lanes per row piece
   const int p1max = (S == groups_per_warp) ? kSpmmWarpRowMax : 64 * S;

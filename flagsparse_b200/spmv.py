@@ -180,7 +180,12 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
     op_code = normalize_op(op, transpose=transpose)
     if op is not None and bool(transpose) and op_code == OP_NON:
         raise ValueError("transpose=True conflicts with op=non")
-    plan = _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy)
+    base_plan = _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy)
+    memo_key = (op_code, block_nnz, max_segments, index_fallback_policy)
+    memo = base_plan._prepared.get(memo_key)
+    if memo is not None:  # the same matrix prepared the same way: reuse the handle
+        return memo
+    plan = base_plan
     if op_transposes(op_code):
         plan = plan.transposed(conj=(op_code == OP_CONJ_TRANS))
         if plan.max_row_nnz < 0:
@@ -197,12 +202,14 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
             max_segments_use = max((max_row_nnz + block_nnz_use - 1) // block_nnz_use, 1)
     else:
         max_segments_use = max_segments
-    return PreparedCsrSpmv(
+    prepared = PreparedCsrSpmv(
         data=plan.data, kernel_indices=plan.indices, kernel_indptr=plan.indptr, shape=plan.shape,
         n_rows=plan.n_rows, n_cols=plan.n_cols, block_nnz=block_nnz_use,
         max_segments=max_segments_use, opt_max_segments=max_segments, max_row_nnz=max_row_nnz,
         transpose=op_transposes(op_code), op=op_code,
         index_fallback_policy=index_fallback_policy, _plan=plan)
+    base_plan._prepared[memo_key] = prepared
+    return prepared
 
 
 def _validate_spmv_x(x, prepared):
@@ -227,36 +234,70 @@ def _validate_spmv_x(x, prepared):
 # -------------------------------------------------------------------------------------------------
 # launch
 # -------------------------------------------------------------------------------------------------
-def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
-    """Enqueue y = alpha * A x + beta * y_in on the current stream (no synchronisation)."""
+_SCALAR_CACHE = {}
+
+
+def _scalar(value, dtype):
+    """Host buffer for alpha / beta; the usual values are built once."""
+    key = (value, dtype)
+    buf = _SCALAR_CACHE.get(key)
+    if buf is None:
+        buf = _lib.scalar_buffer(value, dtype)
+        if len(_SCALAR_CACHE) < 64:
+            _SCALAR_CACHE[key] = buf
+    return buf
+
+
+def _spmv_launch_record(plan: CsrPlan):
+    """Everything about a launch that depends only on the matrix, as ready-made ctypes values
+    (built once per plan; keeps the steady-state call short for launch-latency-bound sizes)."""
+    rec = plan._spmv_record
+    if rec is not None:
+        return rec
     lib = _lib.load()
     items = lib.b2s_spmv_tile_items(plan.vcode, plan.icode)
-    dtype = plan.data.dtype
-    a = _lib.scalar_buffer(alpha, dtype)
-    b = _lib.scalar_buffer(beta, dtype)
     lay = plan.panels()
-    with torch.cuda.device(plan.device):
-        if lay is None:
-            n_tiles, tile_row = plan.tiles(items)
-            carry = plan.scratch("spmv_carry", n_tiles)
-            st = lib.b2s_spmv_csr(
-                plan.vcode, plan.icode, plan.pcode,
-                _lib.ptr(plan.data), _lib.ptr(plan.indices), _lib.ptr(plan.indptr),
-                plan.n_rows, plan.n_cols, plan.nnz,
-                _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b,
-                _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status),
-                _lib.stream_handle(plan.device))
-        else:
-            n_tiles, tile_row = plan.panel_tiles(items)
-            carry = plan.scratch("spmv_panel_carry", n_tiles)
-            ypart = plan.scratch("spmv_panel_part", lay.n_panels * plan.n_rows)
-            st = lib.b2s_spmv_panels(
-                plan.vcode, lay.pcode, _lib.ptr(lay.data), _lib.ptr(lay.cols), _lib.ptr(lay.ptr),
+    if lay is None:
+        n_tiles, tile_row = plan.tiles(items)
+        head = (plan.vcode, plan.icode, plan.pcode, _lib.ptr(plan.data), _lib.ptr(plan.indices),
+                _lib.ptr(plan.indptr), plan.n_rows, plan.n_cols, plan.nnz)
+        rec = (lib.b2s_spmv_csr, head, _lib.ptr(tile_row), n_tiles, None, _lib.ptr(plan.status))
+    else:
+        n_tiles, tile_row = plan.panel_tiles(items)
+        head = (plan.vcode, lay.pcode, _lib.ptr(lay.data), _lib.ptr(lay.cols), _lib.ptr(lay.ptr),
                 plan.n_rows, plan.n_cols, plan.nnz, lay.n_panels, lay.shift,
-                _lib.ptr(lay.panel_start), _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b,
-                _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(ypart), _lib.ptr(plan.status),
-                _lib.stream_handle(plan.device))
-    _lib.check(st, "b2s_spmv")
+                _lib.ptr(lay.panel_start))
+        rec = (lib.b2s_spmv_panels, head, _lib.ptr(tile_row), n_tiles, lay,
+               _lib.ptr(plan.status))
+    plan._spmv_record = rec
+    return rec
+
+
+def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
+    """Enqueue y = alpha * A x + beta * y_in on the current stream (no synchronisation)."""
+    fn, head, tile_row_p, n_tiles, lay, status_p = _spmv_launch_record(plan)
+    dtype = plan.data.dtype
+    a = _scalar(alpha, dtype)
+    b = _scalar(beta, dtype)
+    dev_index = plan.device.index
+    switch = torch.cuda.current_device() != dev_index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev_index)
+    try:
+        stream = torch.cuda.current_stream(plan.device).cuda_stream
+        carry = plan.scratch_on("spmv_carry", n_tiles, stream)
+        tail = (_lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b, tile_row_p, _lib.ptr(carry))
+        if lay is None:
+            st = fn(*head, *tail, status_p, stream)
+        else:
+            ypart = plan.scratch_on("spmv_panel_part", lay.n_panels * plan.n_rows, stream)
+            st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream)
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    if st:
+        _lib.check(st, "b2s_spmv")
     if not plan.status_checked:
         plan.check_status()
 
