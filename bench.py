@@ -581,6 +581,32 @@ def main():
         del p.extra["B"], mm_out
         torch.cuda.empty_cache()
 
+    if nbytes < 1e9:
+        # small problems are bound by launch latency: the same products replayed from a CUDA
+        # graph separate the device time from the Python / launch overhead
+        try:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    step()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        step()
+            torch.cuda.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            graph.replay()
+            g0.record()
+            for _ in range(20):
+                graph.replay()
+            g1.record()
+            torch.cuda.synchronize()
+            per = g0.elapsed_time(g1) / 400.0 / 1e3
+            extra["cuda_graph_replay"] = {"us_per_product": per * 1e6, "gbs": nbytes / per / 1e9}
+        except Exception as exc:  # reported, never fatal for the bench line
+            extra["cuda_graph_replay"] = {"error": str(exc)[:200]}
+
     line = {
         "metric": "effective HBM GB/s (algorithmic bytes / time)",
         "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,

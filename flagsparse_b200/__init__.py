@@ -27,7 +27,11 @@ from .spmv import (
     SPMV_OP_NON,
     SPMV_OP_TRANS,
     PreparedCsrSpmv,
+    coo_to_csr_for_spmv,
+    csr_to_csc,
+    flagsparse_spmv_coo_tocsr,
     flagsparse_spmv_csr,
+    prepare_spmv_coo_tocsr,
     prepare_spmv_csr,
     spmv_csr,
 )
@@ -41,6 +45,10 @@ __all__ = [
     "PreparedCsrSpmv",
     "spmv_csr",
     "spmm_csr",
+    "flagsparse_spmv_coo_tocsr",
+    "prepare_spmv_coo_tocsr",
+    "coo_to_csr_for_spmv",
+    "csr_to_csc",
     "install",
     "clear_plan_cache",
     "set_plan_cache_capacity",

@@ -459,3 +459,85 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
 
 
 spmv_csr = flagsparse_spmv_csr
+
+
+# -------------------------------------------------------------------------------------------------
+# COO front door  (spmv_csr.py:916-1057)
+# -------------------------------------------------------------------------------------------------
+def coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=False):
+    """COO triple -> (data, int32 column indices, int64 indptr) in (row, col) order, the layout
+    the reference's conversion produces (spmv_csr.py:926-950).  Already ordered input (or
+    ``assume_sorted``) is passed through without a sort."""
+    n_rows, n_cols = int(shape[0]), int(shape[1])
+    rows64 = row.to(torch.int64)
+    cols64 = col.to(torch.int64)
+    indptr = torch.zeros(n_rows + 1, dtype=torch.int64, device=data.device)
+    if rows64.numel() == 0:
+        return data, cols64.to(torch.int32), indptr
+    ordered = bool(assume_sorted)
+    if not ordered:
+        key = rows64 * max(1, n_cols) + cols64
+        ordered = bool((key[1:] >= key[:-1]).all().item()) if key.numel() > 1 else True
+        if not ordered:
+            perm = torch.argsort(key)
+            rows64, cols64, data = rows64[perm], cols64[perm], data[perm]
+    torch.cumsum(torch.bincount(rows64, minlength=n_rows), dim=0, out=indptr[1:])
+    return data, cols64.to(torch.int32), indptr
+
+
+def _check_coo(data, row, col, x=None):
+    tensors = (data, row, col) if x is None else (data, row, col, x)
+    names = "data, row, col" if x is None else "data, row, col, x"
+    if not all(torch.is_tensor(t) for t in tensors):
+        raise TypeError(f"{names} must all be torch.Tensor")
+    if not all(t.is_cuda for t in tensors):
+        raise ValueError(f"{names} must all be CUDA tensors")
+    if any(t.ndim != 1 for t in tensors):
+        raise ValueError(f"{names} must all be 1D tensors")
+    if data.dtype not in SUPPORTED_SPMV_VALUE_DTYPES:
+        raise TypeError(_spmv_dtype_error_message())
+
+
+def prepare_spmv_coo_tocsr(data, row, col, shape, block_nnz=256, max_segments=None,
+                           assume_sorted=False):
+    """One-time COO -> CSR conversion plus plan; use with
+    ``flagsparse_spmv_coo_tocsr(x=..., prepared=p)`` (spmv_csr.py:953-985)."""
+    _check_coo(data, row, col)
+    if row.numel() != col.numel() or data.numel() != row.numel():
+        raise ValueError("data, row, col must have the same length")
+    d, i, p = coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=assume_sorted)
+    return prepare_spmv_csr(d, i, p, shape, block_nnz=block_nnz, max_segments=max_segments)
+
+
+def flagsparse_spmv_coo_tocsr(data=None, row=None, col=None, x=None, shape=None, block_nnz=256,
+                              max_segments=None, out=None, return_time=False, use_opt=True,
+                              prepared=None, assume_sorted=False):
+    """COO SpMV through the CSR kernels: y = A @ x (spmv_csr.py:988-1057)."""
+    if prepared is not None:
+        if x is None:
+            raise TypeError("x is required")
+        if shape is None:
+            shape = prepared.shape
+        sh = (int(shape[0]), int(shape[1]))
+        if sh != prepared.shape:
+            raise ValueError(f"shape {sh} does not match prepared.shape {prepared.shape}")
+        return flagsparse_spmv_csr(x=x, shape=shape, block_nnz=block_nnz,
+                                   max_segments=max_segments, out=out, return_time=return_time,
+                                   use_opt=use_opt, prepared=prepared)
+    _check_coo(data, row, col, x)
+    if x.dtype != data.dtype:
+        raise TypeError("x dtype must match data dtype")
+    d, i, p = coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=assume_sorted)
+    return flagsparse_spmv_csr(d, i, p, x, shape, block_nnz=block_nnz,
+                               max_segments=max_segments, out=out, return_time=return_time,
+                               use_opt=use_opt)
+
+
+def csr_to_csc(data, indices, indptr, shape, conj=False):
+    """CSR(A) -> CSR(A^T) (= CSC of A) with the B200 transpose kernel: (data, indices, indptr,
+    (n_cols, n_rows)).  Entries of an output row keep ascending source-row order; ``conj``
+    conjugates complex values.  FlagSparse only has this step hidden inside its SpMV / SpMM
+    (spmv_csr.py:477-515, spmm_csr.py:300-338)."""
+    plan = _checked_spmv_plan(data, indices, indptr, shape)
+    t = plan.transposed(conj=conj)
+    return t.data, t.indices, t.indptr, (t.n_rows, t.n_cols)

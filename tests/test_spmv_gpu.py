@@ -280,3 +280,38 @@ def test_spmv_column_panel_layout_vs_oracle(monkeypatch, dtype, idx_dtype, targe
     yt = flagsparse_spmv_csr(*args[:3], dev(random_values(rng, n_rows, dtype)), args[4], op="trans")
     assert yt.shape == (n_cols,)
     clear_plan_cache()
+
+
+def test_spmv_coo_front_door_and_public_transpose():
+    """flagsparse_spmv_coo_tocsr (spmv_csr.py:988-1057): unsorted COO with duplicates, the
+    prepared form, and csr_to_csc against the oracle's stable transpose."""
+    from flagsparse_b200 import (csr_to_csc, flagsparse_spmv_coo_tocsr, prepare_spmv_coo_tocsr)
+    rng = np.random.default_rng(77)
+    n_rows, n_cols, nnz = 500, 300, 6000
+    row = rng.integers(0, n_rows, nnz)
+    col = rng.integers(0, n_cols, nnz)
+    for dtype in (np.float32, np.float64, np.complex64):
+        data = random_values(rng, nnz, dtype)
+        x = random_values(rng, n_cols, dtype)
+        order = np.lexsort((col, row))
+        ptr = np.zeros(n_rows + 1, dtype=np.int64)
+        np.cumsum(np.bincount(row, minlength=n_rows), out=ptr[1:])
+        # sums inside a row may be reordered by the unstable sort: compare within tolerance
+        expect = oracle.spmv(data[order], col[order], ptr, x, (n_rows, n_cols))
+        y = flagsparse_spmv_coo_tocsr(dev(data), dev(row), dev(col), dev(x), (n_rows, n_cols))
+        assert_parity(host(y), expect, dtype)
+        prep = prepare_spmv_coo_tocsr(dev(data), dev(row), dev(col), (n_rows, n_cols))
+        y2 = flagsparse_spmv_coo_tocsr(x=dev(x), prepared=prep)
+        assert_parity(host(y2), expect, dtype)
+        with pytest.raises(ValueError, match="does not match prepared.shape"):
+            flagsparse_spmv_coo_tocsr(x=dev(x), prepared=prep, shape=(n_rows, n_cols + 1))
+        t_data, t_idx, t_ptr, t_shape = csr_to_csc(dev(data[order]), dev(col[order]), dev(ptr),
+                                                   (n_rows, n_cols), conj=True)
+        e_data, e_idx, e_ptr, e_shape = oracle.transpose_csr(data[order], col[order], ptr,
+                                                             (n_rows, n_cols), conj=True)
+        assert t_shape == e_shape
+        assert np.array_equal(host(t_ptr), e_ptr) and np.array_equal(host(t_idx), e_idx)
+        assert np.array_equal(host(t_data).view(np.uint8), e_data.view(np.uint8))
+    with pytest.raises(TypeError, match="x dtype must match data dtype"):
+        flagsparse_spmv_coo_tocsr(dev(data), dev(row), dev(col), dev(x).to(torch.complex128),
+                                  (n_rows, n_cols))
