@@ -15,7 +15,7 @@ namespace b2s {
 #define B2S_SPMM_CHUNKED 2  // 0: team-per-row kernel; 1: chunk kernel; 2: chunk kernel for narrow B rows
 #endif
 #ifndef B2S_SPMM_GROUP_NNZ
-#define B2S_SPMM_GROUP_NNZ 16  // entries one group of lanes takes before a row is split over more groups
+#define B2S_SPMM_GROUP_NNZ 32  // entries one group of lanes takes before a row is split over more groups
 #endif
 #ifndef B2S_SPMM_THREADS
 #define B2S_SPMM_THREADS 128
@@ -142,6 +142,33 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
       // all of B lies within 2^32 sixteen-byte units: 32-bit row offsets (one multiply, one
       // widening add per gather instead of a 64-bit multiply)
       const uint32_t s32 = static_cast<uint32_t>(-stride16);
+      if constexpr (sizeof(I) == 4 && sizeof(V) == 4) {
+        // consecutive entries, 4-byte col and val staged with the same 16-byte phase: four
+        // columns and four values per 128-bit shared-memory read
+        const unsigned phase_c = (static_cast<unsigned>(smem_addr(scol)) >> 2) & 3u;
+        const unsigned phase_v = (static_cast<unsigned>(smem_addr(sval)) >> 2) & 3u;
+        if (step == 1 && phase_c == phase_v) {
+          for (; i < e && ((static_cast<unsigned>(i) + phase_c) & 3u); ++i) {
+            Pack<V> b;
+            *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<uint32_t>(scol[i]) * s32);
+            fma_pack(acc, sval[i], b);
+          }
+          for (; i + 3 < e; i += 4) {
+            const uint4 c4 = *reinterpret_cast<const uint4*>(scol + i);
+            Pack<V> b0, b1, b2, b3;
+            *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + c4.x * s32);
+            *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + c4.y * s32);
+            *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + c4.z * s32);
+            *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + c4.w * s32);
+            Pack<V> a4;  // for 4-byte values a pack holds exactly four of them
+            *reinterpret_cast<uint4*>(&a4) = *reinterpret_cast<const uint4*>(sval + i);
+            fma_pack(acc, a4.e[0], b0);
+            fma_pack(acc, a4.e[1], b1);
+            fma_pack(acc, a4.e[2], b2);
+            fma_pack(acc, a4.e[3], b3);
+          }
+        }
+      }
       for (; i + 3 * step < e; i += 4 * step) {
         const uint32_t o0 = static_cast<uint32_t>(scol[i]) * s32;
         const uint32_t o1 = static_cast<uint32_t>(scol[i + step]) * s32;
