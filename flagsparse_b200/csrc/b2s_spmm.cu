@@ -148,25 +148,35 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
         const unsigned phase_c = (static_cast<unsigned>(smem_addr(scol)) >> 2) & 3u;
         const unsigned phase_v = (static_cast<unsigned>(smem_addr(sval)) >> 2) & 3u;
         if (step == 1 && phase_c == phase_v) {
-          for (; i < e && ((static_cast<unsigned>(i) + phase_c) & 3u); ++i) {
-            Pack<V> b;
-            *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<uint32_t>(scol[i]) * s32);
-            fma_pack(acc, sval[i], b);
-          }
-          for (; i + 3 < e; i += 4) {
-            const uint4 c4 = *reinterpret_cast<const uint4*>(scol + i);
+          // whole aligned quads from the quad that contains the first entry to the one that
+          // contains the last; entries of a quad outside [i, e) are masked (column 0, not
+          // added), so there are no ragged head / tail loops to diverge on (reads stay inside
+          // the staging buffers: the quad below index 0 and the one above the last entry fall
+          // into their 16-byte slack or the neighbouring buffer)
+          if (i >= e) return;
+          const int first = i;
+          for (int a = i - static_cast<int>((static_cast<unsigned>(i) + phase_c) & 3u); a < e;
+               a += 4) {
+            uint4 c4 = *reinterpret_cast<const uint4*>(scol + a);
+            Pack<V> a4;
+            *reinterpret_cast<uint4*>(&a4) = *reinterpret_cast<const uint4*>(sval + a);
+            const bool k0 = a >= first, k1 = a + 1 >= first && a + 1 < e,
+                       k2 = a + 2 >= first && a + 2 < e, k3 = a + 3 < e;
+            if (!k0) c4.x = 0;  // masked entries read row 0 of B (a valid address) and are not added
+            if (!k1) c4.y = 0;
+            if (!k2) c4.z = 0;
+            if (!k3) c4.w = 0;
             Pack<V> b0, b1, b2, b3;
             *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + c4.x * s32);
             *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + c4.y * s32);
             *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + c4.z * s32);
             *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + c4.w * s32);
-            Pack<V> a4;  // for 4-byte values a pack holds exactly four of them
-            *reinterpret_cast<uint4*>(&a4) = *reinterpret_cast<const uint4*>(sval + i);
-            fma_pack(acc, a4.e[0], b0);
-            fma_pack(acc, a4.e[1], b1);
-            fma_pack(acc, a4.e[2], b2);
-            fma_pack(acc, a4.e[3], b3);
+            if (k0) fma_pack(acc, a4.e[0], b0);
+            if (k1) fma_pack(acc, a4.e[1], b1);
+            if (k2) fma_pack(acc, a4.e[2], b2);
+            if (k3) fma_pack(acc, a4.e[3], b3);
           }
+          return;
         }
       }
       for (; i + 3 * step < e; i += 4 * step) {

@@ -208,3 +208,21 @@ def test_spmm_api_contract():
     assert meta["op_total_ms"] == pytest.approx(meta["symbolic_ms"] + meta["compute_ms"])
     C, meta = f(data, indices, indptr, B, (2, 2), op="non", return_meta=True)
     assert meta["op"] == "non" and meta["symbolic_ms"] == 0.0
+
+
+def test_spmm_does_not_touch_rows_of_B_it_does_not_reference():
+    """Non-finite values in a row of B that no entry of A points at must not reach C (guards the
+    masked lanes of the vectorised inner loop, which read row 0 of B without adding it)."""
+    from flagsparse_b200 import flagsparse_spmm_csr
+    rng = np.random.default_rng(31)
+    lengths = rng.integers(0, 40, 700)
+    data, idx, ptr = csr_from_lengths(rng, lengths, 399, np.float32)
+    idx = idx + 1                                  # nothing references column 0
+    B = random_values(rng, 400 * 32, np.float32).reshape(400, 32)
+    expect = oracle.spmm(data, idx, ptr, B, (700, 400))
+    B[0, :] = np.inf
+    B[0, ::2] = np.nan
+    C = flagsparse_spmm_csr(dev(data), dev(idx, torch.int32), dev(ptr, torch.int32), dev(B),
+                            (700, 400))
+    assert np.isfinite(host(C)).all()
+    assert_parity(host(C), expect, np.float32)
