@@ -32,6 +32,7 @@ SIGNATURES = {
     "b2s_version": (c_int, []),
     "b2s_status_string": (c_char_p, [c_int]),
     "b2s_tune": (c_int, [c_int, c_int64]),
+    "b2s_selftest_wait_timeout": (c_int, [c_void_p, c_int, c_void_p]),
     "b2s_csr_inspect": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p,
                                 c_void_p]),
     "b2s_tile_count": (c_int64, [c_int64, c_int64, c_int]),
@@ -52,7 +53,10 @@ SIGNATURES = {
     "b2s_spmv_panels": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p]),
+                                c_void_p, c_int64, c_void_p]),
+    "b2s_panel_compact_bytes": (c_int64, [c_int64]),
+    "b2s_panel_compact": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                                  c_void_p, c_int64, c_void_p]),
     "b2s_spmm_csr": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                              c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -60,9 +60,11 @@ def set_panel_policy(policy):
 class PanelLayout:
     """The matrix as a stack of column panels (see include/b200sparse.h, b2s_panel_build)."""
 
-    def __init__(self, data, cols, ptr, panel_start, n_panels, shift):
+    def __init__(self, data, cols, ptr, panel_start, n_panels, shift, n_stacked, subpos):
         self.data, self.cols, self.ptr, self.panel_start = data, cols, ptr, panel_start
         self.n_panels, self.shift = n_panels, shift
+        self.n_stacked = int(n_stacked)     # rows of the stack the kernel sees
+        self.subpos = subpos                # int32[n_panels * n_rows] or None (nothing dropped)
         self.pcode = _lib.INDEX_CODE[ptr.dtype]
         self.tiles = {}
 
@@ -157,7 +159,31 @@ class CsrPlan:
                 _lib.stream_handle(self.device))
         _lib.check(st, "b2s_panel_build")
         del ws
-        self._panels = PanelLayout(p_data, p_cols, p_ptr, panel_start, n_panels, shift)
+        # drop the rows of the stack that have no entries (most short rows live in one panel)
+        n_stacked = n_panels * self.n_rows
+        subpos = None
+        if n_stacked <= INDEX_LIMIT_INT32:
+            subpos = torch.empty(n_stacked, dtype=torch.int32, device=self.device)
+            count = torch.zeros(1, dtype=torch.int64, device=self.device)
+            cbytes = int(lib.b2s_panel_compact_bytes(n_stacked))
+            ws = torch.empty(cbytes, dtype=torch.uint8, device=self.device)
+            pcode = _lib.INDEX_CODE[ptr_dtype]
+            with torch.cuda.device(self.device):
+                st = lib.b2s_panel_compact(_lib.ptr(p_ptr), pcode, n_stacked, _lib.ptr(subpos),
+                                           _lib.ptr(count), None, 0, _lib.ptr(ws), cbytes,
+                                           _lib.stream_handle(self.device))
+            _lib.check(st, "b2s_panel_compact")
+            n_compact = int(count.item())
+            c_ptr = torch.empty(n_compact + 1, dtype=ptr_dtype, device=self.device)
+            with torch.cuda.device(self.device):
+                st = lib.b2s_panel_compact(_lib.ptr(p_ptr), pcode, n_stacked, _lib.ptr(subpos),
+                                           None, _lib.ptr(c_ptr), n_compact, None, 0,
+                                           _lib.stream_handle(self.device))
+            _lib.check(st, "b2s_panel_compact")
+            del ws
+            p_ptr, n_stacked = c_ptr, n_compact
+        self._panels = PanelLayout(p_data, p_cols, p_ptr, panel_start, n_panels, shift,
+                                   n_stacked, subpos)
         return self._panels
 
     def panel_tiles(self, items):
@@ -166,7 +192,7 @@ class CsrPlan:
         if hit is not None:
             return hit
         lib = _lib.load()
-        rows = lay.n_panels * self.n_rows
+        rows = lay.n_stacked
         n_tiles = int(lib.b2s_tile_count(rows, self.nnz, items))
         tile_row = torch.empty(n_tiles + 1, dtype=torch.int64, device=self.device)
         with torch.cuda.device(self.device):

@@ -1,17 +1,25 @@
 // CSR SpMV for sm_100a: y = alpha * A x + beta * y_in.
 //
-// One CTA per merge-path tile.  A tile's col / val range is brought into shared memory by two
-// bulk asynchronous copies (TMA engine) that complete on an mbarrier; the products val * x[col]
-// overwrite the staged values; rows are then reduced out of shared memory with a strategy chosen
-// from the row lengths inside the tile:
-//   1. vector-per-row : a group of T = 1..32 lanes per row, T the power of two that covers the
-//                       tile's mean row length, butterfly (__shfl_xor) reduction;
-//   2. warp-per-row   : rows longer than 8*T (up to 1024 entries) are queued and taken by whole
-//                       warps;
-//   3. CTA-per-row    : longer pieces are reduced by the whole CTA; a row that crosses tile
-//                       borders leaves one partial sum per tile in `carry`, and a second kernel
-//                       adds those partials to the row in ascending tile order.
+// One CTA per merge-path tile (b2s_tile_plan).  The tile's col / val range is read straight from
+// global memory, coalesced, a batch of independent loads per thread, followed by the gathers of x;
+// the products go to shared memory.  The row pieces of the tile are then binned by length and
+// reduced out of shared memory:
+//   <= 8 entries   one thread per row, serial sum;
+//   9 .. 64        vector-per-row: 8 lanes per row, butterfly (__shfl_xor) reduction;
+//   65 .. 1024     warp-per-row, 32-lane butterfly;
+//   longer         the whole CTA; a row that crosses tile borders leaves one partial sum per
+//                  tile in `carry`, and a second kernel adds those partials to the row in
+//                  ascending tile order.
+// Row sums are staged in shared memory and written with a coalesced alpha / beta epilogue.
 // No floating-point atomics: every sum has a fixed shape, so results repeat bit for bit.
+//
+// Column-panel layout (b2s_spmv_panels): the same kernel runs over a stack of CSR matrices, one
+// per panel of columns, with panel-local int32 columns; partial results per (panel, row) are
+// added in ascending panel order by panel_combine_kernel.
+//
+// B2S_SPMV_DIRECT=0 selects the earlier variant that stages col / val with cp.async.bulk and an
+// mbarrier; it is kept for comparison (measured slower: the bulk-copy fills and the re-reads of
+// shared memory load the same L1 data pipe the gathers need).
 #include <mutex>
 
 #include "b2s_tile.cuh"
@@ -413,16 +421,36 @@ __global__ void panel_combine_kernel(const V* __restrict__ ypart, int64_t n_rows
   y[r] = out;
 }
 
+// The same with the empty rows of the stack dropped: subpos[p * n_rows + r] is the position of
+// (panel p, row r) among the non-empty stacked rows, or -1.
+template <class V>
+__global__ void panel_combine_sparse_kernel(const V* __restrict__ ypart,
+                                            const int32_t* __restrict__ subpos, int64_t n_rows,
+                                            int n_panels, const V* y_in, V* y, V alpha, V beta,
+                                            int has_beta) {
+  const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (r >= n_rows) return;
+  V s = vt<V>::zero();
+  for (int p = 0; p < n_panels; ++p) {
+    const int32_t c = subpos[p * n_rows + r];
+    if (c >= 0) s = s + ypart[c];
+  }
+  V out = alpha * s;
+  if (has_beta) out = out + beta * y_in[r];
+  y[r] = out;
+}
+
 template <class V, class P>
 int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_ptr,
                        int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
                        const int64_t* panel_start, const void* x, const void* y_in, void* y,
                        const void* alpha, const void* beta, const int64_t* tile_row, void* carry,
-                       void* ypart, int32_t* status, cudaStream_t stream) {
+                       void* ypart, int32_t* status, cudaStream_t stream,
+                       int64_t n_stacked, const int32_t* subpos) {
   // 1) the stacked matrix (n_panels * n_rows rows, panel-local int32 columns) times x with
   //    alpha = 1, beta = 0 -> one partial result per (panel, row)
   const V one = vt<V>::one(), zero = vt<V>::zero();
-  int st = spmv_launch<V, int32_t, P>(p_data, p_cols, p_ptr, n_rows * n_panels, n_cols, nnz, x,
+  int st = spmv_launch<V, int32_t, P>(p_data, p_cols, p_ptr, n_stacked, n_cols, nnz, x,
                                       nullptr, ypart, &one, &zero, tile_row, carry, status,
                                       stream, panel_start, n_panels, panel_shift);
   if (st != B2S_OK) return st;
@@ -432,10 +460,15 @@ int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_
   const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
   if (has_beta && y_in == nullptr) return B2S_ERR_ARG;
   const int threads = 256;
-  panel_combine_kernel<V><<<static_cast<unsigned>((n_rows + threads - 1) / threads), threads, 0,
-                            stream>>>(static_cast<const V*>(ypart), n_rows, n_panels,
-                                      static_cast<const V*>(y_in), static_cast<V*>(y), a, b,
-                                      has_beta);
+  const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
+  if (subpos != nullptr)
+    panel_combine_sparse_kernel<V><<<grid, threads, 0, stream>>>(
+        static_cast<const V*>(ypart), subpos, n_rows, n_panels, static_cast<const V*>(y_in),
+        static_cast<V*>(y), a, b, has_beta);
+  else
+    panel_combine_kernel<V><<<grid, threads, 0, stream>>>(
+        static_cast<const V*>(ypart), n_rows, n_panels, static_cast<const V*>(y_in),
+        static_cast<V*>(y), a, b, has_beta);
   return launch_status();
 }
 
@@ -468,8 +501,11 @@ extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_de
                                const int64_t* panel_start_dev, const void* x_dev,
                                const void* y_in_dev, void* y_dev, const void* alpha,
                                const void* beta, const int64_t* tile_row_dev, void* carry_dev,
-                               void* ypart_dev, int32_t* status_dev, b2s_stream stream) {
+                               void* ypart_dev, int32_t* status_dev, b2s_stream stream,
+                               int64_t n_stacked, const int32_t* subpos_dev) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0 || !alpha || !beta) return B2S_ERR_ARG;
+  if (subpos_dev == nullptr) n_stacked = n_rows * n_panels;
+  if (n_stacked < 0 || n_stacked > n_rows * n_panels) return B2S_ERR_ARG;
   if (n_panels < 1 || n_panels > 256 || panel_shift < 0 || panel_shift > 40) return B2S_ERR_ARG;
   if (n_rows == 0) return B2S_OK;
   if (!p_ptr_dev || !y_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
@@ -487,7 +523,7 @@ extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_de
     return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
                                           n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
                                           y_dev, alpha, beta, tile_row_dev, carry_dev, ypart_dev,
-                                          status_dev, s));
+                                          status_dev, s, n_stacked, subpos_dev));
   }));
   return B2S_ERR_DTYPE;
 }
@@ -579,4 +615,37 @@ extern "C" int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type, cons
   return b2s_spmv_csr(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
                       n_cols, nnz, x_dev, y_in_dev, y_dev, alpha, beta, fs->tile_row, fs->carry,
                       nullptr, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp waits on an mbarrier that nothing ever completes, with
+// a small iteration limit.  The wait gives up, the kernel ORs B2S_ERR_TIMEOUT into the status
+// word and returns normally; the context stays usable.  Used by the failure-path test.
+// ---------------------------------------------------------------------------------------------
+namespace b2s {
+__global__ void wait_timeout_selftest_kernel(int32_t* status, int limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) mbar_init(&bar, 1);
+  __syncthreads();
+  const uint32_t a = smem_addr(&bar);
+  bool done = false;
+  for (int it = 0; it < limit && !done; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; "
+        "selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(a), "r"(0u), "r"(1000u)
+        : "memory");
+    done = ok != 0;
+  }
+  if (!done && threadIdx.x == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
+}
+}  // namespace b2s
+
+extern "C" int b2s_selftest_wait_timeout(int32_t* status_dev, int spin_limit, b2s_stream stream) {
+  if (!status_dev || spin_limit < 1 || spin_limit > 100000) return B2S_ERR_ARG;
+  b2s::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status_dev,
+                                                                                   spin_limit);
+  return b2s::launch_status();
 }

@@ -295,6 +295,42 @@ __global__ void panel_start_kernel(const PP* __restrict__ p_ptr, int64_t n_rows,
   if (p <= n_panels) panel_start[p] = static_cast<int64_t>(p_ptr[p * n_rows]);
 }
 
+// ---- dropping the empty rows of the stack ------------------------------------------------------
+// Most rows have entries in only some panels (a row with one entry is empty in all panels but
+// one).  pos[q] = 1 if stacked row q has entries; after an exclusive scan pos[q] is its index
+// among the non-empty rows.
+template <class PP>
+__global__ void panel_flag_kernel(const PP* __restrict__ p_ptr, int64_t n_stacked,
+                                  uint32_t* __restrict__ pos) {
+  const int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (q < n_stacked) pos[q] = p_ptr[q + 1] > p_ptr[q] ? 1u : 0u;
+}
+
+// subpos[q] = index of stacked row q among the non-empty ones, or -1; the last thread also
+// stores the number of non-empty rows
+template <class PP>
+__global__ void panel_subpos_kernel(const PP* __restrict__ p_ptr, int64_t n_stacked,
+                                    const uint32_t* __restrict__ pos,
+                                    int32_t* __restrict__ subpos, int64_t* __restrict__ count) {
+  const int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (q >= n_stacked) return;
+  const bool full = p_ptr[q + 1] > p_ptr[q];
+  subpos[q] = full ? static_cast<int32_t>(pos[q]) : -1;
+  if (q == n_stacked - 1) *count = static_cast<int64_t>(pos[q]) + (full ? 1 : 0);
+}
+
+// row pointers of the non-empty rows only
+template <class PP>
+__global__ void panel_compact_ptr_kernel(const PP* __restrict__ p_ptr, int64_t n_stacked,
+                                         const int32_t* __restrict__ subpos, int64_t n_compact,
+                                         PP* __restrict__ c_ptr) {
+  const int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (q >= n_stacked) return;
+  const int32_t c = subpos[q];
+  if (c >= 0) c_ptr[c] = p_ptr[q];
+  if (q == n_stacked - 1) c_ptr[n_compact] = p_ptr[n_stacked];
+}
+
 template <class W>
 int64_t panel_scratch_bytes(int64_t nnz) {
   const int64_t n_blocks = (nnz + kRxChunk - 1) / kRxChunk;
@@ -335,6 +371,45 @@ int panel_build_run(const void* data, const void* indices, const void* indptr, i
 }
 
 }  // namespace b2s
+
+extern "C" int64_t b2s_panel_compact_bytes(int64_t n_stacked) {
+  if (n_stacked <= 0) return 256;
+  return b2s::align256(n_stacked * sizeof(uint32_t)) +
+         b2s::align256(b2s::scan_scratch_elems(n_stacked) * sizeof(uint32_t));
+}
+
+extern "C" int b2s_panel_compact(const void* p_ptr_dev, int p_ptr_type, int64_t n_stacked,
+                                 int32_t* subpos_dev, int64_t* count_dev, void* c_ptr_dev,
+                                 int64_t n_compact, void* scratch_dev, int64_t scratch_bytes,
+                                 b2s_stream stream) {
+  if (!p_ptr_dev || !subpos_dev || n_stacked <= 0 || n_stacked > 0x7fffffffLL) return B2S_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>((n_stacked + 255) / 256);
+  if (c_ptr_dev == nullptr) {
+    // phase 1: positions of the non-empty rows and their number
+    if (!count_dev || !scratch_dev) return B2S_ERR_ARG;
+    if (b2s_panel_compact_bytes(n_stacked) > scratch_bytes) return B2S_ERR_WORKSPACE;
+    uint32_t* pos = static_cast<uint32_t*>(scratch_dev);
+    uint32_t* scan_ws = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(scratch_dev) +
+                                                    b2s::align256(n_stacked * sizeof(uint32_t)));
+    B2S_DISPATCH_I(p_ptr_type, PP, {
+      (b2s::panel_flag_kernel<PP><<<grid, 256, 0, s>>>(static_cast<const PP*>(p_ptr_dev),
+                                                       n_stacked, pos));
+      b2s::exclusive_scan<uint32_t>(pos, n_stacked, scan_ws, s);
+      (b2s::panel_subpos_kernel<PP><<<grid, 256, 0, s>>>(static_cast<const PP*>(p_ptr_dev),
+                                                         n_stacked, pos, subpos_dev, count_dev));
+    });
+    return b2s::launch_status();
+  }
+  // phase 2: the compacted row pointers (n_compact + 1 entries)
+  if (n_compact < 0) return B2S_ERR_ARG;
+  B2S_DISPATCH_I(p_ptr_type, PP, {
+    (b2s::panel_compact_ptr_kernel<PP><<<grid, 256, 0, s>>>(
+        static_cast<const PP*>(p_ptr_dev), n_stacked, subpos_dev, n_compact,
+        static_cast<PP*>(c_ptr_dev)));
+  });
+  return b2s::launch_status();
+}
 
 extern "C" int64_t b2s_panel_bytes(int64_t n_cols, int64_t nnz) {
   if (nnz <= 0) return 256;

@@ -291,8 +291,9 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
         if lay is None:
             st = fn(*head, *tail, status_p, stream)
         else:
-            ypart = plan.scratch_on("spmv_panel_part", lay.n_panels * plan.n_rows, stream)
-            st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream)
+            ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
+            st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream, lay.n_stacked,
+                    _lib.ptr(lay.subpos))
     finally:
         if switch:
             torch.cuda.set_device(prev)

@@ -55,6 +55,12 @@ const char* b2s_status_string(int status);
  * Knob 2: bytes of x kept in the persisting part of L2 (0 = off). */
 int b2s_tune(int knob, int64_t value);
 
+/* Failure-path self-test (no counterpart in the reference): launches one warp that waits, with
+ * `spin_limit` (1..100000) bounded tries of about a microsecond each, on a barrier nothing
+ * completes.  The wait runs out, bit B2S_ERR_TIMEOUT is ORed into *status_dev and the kernel
+ * returns normally -- the behaviour every bounded wait in the library has when a copy is lost. */
+int b2s_selftest_wait_timeout(int32_t* status_dev, int spin_limit, b2s_stream stream);
+
 /* ---- input contract ------------------------------------------------------------------------
  * Replaces the device reductions behind the `.item()` checks of _prepare_spmv_csr_matrix
  * (spmv_csr.py:546-563) and _prepare_spmm_csr_matrix (spmm_csr.py:268-296).  One pass over
@@ -135,9 +141,20 @@ int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type,
  * flight stays L2-resident), leaves one partial per (panel, row) in ypart_dev
  * (n_panels * n_rows values) and adds them in ascending panel order with the alpha / beta
  * epilogue.  p_ptr has n_panels * n_rows + 1 entries of p_ptr_type; panel_start_dev has
- * n_panels + 1 int64 entries; tile_row / carry are sized for the stacked matrix
- * (b2s_tile_count(n_panels * n_rows, nnz, b2s_spmv_tile_items(...))).
+ * n_panels + 1 int64 entries.
+ * b2s_panel_compact drops the empty rows of the stack (a row with few entries is empty in most
+ * panels): called with c_ptr_dev == NULL it fills subpos_dev (n_panels * n_rows int32: position
+ * of each stacked row among the non-empty ones, or -1) and *count_dev; called again with
+ * c_ptr_dev it writes the count + 1 row pointers of the non-empty rows.  b2s_spmv_panels then
+ * takes the compacted pointers as p_ptr_dev, n_stacked = count and subpos_dev (or
+ * n_stacked = n_panels * n_rows and subpos_dev = NULL for the uncompacted stack); tile_row /
+ * carry / ypart are sized for n_stacked rows (b2s_tile_count(n_stacked, nnz, items)).
  */
+int64_t b2s_panel_compact_bytes(int64_t n_stacked);
+int b2s_panel_compact(const void* p_ptr_dev, int p_ptr_type, int64_t n_stacked,
+                      int32_t* subpos_dev, int64_t* count_dev, void* c_ptr_dev,
+                      int64_t n_compact, void* scratch_dev, int64_t scratch_bytes,
+                      b2s_stream stream);
 int64_t b2s_panel_bytes(int64_t n_cols, int64_t nnz);
 int b2s_panel_build(int val_type, int idx_type, int ptr_type,
                     const void* data_dev, const void* indices_dev, const void* indptr_dev,
@@ -152,7 +169,8 @@ int b2s_spmv_panels(int val_type, int ptr_type,
                     const void* x_dev, const void* y_in_dev, void* y_dev,
                     const void* alpha, const void* beta,
                     const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
-                    int32_t* status_dev, b2s_stream stream);
+                    int32_t* status_dev, b2s_stream stream,
+                    int64_t n_stacked, const int32_t* subpos_dev);
 
 /* ---- SpMM ----------------------------------------------------------------------------------
  * C = alpha * A B + beta * C_in, B (n_cols x n_dense, leading dimension ldb) and

@@ -171,3 +171,25 @@ def test_inspect_reports_contract_violations():
                              L.stream_handle(ptr.device))
     assert st == 0
     assert stats.tolist()[:7] == [0, 7, 1, -2, 9, 5, 1]
+
+
+def test_bounded_wait_runs_out_with_a_status_bit_not_a_hang():
+    """A wait that can never be satisfied gives up after its iteration limit, reports
+    B2S_ERR_TIMEOUT through the status word, and leaves the context usable; the Python layer
+    turns the bit into an exception."""
+    lib, L = _lib()
+    from flagsparse_b200._plan import CsrPlan
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.b2s_selftest_wait_timeout(L.ptr(status), 200, L.stream_handle(status.device)) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 << L.B2S_ERR_TIMEOUT
+    assert lib.b2s_selftest_wait_timeout(L.ptr(status), 0, L.stream_handle(status.device)) == 2
+    # the context still works, and a plan whose status word carries the bit raises
+    ptr = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    plan = CsrPlan(torch.ones(1, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"),
+                   ptr, (1, 1), 1)
+    plan.status.copy_(status)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        plan.check_status()
+    assert int(plan.status.item()) == 0
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
