@@ -41,7 +41,7 @@ NOMINAL_HBM_GBS = 8000.0
 
 # DRAM bytes (read + written) of one step from ncu (dram__bytes_read.sum + dram__bytes_write.sum
 # over the kernels of a step; profiles/spmv_cfg2_step_launches_dram.md), keyed by (workload, scale)
-NCU_TRAFFIC_BYTES = {("cfg2", 1): 5.02e9}
+NCU_TRAFFIC_BYTES = {("cfg2", 1): 4.50e9}
 
 
 def measured_peaks():
