@@ -82,17 +82,19 @@ constexpr size_t spmv_smem_bytes() {
 // CTAs per SM the register allocation aims at.  12 x 128 threads (<= 42 registers) measured 13 %
 // faster than the 10 the compiler settles on by itself (more gathers in flight); 16-byte values
 // and 8-byte column indices need more registers and would spill at that limit.
-template <class V, class I>
+template <class V, class I, int THREADS>
 constexpr int spmv_min_blocks() {
 #ifdef B2S_SPMV_MINBLOCKS
   return B2S_SPMV_MINBLOCKS;
 #else
-  return (sizeof(V) <= 8 && sizeof(I) == 4) ? 12 : (sizeof(V) <= 8 ? 10 : 8);
+  constexpr int want = (sizeof(V) <= 8 && sizeof(I) == 4) ? 12 : (sizeof(V) <= 8 ? 10 : 8);
+  constexpr int fit = 2048 / THREADS;  // resident threads per SM
+  return want < fit ? want : fit;
 #endif
 }
 
 template <class V, class I, class P, int THREADS, int ITEMS>
-__global__ void __launch_bounds__(THREADS, spmv_min_blocks<V, I>())
+__global__ void __launch_bounds__(THREADS, spmv_min_blocks<V, I, THREADS>())
 spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ x, const V* y_in, V* y, V* __restrict__ carry,
                  const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t nnz, V alpha,
