@@ -193,3 +193,43 @@ def test_bounded_wait_runs_out_with_a_status_bit_not_a_hang():
         plan.check_status()
     assert int(plan.status.item()) == 0
     assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+
+
+def test_csr2csc_with_more_than_2_31_columns_uses_the_64_bit_sort():
+    """n_cols just above 2^31 forces the 64-bit keys of the radix sort (the path nnz > 2^31 would
+    also take).  Checked against torch's stable sort on the device; needs ~30 GB of HBM."""
+    lib, L = _lib()
+    if torch.cuda.get_device_properties(0).total_memory < 60 * 2**30:
+        pytest.skip("needs a large GPU")
+    n_cols = 2**31 + 1000
+    n_rows = 3000
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    lengths = torch.randint(0, 700, (n_rows,), generator=g, device="cuda")
+    ptr = torch.zeros(n_rows + 1, dtype=torch.int64, device="cuda")
+    torch.cumsum(lengths, 0, out=ptr[1:])
+    nnz = int(ptr[-1])
+    # columns: half spread over the whole range, half piled onto a few columns (long output rows)
+    idx = torch.randint(0, n_cols, (nnz,), generator=g, device="cuda", dtype=torch.int64)
+    idx[::2] = (idx[::2] % 7) * 300_000_007 % n_cols
+    data = torch.randn(nnz, generator=g, device="cuda", dtype=torch.float32)
+    t_data, t_idx = torch.empty_like(data), torch.empty_like(idx)
+    t_ptr = torch.empty(n_cols + 1, dtype=torch.int64, device="cuda")
+    nbytes = lib.b2s_csr2csc_bytes(n_rows, n_cols, nnz)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    st = lib.b2s_csr2csc(L.B2S_F32, L.B2S_I64, L.B2S_I64, L.ptr(data), L.ptr(idx), L.ptr(ptr),
+                         n_rows, n_cols, nnz, 0, L.ptr(t_data), L.ptr(t_idx), L.ptr(t_ptr),
+                         L.ptr(ws), nbytes, L.stream_handle(data.device))
+    assert st == 0
+    order = torch.sort(idx, stable=True).indices
+    rows = torch.repeat_interleave(torch.arange(n_rows, device="cuda"), lengths)
+    assert torch.equal(t_idx, rows[order])
+    assert torch.equal(t_data, data[order])
+    # column pointers: spot-check against counts (a full bincount would need 17 GB more)
+    assert int(t_ptr[0]) == 0 and int(t_ptr[-1]) == nnz
+    probe = torch.unique(idx)[:2000]
+    counts = (idx.unsqueeze(0) == probe[:50].unsqueeze(1)).sum(1)
+    assert torch.equal(t_ptr[probe[:50] + 1] - t_ptr[probe[:50]], counts)
+    assert bool((t_ptr[1:200_000] >= t_ptr[:199_999]).all())
+    del ws, t_ptr
+    torch.cuda.empty_cache()
