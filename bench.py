@@ -16,8 +16,11 @@ rows up to 100,000 entries, y = 1.5 * A x + 0.5 * y.  A step is one such product
   --impl reference   only that CPU measurement, as its own line
 
 With N > 1 (launched by torchrun, one rank per GPU) every rank owns one row block of the same
-size (weak scaling): x is broadcast from rank 0, each rank multiplies its block, y is
-all-gathered; value counts the bytes all ranks processed over the slowest rank's time.
+size (weak scaling): x is broadcast from rank 0 (NCCL), each rank multiplies its block, and y is
+assembled on every rank -- by default the last kernel of each rank stores its block straight into
+all ranks' symmetric-memory buffers over NVLink (--gather peer), alternatively by an NCCL
+all-gather (--gather nccl); value counts the bytes all ranks processed over the slowest rank's
+time.
 """
 
 from __future__ import annotations
@@ -417,11 +420,28 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     def gather():
         part.gather_rows(out_local, out=out_full)
 
-    staged = part.split_stages(args.stages)
+    staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
+    gather = args.gather
+    if gather == "peer":
+        # the last kernel of every rank stores its block into all ranks' result buffers; if
+        # symmetric memory cannot be set up on any rank, every rank falls back to NCCL
+        ok = torch.ones(1, dtype=torch.int32, device=device)
+        try:
+            peer_full = part.enable_peer_gather(p.data.dtype, trailing)
+        except Exception as exc:  # noqa: BLE001 - reported below, decided collectively
+            ok.zero_()
+            print(f"[rank {rank}] peer gather unavailable: {exc}", file=sys.stderr, flush=True)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            out_full = peer_full
+        else:
+            part._peer = None
+            gather = "nccl"
 
     def step():
-        if staged:  # kernel of stage s+1 overlaps the all-gather of stage s
+        if staged or gather == "peer":
+            # staged: the gather of stage s overlaps the kernel of stage s+1
             op(dense, src=0, out_local=out_local, out=out_full, alpha=alpha, beta=beta)
         else:
             bcast()
@@ -498,7 +518,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                        "seed": args.seed, "scale": args.scale,
                        "exchange": "NCCL broadcast of x/B from rank 0 + NCCL all-gather of y/C, "
                                    "both inside the timed step",
-                       "stages": args.stages if staged else 1},
+                       "stages": args.stages if staged else 1, "gather": gather},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
                          "peak_kind": peak_kind,
@@ -526,9 +546,12 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOAD_TEXT))
     ap.add_argument("--scale", type=int, default=1, help="divide the row count (debugging)")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--stages", type=int, default=4,
+    ap.add_argument("--stages", type=int, default=1,
                     help="N > 1: row sub-blocks per rank; the all-gather of one overlaps the "
                          "kernel of the next (1 = no overlap)")
+    ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
+                    help="N > 1: how y / C is assembled -- NCCL all-gather, or stores of the last "
+                         "kernel into every rank's symmetric-memory buffer")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the SpMM N=32 side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")

@@ -54,6 +54,16 @@ SIGNATURES = {
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int64, c_void_p]),
+    "b2s_spmv_panels_peers": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int64, c_void_p]),
+    "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
+                                        c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
+                                        c_void_p]),
+    "b2s_peer_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64,
+                                 c_void_p]),
     "b2s_panel_compact_bytes": (c_int64, [c_int64]),
     "b2s_panel_compact": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                   c_void_p, c_int64, c_void_p]),

@@ -454,13 +454,57 @@ __global__ void panel_combine_sparse_kernel(const V* __restrict__ ypart,
   y[r] = out;
 }
 
+// ---- the same combine with the all-gather fused in ---------------------------------------------
+// Every rank of a row-partitioned product owns rows [row_offset, row_offset + n_rows) of the
+// assembled y.  Instead of writing its block locally and handing it to a collective, the combine
+// stores each finished value straight into the y buffer of every rank (its own included) through
+// peer-mapped pointers: ordinary coalesced stores that travel over NVLink.
+struct PeerList {
+  void* p[16];
+};
+
+template <class V>
+__global__ void panel_combine_peers_kernel(const V* __restrict__ ypart,
+                                           const int32_t* __restrict__ subpos, int64_t n_rows,
+                                           int n_panels, const V* y_in, PeerList peers,
+                                           int n_peers, int64_t row_offset, V alpha, V beta,
+                                           int has_beta) {
+  const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (r >= n_rows) return;
+  V s = vt<V>::zero();
+  for (int p = 0; p < n_panels; ++p) {
+    if (subpos != nullptr) {
+      const int32_t c = subpos[p * n_rows + r];
+      if (c >= 0) s = s + ypart[c];
+    } else {
+      s = s + ypart[p * n_rows + r];
+    }
+  }
+  V out = alpha * s;
+  if (has_beta) out = out + beta * y_in[r];
+  for (int q = 0; q < n_peers; ++q) static_cast<V*>(peers.p[q])[row_offset + r] = out;
+}
+
+// Plain block of bytes to the same offset of every peer buffer (16-byte vectors, grid-stride).
+__global__ void peer_scatter_kernel(const uint4* __restrict__ src, int64_t n16, PeerList peers,
+                                    int n_peers, int64_t dst_off16) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n16;
+       i += stride) {
+    const uint4 v = src[i];
+    for (int q = 0; q < n_peers; ++q) static_cast<uint4*>(peers.p[q])[dst_off16 + i] = v;
+  }
+}
+
 template <class V, class P>
 int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_ptr,
                        int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
                        const int64_t* panel_start, const void* x, const void* y_in, void* y,
                        const void* alpha, const void* beta, const int64_t* tile_row, void* carry,
                        void* ypart, int32_t* status, cudaStream_t stream,
-                       int64_t n_stacked, const int32_t* subpos) {
+                       int64_t n_stacked, const int32_t* subpos,
+                       const PeerList* peers = nullptr, int n_peers = 0,
+                       int64_t row_offset = 0) {
   // 1) the stacked matrix (n_panels * n_rows rows, panel-local int32 columns) times x with
   //    alpha = 1, beta = 0 -> one partial result per (panel, row)
   const V one = vt<V>::one(), zero = vt<V>::zero();
@@ -468,6 +512,7 @@ int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_
                                       nullptr, ypart, &one, &zero, tile_row, carry, status,
                                       stream, panel_start, n_panels, panel_shift);
   if (st != B2S_OK) return st;
+  if (y == nullptr && peers == nullptr) return launch_status();  // caller combines separately
   // 2) add the panels of each row and apply alpha / beta
   const V a = *static_cast<const V*>(alpha);
   const V b = *static_cast<const V*>(beta);
@@ -475,7 +520,11 @@ int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_
   if (has_beta && y_in == nullptr) return B2S_ERR_ARG;
   const int threads = 256;
   const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
-  if (subpos != nullptr)
+  if (peers != nullptr)
+    panel_combine_peers_kernel<V><<<grid, threads, 0, stream>>>(
+        static_cast<const V*>(ypart), subpos, n_rows, n_panels, static_cast<const V*>(y_in),
+        *peers, n_peers, row_offset, a, b, has_beta);
+  else if (subpos != nullptr)
     panel_combine_sparse_kernel<V><<<grid, threads, 0, stream>>>(
         static_cast<const V*>(ypart), subpos, n_rows, n_panels, static_cast<const V*>(y_in),
         static_cast<V*>(y), a, b, has_beta);
@@ -522,8 +571,8 @@ extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_de
   if (n_stacked < 0 || n_stacked > n_rows * n_panels) return B2S_ERR_ARG;
   if (n_panels < 1 || n_panels > 256 || panel_shift < 0 || panel_shift > 40) return B2S_ERR_ARG;
   if (n_rows == 0) return B2S_OK;
-  if (!p_ptr_dev || !y_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
-    return B2S_ERR_ARG;
+  if (!p_ptr_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
+    return B2S_ERR_ARG;  // y_dev == NULL: leave the per-panel partials in ypart_dev
   if (nnz > 0 && (!p_data_dev || !p_cols_dev || !x_dev)) return B2S_ERR_ARG;
   const size_t vs = b2s::vsize(val_type);
   if (vs == 0) return B2S_ERR_DTYPE;
@@ -540,6 +589,104 @@ extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_de
                                           status_dev, s, n_stacked, subpos_dev));
   }));
   return B2S_ERR_DTYPE;
+}
+
+static int make_peer_list(void* const* peer_ptrs, int n_peers, size_t align,
+                          b2s::PeerList* out) {
+  if (!peer_ptrs || n_peers < 1 || n_peers > 16) return B2S_ERR_ARG;
+  for (int q = 0; q < 16; ++q) out->p[q] = nullptr;
+  for (int q = 0; q < n_peers; ++q) {
+    if (!peer_ptrs[q]) return B2S_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(peer_ptrs[q]) % align) return B2S_ERR_ALIGNMENT;
+    out->p[q] = peer_ptrs[q];
+  }
+  return B2S_OK;
+}
+
+extern "C" int b2s_spmv_panels_peers(int val_type, int ptr_type, const void* p_data_dev,
+                                     const int32_t* p_cols_dev, const void* p_ptr_dev,
+                                     int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels,
+                                     int panel_shift, const int64_t* panel_start_dev,
+                                     const void* x_dev, const void* y_in_dev,
+                                     void* const* peer_y, int n_peers, int64_t row_offset,
+                                     int64_t peer_rows, const void* alpha, const void* beta,
+                                     const int64_t* tile_row_dev, void* carry_dev,
+                                     void* ypart_dev, int32_t* status_dev, b2s_stream stream,
+                                     int64_t n_stacked, const int32_t* subpos_dev) {
+  if (n_rows < 0 || n_cols < 0 || nnz < 0 || row_offset < 0 || !alpha || !beta) return B2S_ERR_ARG;
+  if (row_offset + n_rows > peer_rows) return B2S_ERR_ARG;  // block must fit the peers' buffers
+  if (subpos_dev == nullptr) n_stacked = n_rows * n_panels;
+  if (n_stacked < 0 || n_stacked > n_rows * n_panels) return B2S_ERR_ARG;
+  if (n_panels < 1 || n_panels > 256 || panel_shift < 0 || panel_shift > 40) return B2S_ERR_ARG;
+  if (n_rows == 0) return B2S_OK;
+  if (!p_ptr_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
+    return B2S_ERR_ARG;
+  if (nnz > 0 && (!p_data_dev || !p_cols_dev || !x_dev)) return B2S_ERR_ARG;
+  const size_t vs = b2s::vsize(val_type);
+  if (vs == 0) return B2S_ERR_DTYPE;
+  b2s::PeerList peers;
+  const int pst = make_peer_list(peer_y, n_peers, vs, &peers);
+  if (pst != B2S_OK) return pst;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(ptr_type, P, {
+    return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
+                                          n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
+                                          nullptr, alpha, beta, tile_row_dev, carry_dev,
+                                          ypart_dev, status_dev, s, n_stacked, subpos_dev, &peers,
+                                          n_peers, row_offset));
+  }));
+  return B2S_ERR_DTYPE;
+}
+
+extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
+                                       const int32_t* subpos_dev, int64_t n_rows, int n_panels,
+                                       const void* y_in_dev, void* const* peer_y, int n_peers,
+                                       int64_t row_offset, int64_t peer_rows, const void* alpha,
+                                       const void* beta, b2s_stream stream) {
+  if (n_rows < 0 || row_offset < 0 || n_panels < 1 || n_panels > 256 || !alpha || !beta)
+    return B2S_ERR_ARG;
+  if (row_offset + n_rows > peer_rows) return B2S_ERR_ARG;
+  if (n_rows == 0) return B2S_OK;
+  if (!ypart_dev) return B2S_ERR_ARG;
+  const size_t vs = b2s::vsize(val_type);
+  if (vs == 0) return B2S_ERR_DTYPE;
+  b2s::PeerList peers;
+  const int pst = make_peer_list(peer_y, n_peers, vs, &peers);
+  if (pst != B2S_OK) return pst;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = 256;
+  const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
+  B2S_DISPATCH_V(val_type, {
+    const V a = *static_cast<const V*>(alpha);
+    const V b = *static_cast<const V*>(beta);
+    const int has_beta = b2s::vt<V>::is_zero(b) ? 0 : 1;
+    if (has_beta && y_in_dev == nullptr) return B2S_ERR_ARG;
+    (b2s::panel_combine_peers_kernel<V><<<grid, threads, 0, s>>>(
+        static_cast<const V*>(ypart_dev), subpos_dev, n_rows, n_panels,
+        static_cast<const V*>(y_in_dev), peers, n_peers, row_offset, a, b, has_beta));
+  });
+  return b2s::launch_status();
+}
+
+extern "C" int b2s_peer_scatter(const void* src_dev, int64_t bytes, void* const* peer_dst,
+                                int n_peers, int64_t dst_offset_bytes, int64_t peer_bytes,
+                                b2s_stream stream) {
+  if (bytes < 0 || dst_offset_bytes < 0) return B2S_ERR_ARG;
+  if (dst_offset_bytes + bytes > peer_bytes) return B2S_ERR_ARG;  // must fit the peers' buffers
+  if (bytes == 0) return B2S_OK;
+  if (!src_dev) return B2S_ERR_ARG;
+  if ((bytes % 16) || (dst_offset_bytes % 16) || (reinterpret_cast<uintptr_t>(src_dev) % 16))
+    return B2S_ERR_ALIGNMENT;
+  b2s::PeerList peers;
+  const int pst = make_peer_list(peer_dst, n_peers, 16, &peers);
+  if (pst != B2S_OK) return pst;
+  const int64_t n16 = bytes / 16;
+  const int threads = 256;
+  int64_t want = (n16 + threads - 1) / threads;
+  const unsigned grid = static_cast<unsigned>(want > 148 * 8 ? 148 * 8 : want);
+  b2s::peer_scatter_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src_dev), n16, peers, n_peers, dst_offset_bytes / 16);
+  return b2s::launch_status();
 }
 
 extern "C" int b2s_spmv_csr(int val_type, int idx_type, int ptr_type, const void* data_dev,

@@ -68,6 +68,7 @@ class RowPartitionedCsr:
         self.row_offset = sum(self.rows_per_rank[: self.rank])
         self._pads = {}
         self._stages = None
+        self._peer = None
 
     @classmethod
     def from_global(cls, data, indices, indptr, shape, group=None, **kw):
@@ -112,6 +113,76 @@ class RowPartitionedCsr:
             out[off:off + rows].copy_(everyone[p * self.max_rows: p * self.max_rows + rows])
             off += rows
         return out
+
+    # -- all-gather fused into the kernels: stores into every rank's buffer ------------------------
+    def enable_peer_gather(self, dtype, trailing=()):
+        """Allocate the assembled y / C in symmetric memory (one buffer per rank, each mapped
+        into every process so that kernels can store into it over NVLink).  Afterwards spmv() /
+        spmm() have their last kernel store this rank's block straight into all copies instead
+        of calling an all-gather.  Collective: every rank calls it with the same arguments.
+        Plain peer stores only: NVLink multicast is switched off for these buffers.
+
+        The caller owns the ordering between steps: a rank may start storing the next result as
+        soon as it has passed the end-of-step fence, so a consumer that reads the assembled
+        result asynchronously must finish (or call ``fence()``) before the next product."""
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        dev = self.data.device
+        full = symm.empty((self.n_rows, *trailing), dtype=dtype, device=dev)
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm.rendezvous(full, group)
+        offset = int(getattr(hdl, "offset", 0) or 0)
+        ptrs = [int(p) + offset for p in hdl.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != full.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe the buffer just made")
+        row_items = 1
+        for t in trailing:
+            row_items *= int(t)
+        self._peer = {
+            "full": full, "handle": hdl, "n": self.world,
+            "array": (ctypes.c_void_p * self.world)(*ptrs),
+            "flag": torch.zeros(1, dtype=torch.int32, device=dev),
+            "trailing": tuple(int(t) for t in trailing), "dtype": dtype,
+            "row_bytes": row_items * full.element_size(),
+        }
+        dist.barrier(group=self.group)
+        return full
+
+    def fence(self):
+        """Stream-ordered barrier across the ranks (a one-element all-reduce): when it has
+        completed here, every rank has finished the kernels it had enqueued before its own
+        fence, so all their stores into this rank's buffer have landed."""
+        dist.all_reduce(self._peer["flag"], group=self.group)
+
+    def _peer_spmv(self, x, out_local, alpha, beta):
+        from .spmv import prepare_spmv_csr, spmv_block_to_peers
+        peer = self._peer
+        blocks = self._stages or [(self.data, self.indices, self.indptr)]
+        h = self.n_local // len(blocks)
+        side = None
+        if len(blocks) > 1:
+            # the stores of block s drain on a second stream while block s+1 is multiplied
+            side = peer.get("side")
+            if side is None:
+                side = peer["side"] = torch.cuda.Stream(device=x.device)
+        for s, (d, i, p) in enumerate(blocks):
+            prepared = prepare_spmv_csr(d, i, p, (h, self.n_cols))
+            y_in = None if out_local is None else out_local[s * h:(s + 1) * h]
+            if len(blocks) == 1:
+                row_offset = self.row_offset
+            else:
+                row_offset = (s * self.world + self.rank) * h
+            if not spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array"], peer["n"],
+                                       row_offset, self.n_rows, store_stream=side):
+                if s == 0:
+                    return None
+                raise RuntimeError("row block cannot be stored to the peers")
+        if side is not None:
+            torch.cuda.current_stream(x.device).wait_stream(side)
+        self.fence()
+        return peer["full"]
 
     # -- pipelined variant: several row blocks per rank ------------------------------------------
     def split_stages(self, stages):
@@ -167,6 +238,12 @@ class RowPartitionedCsr:
         """y = alpha * A x + beta * y0 with x taken from rank `src`; y0 is this rank's block in
         out_local.  Returns the assembled y on every rank."""
         self.broadcast_dense(x, src)
+        peer = self._peer
+        if peer is not None and peer["trailing"] == () and peer["dtype"] == x.dtype \
+                and self.local_spmv is _default_local_spmv:
+            done = self._peer_spmv(x, out_local, alpha, beta)
+            if done is not None:
+                return done
         if getattr(self, "_stages", None):
             return self._pipelined(self.local_spmv, x, out_local, out, alpha, beta)
         y_local = self.spmv_local(x, out=out_local, alpha=alpha, beta=beta)
@@ -174,6 +251,23 @@ class RowPartitionedCsr:
 
     def spmm(self, B, src=0, out_local=None, out=None, alpha=1.0, beta=0.0):
         self.broadcast_dense(B, src)
+        peer = self._peer
+        if peer is not None and peer["trailing"] == tuple(B.shape[1:]) \
+                and peer["dtype"] == B.dtype and not self._stages:
+            from . import _lib
+            C_local = self.spmm_local(B, out=out_local, alpha=alpha, beta=beta)
+            row_bytes = peer["row_bytes"]
+            nbytes, offset = self.n_local * row_bytes, self.row_offset * row_bytes
+            if C_local.is_contiguous() and nbytes % 16 == 0 and offset % 16 == 0 \
+                    and C_local.data_ptr() % 16 == 0:
+                with torch.cuda.device(C_local.device):
+                    st = _lib.load().b2s_peer_scatter(
+                        _lib.ptr(C_local), nbytes, peer["array"], peer["n"], offset,
+                        self.n_rows * row_bytes, _lib.stream_handle(C_local.device))
+                _lib.check(st, "b2s_peer_scatter")
+                self.fence()
+                return peer["full"]
+            return self.gather_rows(C_local, out=out)
         if getattr(self, "_stages", None):
             return self._pipelined(self.local_spmm, B, out_local, out, alpha, beta)
         C_local = self.spmm_local(B, out=out_local, alpha=alpha, beta=beta)

@@ -303,6 +303,66 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
         plan.check_status()
 
 
+def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row_offset,
+                        peer_rows, store_stream=None):
+    """Several GPUs: multiply this rank's row block and store the result block at rows
+    [row_offset, row_offset + n_rows) of the y buffer (peer_rows rows) of every rank
+    (`peer_array`: ctypes array of the n_peers device pointers, own buffer included).  On the
+    column-panel layout the stores are issued by the combine kernel itself
+    (b2s_spmv_panels_peers); otherwise the block is computed into scratch and copied out by
+    b2s_peer_scatter.  Returns False, having done nothing, when the block cannot go this way
+    (on the scratch route its byte size or offset is not a multiple of 16); the caller then
+    falls back to a collective.
+
+    store_stream (a torch.cuda.Stream): on the panel layout, run the combine + store kernel on
+    that stream, ordered after this block's tile kernel by an event, so that the caller can go
+    on launching the next block on the current stream while the stores drain over NVLink."""
+    plan = prepared.plan()
+    lib = _lib.load()
+    fn, head, tile_row_p, n_tiles, lay, status_p = _spmv_launch_record(plan)
+    dtype = plan.data.dtype
+    itemsize = plan.data.element_size()
+    if row_offset < 0 or row_offset + plan.n_rows > peer_rows:
+        raise ValueError("row block does not fit the assembled result")
+    if lay is None and ((plan.n_rows * itemsize) % 16 or (row_offset * itemsize) % 16):
+        return False
+    a, b = _scalar(alpha, dtype), _scalar(beta, dtype)
+    with torch.cuda.device(plan.device):
+        stream = torch.cuda.current_stream(plan.device).cuda_stream
+        carry = plan.scratch_on("spmv_carry", n_tiles, stream)
+        if lay is not None and store_stream is not None:
+            ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
+            one, zero = _scalar(1.0, dtype), _scalar(0.0, dtype)
+            st = lib.b2s_spmv_panels(
+                *head, _lib.ptr(x), None, None, one, zero, tile_row_p, _lib.ptr(carry),
+                _lib.ptr(ypart), status_p, stream, lay.n_stacked, _lib.ptr(lay.subpos))
+            _lib.check(st, "b2s_spmv_panels")
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(plan.device))
+            store_stream.wait_event(done)
+            st = lib.b2s_panel_combine_peers(
+                plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows, lay.n_panels,
+                _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows, a, b,
+                store_stream.cuda_stream)
+            _lib.check(st, "b2s_panel_combine_peers")
+        elif lay is not None:
+            ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
+            st = lib.b2s_spmv_panels_peers(
+                *head, _lib.ptr(x), _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows,
+                a, b, tile_row_p, _lib.ptr(carry), _lib.ptr(ypart), status_p, stream,
+                lay.n_stacked, _lib.ptr(lay.subpos))
+            _lib.check(st, "b2s_spmv_panels_peers")
+        else:
+            tmp = plan.scratch_on("spmv_peer_block", plan.n_rows, stream)
+            st = fn(*head, _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(tmp), a, b, tile_row_p,
+                    _lib.ptr(carry), status_p, stream)
+            _lib.check(st, "b2s_spmv_csr")
+            st = lib.b2s_peer_scatter(_lib.ptr(tmp), plan.n_rows * itemsize, peer_array, n_peers,
+                                      row_offset * itemsize, peer_rows * itemsize, stream)
+            _lib.check(st, "b2s_peer_scatter")
+    return True
+
+
 def _b200_spmv_csr_impl_prepared(prepared, x, out=None, alpha=1.0, beta=0.0):
     plan = prepared.plan()
     dtype = plan.data.dtype

@@ -172,6 +172,40 @@ int b2s_spmv_panels(int val_type, int ptr_type,
                     int32_t* status_dev, b2s_stream stream,
                     int64_t n_stacked, const int32_t* subpos_dev);
 
+/* ---- all-gather fused into the last kernel (several GPUs, no counterpart in the reference) ----
+ * In a row-partitioned product every rank owns rows [row_offset, row_offset + n_rows) of the
+ * assembled y and every rank wants all of y.  peer_y is a HOST array of n_peers (<= 16) device
+ * pointers: the y buffer (peer_rows rows) of each rank, this rank's own included, as addresses
+ * that kernels of the current device may write (symmetric / peer-mapped memory).
+ * b2s_spmv_panels_peers is b2s_spmv_panels whose combine kernel stores each value into all of
+ * them (plain coalesced stores over NVLink) instead of into a local y; b2s_peer_scatter does the
+ * same for an already computed block of bytes (16-byte multiples; peer_bytes = size of each
+ * destination buffer), e.g. the C block of an SpMM.  Blocks that would not fit the destination
+ * are refused.  The caller orders the ranks afterwards (any barrier across the ranks after these
+ * kernels have finished); neither call waits for a peer.
+ */
+int b2s_spmv_panels_peers(int val_type, int ptr_type,
+                          const void* p_data_dev, const int32_t* p_cols_dev, const void* p_ptr_dev,
+                          int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels,
+                          int panel_shift, const int64_t* panel_start_dev,
+                          const void* x_dev, const void* y_in_dev,
+                          void* const* peer_y, int n_peers, int64_t row_offset, int64_t peer_rows,
+                          const void* alpha, const void* beta,
+                          const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
+                          int32_t* status_dev, b2s_stream stream,
+                          int64_t n_stacked, const int32_t* subpos_dev);
+int b2s_peer_scatter(const void* src_dev, int64_t bytes, void* const* peer_dst, int n_peers,
+                     int64_t dst_offset_bytes, int64_t peer_bytes, b2s_stream stream);
+/* The combine + store step alone: b2s_spmv_panels called with y_dev == NULL stops after the
+ * carries and leaves the per-panel partials in ypart_dev; this call adds them, applies alpha /
+ * beta and stores into the peers.  Split so that it can run on a second stream while the tile
+ * kernel of the next row block is already running. */
+int b2s_panel_combine_peers(int val_type, const void* ypart_dev, const int32_t* subpos_dev,
+                            int64_t n_rows, int n_panels, const void* y_in_dev,
+                            void* const* peer_y, int n_peers, int64_t row_offset,
+                            int64_t peer_rows, const void* alpha, const void* beta,
+                            b2s_stream stream);
+
 /* ---- SpMM ----------------------------------------------------------------------------------
  * C = alpha * A B + beta * C_in, B (n_cols x n_dense, leading dimension ldb) and
  * C (n_rows x n_dense, leading dimension ldc) row-major.  Replaces _spmm_csr_real_kernel

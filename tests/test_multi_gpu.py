@@ -37,11 +37,91 @@ def _worker(rank, world, port, results):
         C = part.spmm(B, src=0)
         single_C = flagsparse_spmm_csr(p.data, p.indices, p.indptr, p.B, p.shape)
         err_mm = float(torch.linalg.matrix_norm(C - single_C) / torch.linalg.matrix_norm(single_C))
+        # the same products with the all-gather fused into the last kernel (stores into every
+        # rank's symmetric-memory buffer over NVLink)
+        import flagsparse_b200._plan as plan_mod
+        from flagsparse_b200 import clear_plan_cache
+        y_full = part.enable_peer_gather(p.x.dtype)
+        y2 = part.spmv(x, src=0)                       # scratch route (x fits L2: no panels)
         torch.cuda.synchronize()
-        results[rank] = (err, err_mm, part.rows_per_rank)
+        dist.barrier()
+        same = bool(torch.equal(y2, y))
+        plan_mod.PANEL_TRIGGER_BYTES, plan_mod.PANEL_MIN_NNZ = 0, 0
+        plan_mod.PANEL_TARGET_BYTES = 4096 * 4
+        clear_plan_cache()
+        y3 = part.spmv(x, src=0).clone()               # panel route: the combine kernel stores
+        torch.cuda.synchronize()
+        dist.barrier()
+        used_peer = y3 is not None and part._peer is not None
+        err_panel = float(torch.linalg.vector_norm(y3 - single) / torch.linalg.vector_norm(single))
+        plan_mod.PANEL_POLICY = "off"
+        clear_plan_cache()
+        part_mm = RowPartitionedCsr.from_global(p.data, p.indices, p.indptr, p.shape)
+        C_full = part_mm.enable_peer_gather(p.B.dtype, trailing=(int(p.B.shape[1]),))
+        C2 = part_mm.spmm(B, src=0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        same_mm = bool(torch.equal(C2, C))
+        results[rank] = (err, err_mm, part.rows_per_rank, same, err_panel, same_mm,
+                         y2.data_ptr() == y_full.data_ptr(), C2.data_ptr() == C_full.data_ptr())
     finally:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _staged_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        import flagsparse_b200._plan as plan_mod
+        from flagsparse_b200 import flagsparse_spmv_csr, workloads
+        from flagsparse_b200.distributed import RowPartitionedCsr, slice_rows
+        plan_mod.PANEL_TRIGGER_BYTES, plan_mod.PANEL_MIN_NNZ = 0, 0
+        plan_mod.PANEL_TARGET_BYTES = 8192 * 8
+        p = workloads.cfg2_powerlaw_spmv(device="cuda", scale=128, seed=9)   # float64, 131072 rows
+        single = flagsparse_spmv_csr(p.data, p.indices, p.indptr, p.x, p.shape, alpha=1.5,
+                                     beta=0.5, out=p.y0.clone())
+        half = p.shape[0] // world
+        d, i, ptr = slice_rows(p.data, p.indices, p.indptr, rank * half, (rank + 1) * half)
+        y0_block = p.y0[rank * half:(rank + 1) * half].clone()
+        stages, h = 4, half // 4
+        expect = torch.cat([single[q * half + s * h: q * half + (s + 1) * h]
+                            for s in range(stages) for q in range(world)])
+        out = {}
+        for gather in ("nccl", "peer"):
+            part = RowPartitionedCsr(d.contiguous(), i.contiguous(), ptr.contiguous(), p.shape[1])
+            assert part.split_stages(stages)
+            if gather == "peer":
+                part.enable_peer_gather(p.x.dtype)
+            x = p.x.clone() if rank == 0 else torch.zeros_like(p.x)
+            y = part.spmv(x, src=0, out_local=y0_block.clone(), alpha=1.5, beta=0.5)
+            torch.cuda.synchronize()
+            dist.barrier()
+            out[gather] = float(torch.linalg.vector_norm(y - expect)
+                                / torch.linalg.vector_norm(expect))
+        results[rank] = out
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_block_cyclic_stages_with_nccl_and_with_peer_stores():
+    """Four row sub-blocks per rank (block-cyclic global order): the NCCL all-gather of one
+    stage overlapping the next kernel, and the combine kernel of one stage storing into the
+    peers' buffers on a second stream while the next stage is multiplied."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_staged_worker, args=(2, port, results), nprocs=2, join=True)
+        for rank in range(2):
+            assert results[rank]["nccl"] <= 1e-12 and results[rank]["peer"] <= 1e-12, results[rank]
 
 
 def test_two_nccl_ranks_match_single_gpu():
@@ -55,6 +135,9 @@ def test_two_nccl_ranks_match_single_gpu():
         results = manager.dict()
         mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
         for rank in range(2):
-            err, err_mm, rows = results[rank]
+            err, err_mm, rows, same, err_panel, same_mm, y_in_place, c_in_place = results[rank]
             assert err <= 1e-5 and err_mm <= 1e-5, (err, err_mm)   # float32 tolerance
+            assert same and same_mm, "peer-store gather differs from the NCCL all-gather"
+            assert err_panel <= 1e-5, err_panel
+            assert c_in_place, "SpMM result did not come back in the symmetric buffer"
             assert sum(rows) == (1 << 26) // 512
