@@ -422,8 +422,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
 
     staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
-    gather = args.gather
-    if gather == "peer":
+    gather_mode = args.gather
+    if gather_mode == "peer":
         # the last kernel of every rank stores its block into all ranks' result buffers; if
         # symmetric memory cannot be set up on any rank, every rank falls back to NCCL
         ok = torch.ones(1, dtype=torch.int32, device=device)
@@ -437,10 +437,10 @@ def run_multi_gpu(args, rank, world, local_rank, device):
             out_full = peer_full
         else:
             part._peer = None
-            gather = "nccl"
+            gather_mode = "nccl"
 
     def step():
-        if staged or gather == "peer":
+        if staged or gather_mode == "peer":
             # staged: the gather of stage s overlaps the kernel of stage s+1
             op(dense, src=0, out_local=out_local, out=out_full, alpha=alpha, beta=beta)
         else:
@@ -518,7 +518,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                        "seed": args.seed, "scale": args.scale,
                        "exchange": "NCCL broadcast of x/B from rank 0 + NCCL all-gather of y/C, "
                                    "both inside the timed step",
-                       "stages": args.stages if staged else 1, "gather": gather},
+                       "stages": args.stages if staged else 1, "gather": gather_mode},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
                          "peak_kind": peak_kind,
