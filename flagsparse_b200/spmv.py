@@ -420,9 +420,16 @@ def _spmv_prepared_with_int32_indices(prepared, reason):
         index_fallback_applied=True, index_fallback_reason=str(reason))
 
 
+def _triton_spmv_csr_impl_prepared(prepared, x, **kw):
+    """Name the reference's tests patch to force a launch failure
+    (tests/pytest/test_spmv_csr_accuracy.py:152-180); here it forwards to the B200 launch."""
+    return _b200_spmv_csr_impl_prepared(prepared, x, **kw)
+
+
 def _run_spmv_prepared(prepared, x, use_opt=False, opt_buckets=None, out=None, alpha=1.0,
                        beta=0.0):
-    return _b200_spmv_csr_impl_prepared(prepared, x, out=out, alpha=alpha, beta=beta)
+    # looked up by name at call time so that patching the module attribute takes effect
+    return _triton_spmv_csr_impl_prepared(prepared, x, out=out, alpha=alpha, beta=beta)
 
 
 def _run_spmv_prepared_with_fallback(prepared, x, use_opt=False, opt_buckets=None, out=None,
