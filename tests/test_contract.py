@@ -121,3 +121,42 @@ def test_install_rebinds_a_flagsparse_like_package():
     finally:
         for m in (root, ops, spmv, spmm):
             sys.modules.pop(m.__name__, None)
+
+
+def test_install_into_the_real_flagsparse_package_when_its_source_is_at_hand():
+    """Only where a FlagSparse checkout is reachable (FLAGSPARSE_SRC or the usual location):
+    install() rebinds the public names on the package and its submodules; uninstall() puts the
+    Triton implementations back."""
+    import importlib
+    import os
+    import sys
+
+    src = os.environ.get("FLAGSPARSE_SRC", "/root/reference/src")
+    if not os.path.isdir(os.path.join(src, "flagsparse")):
+        pytest.skip("no FlagSparse source tree here")
+    sys.path.insert(0, src)
+    try:
+        flagsparse = importlib.import_module("flagsparse")
+        ops = importlib.import_module("flagsparse.sparse_operations")
+        ref_spmv, ref_spmm = ops.flagsparse_spmv_csr, ops.flagsparse_spmm_csr
+        import flagsparse_b200
+        replaced = flagsparse_b200.install(flagsparse)
+        assert flagsparse.flagsparse_spmv_csr is flagsparse_b200.flagsparse_spmv_csr
+        assert ops.flagsparse_spmm_csr is flagsparse_b200.flagsparse_spmm_csr
+        assert ops.spmv_csr.flagsparse_spmv_csr is flagsparse_b200.flagsparse_spmv_csr
+        assert ops.spmm_csr.flagsparse_spmm_csr is flagsparse_b200.flagsparse_spmm_csr
+        # same signature prefix as the reference: every reference parameter, in order
+        import inspect
+        for ours, theirs in ((flagsparse_b200.flagsparse_spmv_csr, ref_spmv),
+                             (flagsparse_b200.flagsparse_spmm_csr, ref_spmm),
+                             (flagsparse_b200.prepare_spmv_csr, ops.prepare_spmv_csr)):
+            a = list(inspect.signature(ours).parameters.items())
+            b = list(inspect.signature(theirs).parameters.items())
+            assert [k for k, _ in a[:len(b)]] == [k for k, _ in b]
+            assert [v.default for _, v in a[:len(b)]] == [v.default for _, v in b]
+        flagsparse_b200.uninstall(replaced)
+        assert ops.flagsparse_spmv_csr is ref_spmv and ops.flagsparse_spmm_csr is ref_spmm
+    finally:
+        sys.path.remove(src)
+        for name in [m for m in sys.modules if m == "flagsparse" or m.startswith("flagsparse.")]:
+            sys.modules.pop(name, None)
