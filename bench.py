@@ -295,9 +295,11 @@ def time_e2e(p, kind, steps, warmup, depth=2):
 # -------------------------------------------------------------------------------------------------
 # CPU baseline: the oracle port on a bounded row slice
 # -------------------------------------------------------------------------------------------------
-def cpu_baseline(p, kind, target_seconds=12.0, max_nnz=40_000_000):
-    """Rows are independent, so the first rows of the matrix holding <= max_nnz entries stand in
-    for the whole: same x / B, same arithmetic, all host cores (OpenMP over rows)."""
+def cpu_sample(p, kind, max_nnz=40_000_000):
+    """A bounded CPU-side sample of the workload: rows are independent, so the first rows of the
+    matrix holding <= max_nnz entries stand in for the whole (same x / B, same arithmetic).
+    Returns (callable running the oracle once, algorithmic bytes of one run, description,
+    scipy callable or None)."""
     import numpy as np
 
     import oracle
@@ -305,8 +307,7 @@ def cpu_baseline(p, kind, target_seconds=12.0, max_nnz=40_000_000):
     op = p.extra.get("op", "non")
     ptr_all = p.indptr
     if op != "non":
-        # the transposed product is timed on the reference's route: materialise op(A) first
-        n_slice = p.shape[0]
+        n_slice = p.shape[0]  # the transposed product needs every row of A
     else:
         n_slice = int(torch.searchsorted(ptr_all.long(), torch.tensor(
             [max_nnz], device=ptr_all.device), right=True).item()) - 1
@@ -328,6 +329,26 @@ def cpu_baseline(p, kind, target_seconds=12.0, max_nnz=40_000_000):
         dense = p.B.cpu().numpy()
         fn = lambda: oracle.spmm_acc(data, idx, ptr, dense, shape)  # noqa: E731
         nbytes = W.spmm_bytes(n_out, n_in, nnz_s, dense.shape[1], vb, ib, pb, False)
+    scipy_fn = None
+    try:
+        import scipy.sparse as sp
+        A = sp.csr_matrix((data, idx, ptr), shape=shape)
+        scipy_fn = lambda: A @ dense  # noqa: E731
+    except Exception:
+        pass
+    text = (f"first {n_slice} rows ({nnz_s} non-zeros) of the same matrix, full x/B, "
+            "oracle/csr_oracle.c (OpenMP over rows)")
+    return fn, nbytes, text, scipy_fn
+
+
+def host_cores():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
+
+
+def cpu_baseline(p, kind, target_seconds=12.0):
+    """The oracle port timed on the sample for about target_seconds (best run), plus scipy's
+    single-threaded CSR product on the same sample."""
+    fn, nbytes, text, scipy_fn = cpu_sample(p, kind)
     fn()  # warm the caches and the thread pool
     reps, t_total, best = 0, 0.0, float("inf")
     while reps < 3 or (t_total < target_seconds and reps < 200):
@@ -337,49 +358,45 @@ def cpu_baseline(p, kind, target_seconds=12.0, max_nnz=40_000_000):
         best = min(best, dt)
         t_total += dt
         reps += 1
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
     scipy_gbs = None
-    try:
-        import scipy.sparse as sp
-        A = sp.csr_matrix((data, idx, ptr), shape=shape)
+    if scipy_fn is not None:
         t0 = time.perf_counter()
         for _ in range(3):
-            A @ dense
+            scipy_fn()
         scipy_gbs = nbytes / ((time.perf_counter() - t0) / 3) / 1e9
-    except Exception:
-        pass
     return {
-        "value": nbytes / best / 1e9,
-        "unit": "GB/s",
-        "cores": cores,
-        "kind": "port",
-        "sample": f"first {n_slice} rows ({nnz_s} non-zeros) of the same matrix, full x/B, "
-                  f"best of {reps} runs of oracle/csr_oracle.c (OpenMP over rows)",
-        "scipy_1core_gbs": scipy_gbs,
+        "value": nbytes / best / 1e9, "unit": "GB/s", "cores": host_cores(), "kind": "port",
+        "sample": text + f", best of {reps} runs", "scipy_1core_gbs": scipy_gbs,
     }
 
 
 # -------------------------------------------------------------------------------------------------
 def run_reference_arm(args, rank, world):
     """The reference has no CPU implementation of this path (its functions reject CPU tensors
-    and its kernels are Triton); the arm times the CPU restatement of its arithmetic."""
+    and its kernels are Triton); the arm times the CPU restatement of its arithmetic, one run of
+    the bounded sample per step, all host threads."""
     if rank != 0:
         return
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     p, kind = make_problem(args.workload, dev, args.scale, args.seed)
-    samples = []
-    base = None
-    for _ in range(max(1, args.warmup) + max(1, args.steps)):
-        base = cpu_baseline(p, kind, target_seconds=2.0)
-        samples.append(base["value"])
-    samples = samples[max(1, args.warmup):]
-    value = statistics.median(samples)
-    base["value"] = value
+    fn, nbytes, text, _ = cpu_sample(p, kind)
+    for _ in range(max(1, args.warmup)):
+        fn()
+    times = []
+    for _ in range(max(1, args.steps)):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    per_step = statistics.median(times)
+    value = nbytes / per_step / 1e9
+    base = {"value": value, "unit": "GB/s", "cores": host_cores(), "kind": "port",
+            "sample": text + f", median of {len(times)} runs"}
     line = {
         "impl": "reference", "metric": "effective HBM GB/s (algorithmic bytes / time)",
         "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype], "data": "synthetic",
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype],
+        "data": "synthetic",
         "config": {"workload": WORKLOAD_TEXT[args.workload], "rows": p.shape[0], "nnz": p.nnz},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0,

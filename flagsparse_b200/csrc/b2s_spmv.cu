@@ -35,6 +35,9 @@ namespace b2s {
 #ifndef B2S_SPMV_DIRECT
 #define B2S_SPMV_DIRECT 1  // 1: col / val straight from global memory; 0: staged by bulk copies
 #endif
+#ifndef B2S_SPMV_PREFETCH_AHEAD
+#define B2S_SPMV_PREFETCH_AHEAD 0  // tiles ahead whose col / val are prefetched into L2 (0 = off)
+#endif
 #ifndef B2S_SPMV_UNROLL
 #define B2S_SPMV_UNROLL 8
 #endif
@@ -137,6 +140,29 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     // flight before the gathers; measured cheaper for the load/store pipe than staging them
     // (bulk-copy fills of shared memory and the re-reads count against the same data pipe)
     prod_w = reinterpret_cast<V*>(val_buf);
+#if B2S_SPMV_PREFETCH_AHEAD > 0
+    // pull the col / val range of the tile that will run in this CTA's slot one wave from now
+    // into L2, so that its loads find them there instead of waiting on DRAM
+    {
+      const int64_t ta = t + B2S_SPMV_PREFETCH_AHEAD;
+      if (ta < static_cast<int64_t>(gridDim.x)) {
+        const int64_t total = n_rows + nnz;
+        int64_t da = ta * static_cast<int64_t>(ITEMS);
+        if (da > total) da = total;
+        const int64_t ja = da - tile_row[ta];
+        int64_t na = nnz - ja;
+        if (na > ITEMS) na = ITEMS;
+        const char* pc = reinterpret_cast<const char*>(col + ja);
+        const char* pv = reinterpret_cast<const char*>(val + ja);
+        const int64_t bc = na * static_cast<int64_t>(sizeof(I));
+        const int64_t bv = na * static_cast<int64_t>(sizeof(V));
+        for (int64_t o = tid * 128LL; o < bc; o += THREADS * 128LL)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + o));
+        for (int64_t o = tid * 128LL; o < bv; o += THREADS * 128LL)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(pv + o));
+      }
+    }
+#endif
     for (int k = tid; k < n_end; k += THREADS)
       row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
     if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
