@@ -405,6 +405,28 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def gather_ceiling(device, spmv_gathers_per_s):
+    """The rate of divergent 8-byte gathers from an L2-resident array (32 MB, 2^26 random
+    indices), measured with the library's probe kernel: the bound the x gather of SpMV runs
+    against when the column indices have no locality."""
+    from flagsparse_b200 import _lib
+    lib = _lib.load()
+    n, n_x = 1 << 26, 1 << 22
+    idx = torch.randint(0, n_x, (n,), dtype=torch.int32, device=device)
+    x = torch.zeros(n_x, dtype=torch.float64, device=device)
+    sink = torch.zeros(1, dtype=torch.float64, device=device)
+    stream = torch.cuda.current_stream(device)
+
+    def launch():
+        _lib.check(lib.b2s_probe_gather(idx.data_ptr(), n, x.data_ptr(), n_x, sink.data_ptr(),
+                                        stream.cuda_stream), "b2s_probe_gather")
+
+    per = time_device(launch, 10, 3) / 10
+    rate = n / per
+    return {"ggathers_per_s": rate / 1e9, "spmv_ggathers_per_s": spmv_gathers_per_s / 1e9,
+            "frac": spmv_gathers_per_s / rate, "x_bytes": n_x * 8, "gathers": n}
+
+
 def run_multi_gpu(args, rank, world, local_rank, device):
     """Weak scaling over the GPUs of one node: rank r owns the r-th row block, a matrix of the
     single-GPU workload's size drawn with seed + r; the global matrix is (world * rows) x cols.
@@ -636,6 +658,9 @@ def main():
         p.extra["alpha"], p.extra["beta"] = saved
         del p.extra["B"], mm_out
         torch.cuda.empty_cache()
+
+    if kind == "spmv" and not args.no_extra:
+        extra["gather_ceiling"] = gather_ceiling(device, p.nnz / per_step)
 
     if nbytes < 1e9:
         # small problems are bound by launch latency: the same products replayed from a CUDA

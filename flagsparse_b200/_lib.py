@@ -33,6 +33,7 @@ SIGNATURES = {
     "b2s_status_string": (c_char_p, [c_int]),
     "b2s_tune": (c_int, [c_int, c_int64]),
     "b2s_selftest_wait_timeout": (c_int, [c_void_p, c_int, c_void_p]),
+    "b2s_probe_gather": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     "b2s_csr_inspect": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p,
                                 c_void_p]),
     "b2s_tile_count": (c_int64, [c_int64, c_int64, c_int]),

@@ -61,6 +61,14 @@ int b2s_tune(int knob, int64_t value);
  * returns normally -- the behaviour every bounded wait in the library has when a copy is lost. */
 int b2s_selftest_wait_timeout(int32_t* status_dev, int spin_limit, b2s_stream stream);
 
+/* Measurement aid (no counterpart in the reference): n divergent 8-byte gathers x[idx[i]] and
+ * nothing else -- idx read coalesced, eight gathers per thread in flight, sums discarded.  Timed
+ * by the caller over an L2-resident x it gives the ceiling the SpMV gather of x runs against
+ * (one gather per clock per SM on B200).  idx values must lie in [0, n_x); *sink_dev (one
+ * double) is written only if a sum takes a value it cannot take. */
+int b2s_probe_gather(const int32_t* idx_dev, int64_t n, const double* x_dev, int64_t n_x,
+                     double* sink_dev, b2s_stream stream);
+
 /* ---- input contract ------------------------------------------------------------------------
  * Replaces the device reductions behind the `.item()` checks of _prepare_spmv_csr_matrix
  * (spmv_csr.py:546-563) and _prepare_spmm_csr_matrix (spmm_csr.py:268-296).  One pass over
