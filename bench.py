@@ -461,6 +461,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
 
     if args.stages <= 0:
         args.stages = 1 if world < 4 else 2
+    if args.store_ctas >= 0:
+        part.peer_store_ctas = args.store_ctas
     staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
     gather_mode = args.gather
@@ -559,7 +561,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                        "seed": args.seed, "scale": args.scale,
                        "exchange": "NCCL broadcast of x/B from rank 0 + NCCL all-gather of y/C, "
                                    "both inside the timed step",
-                       "stages": args.stages if staged else 1, "gather": gather_mode},
+                       "stages": args.stages if staged else 1, "gather": gather_mode,
+                       "store_ctas": part.peer_store_ctas},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
                          "peak_kind": peak_kind,
@@ -587,6 +590,10 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOAD_TEXT))
     ap.add_argument("--scale", type=int, default=1, help="divide the row count (debugging)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--store-ctas", type=int, default=-1,
+                    help="several GPUs, peer gather with stages: CTAs of the combine + store "
+                         "kernel that runs beside the next stage (-1 = library default, "
+                         "0 = one thread per row)")
     ap.add_argument("--stages", type=int, default=0,
                     help="N > 1: row sub-blocks per rank; the gather of one overlaps the kernel "
                          "of the next (1 = no overlap; 0 = 1 below four GPUs, 2 from four on: "

@@ -62,7 +62,7 @@ SIGNATURES = {
                                       c_int64, c_void_p]),
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
-                                        c_void_p]),
+                                        c_int, c_void_p]),
     "b2s_peer_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64,
                                  c_void_p]),
     "b2s_panel_compact_bytes": (c_int64, [c_int64]),

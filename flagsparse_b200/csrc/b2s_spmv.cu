@@ -495,20 +495,25 @@ __global__ void panel_combine_peers_kernel(const V* __restrict__ ypart,
                                            int n_panels, const V* y_in, PeerList peers,
                                            int n_peers, int64_t row_offset, V alpha, V beta,
                                            int has_beta) {
-  const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-  if (r >= n_rows) return;
-  V s = vt<V>::zero();
-  for (int p = 0; p < n_panels; ++p) {
-    if (subpos != nullptr) {
-      const int32_t c = subpos[p * n_rows + r];
-      if (c >= 0) s = s + ypart[c];
-    } else {
-      s = s + ypart[p * n_rows + r];
+  // grid-stride: with one thread per row the loop runs once; a small grid (grid_limit of the
+  // entry point) keeps the kernel to a few CTAs per SM so that it can drain over NVLink beside
+  // the tile kernel of the next row block instead of filling the GPU with stalled stores
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < n_rows;
+       r += stride) {
+    V s = vt<V>::zero();
+    for (int p = 0; p < n_panels; ++p) {
+      if (subpos != nullptr) {
+        const int32_t c = subpos[p * n_rows + r];
+        if (c >= 0) s = s + ypart[c];
+      } else {
+        s = s + ypart[p * n_rows + r];
+      }
     }
+    V out = alpha * s;
+    if (has_beta) out = out + beta * y_in[r];
+    for (int q = 0; q < n_peers; ++q) static_cast<V*>(peers.p[q])[row_offset + r] = out;
   }
-  V out = alpha * s;
-  if (has_beta) out = out + beta * y_in[r];
-  for (int q = 0; q < n_peers; ++q) static_cast<V*>(peers.p[q])[row_offset + r] = out;
 }
 
 // Plain block of bytes to the same offset of every peer buffer (16-byte vectors, grid-stride).
@@ -668,8 +673,9 @@ extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
                                        const int32_t* subpos_dev, int64_t n_rows, int n_panels,
                                        const void* y_in_dev, void* const* peer_y, int n_peers,
                                        int64_t row_offset, int64_t peer_rows, const void* alpha,
-                                       const void* beta, b2s_stream stream) {
-  if (n_rows < 0 || row_offset < 0 || n_panels < 1 || n_panels > 256 || !alpha || !beta)
+                                       const void* beta, int grid_limit, b2s_stream stream) {
+  if (n_rows < 0 || row_offset < 0 || n_panels < 1 || n_panels > 256 || !alpha || !beta ||
+      grid_limit < 0)
     return B2S_ERR_ARG;
   if (row_offset + n_rows > peer_rows) return B2S_ERR_ARG;
   if (n_rows == 0) return B2S_OK;
@@ -681,7 +687,9 @@ extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
   if (pst != B2S_OK) return pst;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = 256;
-  const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
+  int64_t want = (n_rows + threads - 1) / threads;
+  if (grid_limit > 0 && want > grid_limit) want = grid_limit;
+  const unsigned grid = static_cast<unsigned>(want);
   B2S_DISPATCH_V(val_type, {
     const V a = *static_cast<const V*>(alpha);
     const V b = *static_cast<const V*>(beta);

@@ -69,6 +69,9 @@ class RowPartitionedCsr:
         self._pads = {}
         self._stages = None
         self._peer = None
+        # CTAs (of 256 threads) of a combine + store kernel that drains beside the tile kernel
+        # of the next stage; 0 = one thread per row
+        self.peer_store_ctas = 2 * 148
 
     @classmethod
     def from_global(cls, data, indices, indptr, shape, group=None, **kw):
@@ -164,9 +167,11 @@ class RowPartitionedCsr:
         side = None
         if len(blocks) > 1:
             # the stores of block s drain on a second stream while block s+1 is multiplied
+            # (high priority: its few CTAs take the next free slots of the SMs instead of
+            # queueing behind every CTA of the tile kernel launched after them)
             side = peer.get("side")
             if side is None:
-                side = peer["side"] = torch.cuda.Stream(device=x.device)
+                side = peer["side"] = torch.cuda.Stream(device=x.device, priority=-1)
         for s, (d, i, p) in enumerate(blocks):
             prepared = prepare_spmv_csr(d, i, p, (h, self.n_cols))
             y_in = None if out_local is None else out_local[s * h:(s + 1) * h]
@@ -174,8 +179,10 @@ class RowPartitionedCsr:
                 row_offset = self.row_offset
             else:
                 row_offset = (s * self.world + self.rank) * h
+            last = s + 1 == len(blocks)
             if not spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array"], peer["n"],
-                                       row_offset, self.n_rows, store_stream=side):
+                                       row_offset, self.n_rows, store_stream=side,
+                                       store_ctas=0 if last else self.peer_store_ctas):
                 if s == 0:
                     return None
                 raise RuntimeError("row block cannot be stored to the peers")

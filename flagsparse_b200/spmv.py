@@ -304,7 +304,7 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
 
 
 def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row_offset,
-                        peer_rows, store_stream=None):
+                        peer_rows, store_stream=None, store_ctas=0):
     """Several GPUs: multiply this rank's row block and store the result block at rows
     [row_offset, row_offset + n_rows) of the y buffer (peer_rows rows) of every rank
     (`peer_array`: ctypes array of the n_peers device pointers, own buffer included).  On the
@@ -316,7 +316,9 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
 
     store_stream (a torch.cuda.Stream): on the panel layout, run the combine + store kernel on
     that stream, ordered after this block's tile kernel by an event, so that the caller can go
-    on launching the next block on the current stream while the stores drain over NVLink."""
+    on launching the next block on the current stream while the stores drain over NVLink.
+    store_ctas > 0 caps that kernel's grid (CTAs of 256 threads); together with a high-priority
+    store_stream a small grid runs beside the next block's tile kernel."""
     plan = prepared.plan()
     lib = _lib.load()
     fn, head, tile_row_p, n_tiles, lay, status_p = _spmv_launch_record(plan)
@@ -343,7 +345,7 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
             st = lib.b2s_panel_combine_peers(
                 plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows, lay.n_panels,
                 _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows, a, b,
-                store_stream.cuda_stream)
+                int(store_ctas), store_stream.cuda_stream)
             _lib.check(st, "b2s_panel_combine_peers")
         elif lay is not None:
             ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)

@@ -207,12 +207,15 @@ int b2s_peer_scatter(const void* src_dev, int64_t bytes, void* const* peer_dst, 
 /* The combine + store step alone: b2s_spmv_panels called with y_dev == NULL stops after the
  * carries and leaves the per-panel partials in ypart_dev; this call adds them, applies alpha /
  * beta and stores into the peers.  Split so that it can run on a second stream while the tile
- * kernel of the next row block is already running. */
+ * kernel of the next row block is already running.  grid_limit > 0 caps the number of CTAs
+ * (256 threads each, grid-stride over the rows): on a high-priority stream a few CTAs per SM
+ * drain over NVLink beside the other kernel instead of occupying every free slot with stores
+ * that wait for the link; 0 = one thread per row. */
 int b2s_panel_combine_peers(int val_type, const void* ypart_dev, const int32_t* subpos_dev,
                             int64_t n_rows, int n_panels, const void* y_in_dev,
                             void* const* peer_y, int n_peers, int64_t row_offset,
                             int64_t peer_rows, const void* alpha, const void* beta,
-                            b2s_stream stream);
+                            int grid_limit, b2s_stream stream);
 
 /* ---- SpMM ----------------------------------------------------------------------------------
  * C = alpha * A B + beta * C_in, B (n_cols x n_dense, leading dimension ldb) and
