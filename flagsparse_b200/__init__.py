@@ -22,6 +22,14 @@ from .spmm import (
     flagsparse_spmm_csr,
     spmm_csr,
 )
+from .spmm_route import (
+    PreparedCsrSpmmRoute,
+    SpmmCsrAlgorithmUnavailable,
+    flagsparse_spmm_csr_run,
+    list_spmm_csr_algorithms,
+    prepare_spmm_csr_route,
+    resolve_spmm_csr_algorithm,
+)
 from .spmv import (
     SPMV_OP_CONJ_TRANS,
     SPMV_OP_NON,
@@ -45,6 +53,12 @@ __all__ = [
     "PreparedCsrSpmv",
     "spmv_csr",
     "spmm_csr",
+    "prepare_spmm_csr_route",
+    "flagsparse_spmm_csr_run",
+    "PreparedCsrSpmmRoute",
+    "SpmmCsrAlgorithmUnavailable",
+    "list_spmm_csr_algorithms",
+    "resolve_spmm_csr_algorithm",
     "flagsparse_spmv_coo_tocsr",
     "prepare_spmv_coo_tocsr",
     "coo_to_csr_for_spmv",
@@ -60,7 +74,8 @@ __all__ = [
 ]
 
 _PATCHED_NAMES = ("flagsparse_spmv_csr", "flagsparse_spmm_csr", "prepare_spmv_csr",
-                  "PreparedCsrSpmv")
+                  "PreparedCsrSpmv", "prepare_spmm_csr_route", "flagsparse_spmm_csr_run",
+                  "PreparedCsrSpmmRoute")
 
 
 def install(flagsparse_module=None):
@@ -69,8 +84,8 @@ def install(flagsparse_module=None):
     FlagSparse resolves its public names lazily from ``flagsparse.sparse_operations``
     (src/flagsparse/__init__.py:247-254) and imports them eagerly into that subpackage
     (sparse_operations/__init__.py:36-72); there is no plugin registry.  This function sets
-    the four names on ``flagsparse``, ``flagsparse.sparse_operations`` and the ``spmv_csr`` /
-    ``spmm_csr`` submodules.  Returns a dict of the objects it replaced (pass it to
+    the names of ``_PATCHED_NAMES`` on ``flagsparse``, ``flagsparse.sparse_operations`` and the
+    ``spmv_csr`` / ``spmm_csr`` submodules.  Returns a dict of the objects it replaced (pass it to
     ``uninstall``).
     """
     import importlib

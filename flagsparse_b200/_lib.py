@@ -63,6 +63,8 @@ SIGNATURES = {
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_int, c_void_p]),
+    "b2s_dense_transpose": (c_int, [c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                    c_void_p]),
     "b2s_peer_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64,
                                  c_void_p]),
     "b2s_panel_compact_bytes": (c_int64, [c_int64]),

@@ -483,3 +483,66 @@ extern "C" int b2s_csr2csc(int val_type, int idx_type, int ptr_type, const void*
   })));
   return B2S_ERR_DTYPE;
 }
+
+// =================================================================================================
+// Dense transpose (column-major B / C around the row-major SpMM kernel)
+// =================================================================================================
+namespace b2s {
+
+// dst[c * ld_dst + r] = src[r * ld_src + c] for a rows x cols matrix.  32 x 32 tiles through
+// padded shared memory: 32 consecutive elements of a source row are read by one warp and 32
+// consecutive elements of a destination row are written by one warp.  One-dimensional grid over
+// the tiles (tile rows can exceed the 65,535 limit of the other grid dimensions).
+template <class T>
+__global__ void __launch_bounds__(256)
+    dense_transpose_kernel(const T* __restrict__ src, int64_t rows, int64_t cols, int64_t ld_src,
+                           T* __restrict__ dst, int64_t ld_dst, int64_t tiles_x) {
+  __shared__ T tile[32][33];
+  const int64_t t = blockIdx.x;
+  const int64_t r0 = (t / tiles_x) * 32;
+  const int64_t c0 = (t % tiles_x) * 32;
+  const int tx = threadIdx.x & 31;
+  const int ty = threadIdx.x >> 5;  // 0..7
+#pragma unroll
+  for (int k = 0; k < 32; k += 8) {
+    const int64_t r = r0 + ty + k, c = c0 + tx;
+    if (r < rows && c < cols) tile[ty + k][tx] = src[r * ld_src + c];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 32; k += 8) {
+    const int64_t c = c0 + ty + k, r = r0 + tx;
+    if (r < rows && c < cols) dst[c * ld_dst + r] = tile[tx][ty + k];
+  }
+}
+
+template <class T>
+int dense_transpose_launch(const void* src, int64_t rows, int64_t cols, int64_t ld_src, void* dst,
+                           int64_t ld_dst, cudaStream_t s) {
+  const int64_t tiles_x = (cols + 31) / 32, tiles_y = (rows + 31) / 32;
+  const int64_t tiles = tiles_x * tiles_y;
+  if (tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
+  dense_transpose_kernel<T><<<static_cast<unsigned>(tiles), 256, 0, s>>>(
+      static_cast<const T*>(src), rows, cols, ld_src, static_cast<T*>(dst), ld_dst, tiles_x);
+  return launch_status();
+}
+
+}  // namespace b2s
+
+extern "C" int b2s_dense_transpose(int elem_bytes, const void* src_dev, int64_t rows, int64_t cols,
+                                   int64_t ld_src, void* dst_dev, int64_t ld_dst,
+                                   b2s_stream stream) {
+  if (rows < 0 || cols < 0 || ld_src < cols || ld_dst < rows) return B2S_ERR_ARG;
+  if (rows == 0 || cols == 0) return B2S_OK;
+  if (!src_dev || !dst_dev) return B2S_ERR_ARG;
+  if (elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16) return B2S_ERR_DTYPE;
+  const uintptr_t both =
+      reinterpret_cast<uintptr_t>(src_dev) | reinterpret_cast<uintptr_t>(dst_dev);
+  if (both % static_cast<uintptr_t>(elem_bytes)) return B2S_ERR_ALIGNMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (elem_bytes == 4)
+    return b2s::dense_transpose_launch<uint32_t>(src_dev, rows, cols, ld_src, dst_dev, ld_dst, s);
+  if (elem_bytes == 8)
+    return b2s::dense_transpose_launch<uint64_t>(src_dev, rows, cols, ld_src, dst_dev, ld_dst, s);
+  return b2s::dense_transpose_launch<uint4>(src_dev, rows, cols, ld_src, dst_dev, ld_dst, s);
+}

@@ -217,6 +217,16 @@ int b2s_panel_combine_peers(int val_type, const void* ypart_dev, const int32_t* 
                             int64_t peer_rows, const void* alpha, const void* beta,
                             int grid_limit, b2s_stream stream);
 
+/* ---- dense transpose ---------------------------------------------------------------------------
+ * dst[c * ld_dst + r] = src[r * ld_src + c] for a rows x cols matrix of 4-, 8- or 16-byte
+ * elements.  Serves dense_layout="col" of the prepared SpMM route (_run_spmm_csr_base_route,
+ * spmm_csr.py:713-788, with _materialize_dense_layout :617-627): a column-major B is turned
+ * into the row-major operand the SpMM kernel gathers whole rows from, and the row-major result
+ * into the column-major C the caller gets.  (The reference instead hands its kernel the two
+ * strides of B and C and gathers single elements.) */
+int b2s_dense_transpose(int elem_bytes, const void* src_dev, int64_t rows, int64_t cols,
+                        int64_t ld_src, void* dst_dev, int64_t ld_dst, b2s_stream stream);
+
 /* ---- SpMM ----------------------------------------------------------------------------------
  * C = alpha * A B + beta * C_in, B (n_cols x n_dense, leading dimension ldb) and
  * C (n_rows x n_dense, leading dimension ldc) row-major.  Replaces _spmm_csr_real_kernel

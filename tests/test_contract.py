@@ -149,14 +149,70 @@ def test_install_into_the_real_flagsparse_package_when_its_source_is_at_hand():
         import inspect
         for ours, theirs in ((flagsparse_b200.flagsparse_spmv_csr, ref_spmv),
                              (flagsparse_b200.flagsparse_spmm_csr, ref_spmm),
-                             (flagsparse_b200.prepare_spmv_csr, ops.prepare_spmv_csr)):
+                             (flagsparse_b200.prepare_spmv_csr, ops.prepare_spmv_csr),
+                             (flagsparse_b200.prepare_spmm_csr_route, ops.prepare_spmm_csr_route),
+                             (flagsparse_b200.flagsparse_spmm_csr_run,
+                              ops.flagsparse_spmm_csr_run)):
             a = list(inspect.signature(ours).parameters.items())
             b = list(inspect.signature(theirs).parameters.items())
             assert [k for k, _ in a[:len(b)]] == [k for k, _ in b]
             assert [v.default for _, v in a[:len(b)]] == [v.default for _, v in b]
+            assert [v.kind for _, v in a[:len(b)]] == [v.kind for _, v in b]
+        # the route registry answers the same questions as the reference's
+        import torch
+        for dtype in (torch.float32, torch.float64, torch.complex64, torch.complex128):
+            assert (flagsparse_b200.list_spmm_csr_algorithms(dtype=dtype)
+                    == ops.spmm_csr.list_spmm_csr_algorithms(dtype=dtype))
+        for token in ("base", "CSR", " alg1 ", "csr_alg2", "auto", None):
+            from flagsparse_b200 import spmm_route
+            assert (spmm_route._normalize_spmm_csr_alg(token)
+                    == ops.spmm_csr._normalize_spmm_csr_alg(token))
+        for token in ("auto", None, "Row-Major", "F", "fortran", "column", "c_order"):
+            assert (spmm_route._normalize_dense_layout(token)
+                    == ops.spmm_csr._normalize_dense_layout(token))
+        assert issubclass(flagsparse_b200.SpmmCsrAlgorithmUnavailable, RuntimeError)
         flagsparse_b200.uninstall(replaced)
         assert ops.flagsparse_spmv_csr is ref_spmv and ops.flagsparse_spmm_csr is ref_spmm
     finally:
         sys.path.remove(src)
         for name in [m for m in sys.modules if m == "flagsparse" or m.startswith("flagsparse.")]:
             sys.modules.pop(name, None)
+
+
+def test_route_names_layouts_and_registry_without_a_gpu():
+    """The route API's name handling (spmm_csr.py:571-639, :2012-2037): aliases, "auto",
+    unknown names, the dtypes each route is registered for, dense-layout spellings."""
+    import torch
+
+    import flagsparse_b200 as fb
+    from flagsparse_b200 import spmm_route as R
+
+    assert R._normalize_spmm_csr_alg(None) == "auto"
+    assert R._normalize_spmm_csr_alg(" Base ") == "csr_base"
+    assert R._normalize_spmm_csr_alg("ALG1") == "spmm_csr_alg1"
+    assert R._normalize_spmm_csr_alg("csr_alg2") == "spmm_csr_alg2"
+    assert fb.resolve_spmm_csr_algorithm("auto", "non", torch.complex64) == "csr_base"
+    assert fb.resolve_spmm_csr_algorithm("alg2", 1, torch.float64) == "spmm_csr_alg2"
+    with pytest.raises(ValueError, match="unsupported CSR SpMM algorithm"):
+        fb.resolve_spmm_csr_algorithm("fastest", "non", torch.float32)
+    with pytest.raises(TypeError, match="does not support dtype"):
+        fb.resolve_spmm_csr_algorithm("alg1", "non", torch.complex128)
+    with pytest.raises(ValueError):
+        fb.resolve_spmm_csr_algorithm("base", "upside-down", torch.float32)
+    assert fb.list_spmm_csr_algorithms() == ("csr_base", "alpha_alg1_tle_opt",
+                                             "alpha_alg1_tle_opt2", "spmm_csr_alg1",
+                                             "spmm_csr_alg2")
+    assert fb.list_spmm_csr_algorithms(op="conj", dtype=torch.complex64) == ("csr_base",)
+    for token in (None, "auto", "default", "row", "Row_Major", "C", "c_order"):
+        assert R._normalize_dense_layout(token) == "row"
+    for token in ("col", "COLUMN", "col-major", "column_major", "f", "Fortran"):
+        assert R._normalize_dense_layout(token) == "col"
+    with pytest.raises(ValueError, match="dense_layout"):
+        R._normalize_dense_layout("tiled")
+    with pytest.raises(TypeError, match="PreparedCsrSpmmRoute"):
+        fb.flagsparse_spmm_csr_run("not a handle", torch.zeros(2, 2))
+    t = torch.zeros(6, 4)
+    assert R._dense_layout_name(t) == "row" and R._dense_layout_name(t.t()) == "col"
+    assert R._dense_layout_name(t[:, ::2]) == "strided" and R._dense_layout_name(t[0]) == "unknown"
+    c = R._empty_col_major(5, 3, torch.float32, "cpu")
+    assert c.shape == (5, 3) and c.stride() == (1, 5) and R._is_col_major_2d(c)
