@@ -179,6 +179,15 @@ def problem_bytes_flops(p, kind):
     return b, f
 
 
+def gathered_bytes(p, kind, nbytes):
+    """Secondary diagnostic: the algorithmic bytes with the `x / B read once` term replaced by
+    what the SMs pull through L1 / L2, one value (SpMV) or one row of B (SpMM) per non-zero."""
+    vb = p.data.element_size()
+    n_in = p.shape[0] if p.extra.get("op", "non") != "non" else p.shape[1]
+    n = 1 if kind == "spmv" else int(p.B.shape[1])
+    return nbytes - n_in * n * vb + p.nnz * n * vb
+
+
 def make_step(p, kind):
     """Returns (step callable, output tensor, kernels launched per step)."""
     from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr
@@ -201,16 +210,21 @@ def make_step(p, kind):
     return step, out, 2  # tile kernel + carry fix-up kernel (+ panel combine, see main)
 
 
-def uses_panels(p, kind):
-    """True when the SpMV of this problem runs on the column-panel layout (one more launch)."""
-    if kind != "spmv":
-        return False
+def extra_launches(p, kind):
+    """Kernels per step beyond the tile kernel and the carry fix-up: 1 when the SpMV runs on the
+    column-panel layout (panel combine), 3 when the SpMM splits the long rows off (a second tile
+    kernel and fix-up for the panel stack, and the combine)."""
     from flagsparse_b200 import _plan
-    key = _plan.plan_key("spmv", p.data, p.indices, p.indptr, p.shape)
+    key = _plan.plan_key(kind, p.data, p.indices, p.indptr, p.shape)
     plan = _plan.cache_get(key)
-    if plan is not None and p.extra.get("op", "non") != "non":
+    if plan is None:
+        return 0
+    if p.extra.get("op", "non") != "non":
         plan = plan.transposed(conj=p.extra.get("op") == "conj")
-    return bool(plan is not None and plan.panels() is not None)
+    if kind == "spmv":
+        return 1 if plan.panels() is not None else 0
+    row_bytes = int(p.B.shape[1]) * p.B.element_size()
+    return 3 if plan.long_row_split(row_bytes) is not None else 0
 
 
 def time_device(step, steps, warmup, sampler=None):
@@ -569,7 +583,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                          "note": "per-GPU rate of the local kernel phase alone"},
             "e2e": {"value": job_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": world * args.steps * (2 + (1 if uses_panels(p, kind) else 0)),
+            "gpu_launches": world * args.steps * (2 + extra_launches(p, kind)),
             "clocks": sampler.summary(),
             "extra": {"gflops": job_flops / per_step / 1e9,
                       "pct_of_8tbs_nominal_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS,
@@ -643,7 +657,9 @@ def main():
         e2e_s, h2d, d2h = time_e2e(p, kind, max(4, min(args.steps, 12)), 4)
 
     extra = {"gflops": flops / per_step / 1e9, "pct_of_8tbs_nominal": 100.0 * gbs / NOMINAL_HBM_GBS,
-             "algorithmic_bytes_per_step": nbytes}
+             "algorithmic_bytes_per_step": nbytes,
+             "gathered_bytes_per_step": gathered_bytes(p, kind, nbytes),
+             "gathered_gbs": gathered_bytes(p, kind, nbytes) / per_step / 1e9}
     if args.workload == "cfg2" and not args.no_extra:
         # the second half of the target: SpMM N=32 on the same matrix
         from flagsparse_b200 import workloads as W
@@ -661,6 +677,8 @@ def main():
             "ms_per_step": mm_s * 1e3, "gbs": mm_bytes / mm_s / 1e9,
             "gflops": mm_flops / mm_s / 1e9, "frac_of_measured_peak": mm_bytes / mm_s / 1e9 / peak,
             "algorithmic_bytes_per_step": mm_bytes,
+            "gathered_bytes_per_step": gathered_bytes(p, "spmm", mm_bytes),
+            "gathered_gbs": gathered_bytes(p, "spmm", mm_bytes) / mm_s / 1e9,
         }
         p.extra["alpha"], p.extra["beta"] = saved
         del p.extra["B"], mm_out
@@ -709,7 +727,7 @@ def main():
                      "peak_kind": peak_kind},
         "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps_in_flight": 2},
-        "gpu_launches": (launches_per_step + (1 if uses_panels(p, kind) else 0)) * args.steps,
+        "gpu_launches": (launches_per_step + extra_launches(p, kind)) * args.steps,
         "clocks": sampler.summary(),
         "extra": extra,
     }

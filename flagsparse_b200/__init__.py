@@ -14,7 +14,12 @@ from ._contract import (
     SUPPORTED_INDEX_DTYPES,
     SUPPORTED_VALUE_DTYPES,
 )
-from ._plan import clear_plan_cache, set_panel_policy, set_plan_cache_capacity
+from ._plan import (
+    clear_plan_cache,
+    set_long_row_policy,
+    set_panel_policy,
+    set_plan_cache_capacity,
+)
 from .spmm import (
     SPMM_OP_CONJ_TRANS,
     SPMM_OP_NON,
@@ -67,6 +72,7 @@ __all__ = [
     "clear_plan_cache",
     "set_plan_cache_capacity",
     "set_panel_policy",
+    "set_long_row_policy",
     "SUPPORTED_VALUE_DTYPES",
     "SUPPORTED_INDEX_DTYPES",
     "SPMV_OP_NON", "SPMV_OP_TRANS", "SPMV_OP_CONJ_TRANS",

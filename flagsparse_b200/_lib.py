@@ -51,6 +51,9 @@ SIGNATURES = {
     "b2s_panel_build": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_int64, c_void_p]),
+    "b2s_panel_build_global": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                c_int, c_void_p, c_void_p, c_int64, c_void_p]),
     "b2s_spmv_panels": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -63,6 +66,8 @@ SIGNATURES = {
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_int, c_void_p]),
+    "b2s_spmm_rows_combine": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64,
+                                      c_void_p, c_int64, c_void_p, c_void_p]),
     "b2s_dense_transpose": (c_int, [c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                     c_void_p]),
     "b2s_peer_scatter": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64,

@@ -57,6 +57,107 @@ def set_panel_policy(policy):
     PANEL_POLICY = policy
 
 
+# Long rows by column panel for SpMM (b2s_panel_build_global + b2s_spmm_rows_combine).  On random
+# columns every non-zero gathers a row of B from DRAM; the rows longer than LONG_ROW_MIN of a
+# power-law matrix hold half of the non-zeros and revisit every slice of B many times, so they
+# are multiplied panel by panel out of L2.  "auto": used when B does not fit L2 and the long rows
+# hold at least LONG_ROW_MIN_SHARE of the non-zeros; "off": never.
+LONG_ROW_POLICY = "auto"
+LONG_ROW_MIN = 1024                  # rows longer than this are taken out of the main product
+LONG_ROW_TRIGGER_BYTES = 96 << 20    # B larger than this is a candidate
+LONG_ROW_TARGET_BYTES = 40 << 20     # largest slice of B one panel touches
+LONG_ROW_MIN_SHARE = 0.2
+LONG_ROW_MIN_NNZ = 1 << 22
+
+
+def set_long_row_policy(policy="auto", min_len=None, trigger_bytes=None, target_bytes=None,
+                        min_share=None, min_nnz=None):
+    """'auto' (default) or 'off': whether SpMM may split the long rows of a matrix off and
+    multiply them by column panel.  The other arguments override the thresholds (tests use them
+    to exercise the split on small matrices); None leaves a threshold as it is."""
+    global LONG_ROW_POLICY, LONG_ROW_MIN, LONG_ROW_TRIGGER_BYTES, LONG_ROW_TARGET_BYTES
+    global LONG_ROW_MIN_SHARE, LONG_ROW_MIN_NNZ
+    if policy not in ("auto", "off"):
+        raise ValueError("long-row policy must be 'auto' or 'off'")
+    LONG_ROW_POLICY = policy
+    if min_len is not None:
+        LONG_ROW_MIN = int(min_len)
+    if trigger_bytes is not None:
+        LONG_ROW_TRIGGER_BYTES = int(trigger_bytes)
+    if target_bytes is not None:
+        LONG_ROW_TARGET_BYTES = int(target_bytes)
+    if min_share is not None:
+        LONG_ROW_MIN_SHARE = float(min_share)
+    if min_nnz is not None:
+        LONG_ROW_MIN_NNZ = int(min_nnz)
+
+
+def long_row_shift(n_cols, row_bytes):
+    """Panel width (as a shift) for rows of B of `row_bytes` bytes, or None when the split does
+    not apply: the widest power of two whose slice of B stays within LONG_ROW_TARGET_BYTES, made
+    wider if that would need more than 256 panels."""
+    if LONG_ROW_POLICY != "auto" or row_bytes <= 0 or n_cols * row_bytes <= LONG_ROW_TRIGGER_BYTES:
+        return None
+    shift = 1
+    while (2 << shift) * row_bytes <= LONG_ROW_TARGET_BYTES:
+        shift += 1
+    while ((n_cols - 1) >> shift) + 1 > 256:
+        shift += 1
+    if shift > 31 or ((n_cols - 1) >> shift) + 1 < 2:
+        return None
+    return shift
+
+
+def build_panel_stack(data, indices, indptr, n_rows, n_cols, n_panels, shift, global_cols):
+    """Re-lay a CSR matrix as a stack of column panels with the empty rows of the stack dropped
+    where the stack is small enough to index with int32.  Returns (p_data, p_cols, p_ptr,
+    panel_start, n_stacked, subpos); subpos is None when nothing was dropped."""
+    lib = _lib.load()
+    device = data.device
+    nnz = int(data.numel())
+    vcode = _lib.VALUE_CODE[data.dtype]
+    icode, pcode_in = _lib.INDEX_CODE[indices.dtype], _lib.INDEX_CODE[indptr.dtype]
+    ptr_dtype = torch.int32 if nnz <= INDEX_LIMIT_INT32 else torch.int64
+    p_data = torch.empty_like(data)
+    p_cols = torch.empty(nnz, dtype=torch.int32, device=device)
+    p_ptr = torch.empty(n_panels * n_rows + 1, dtype=ptr_dtype, device=device)
+    panel_start = torch.empty(n_panels + 1, dtype=torch.int64, device=device)
+    nbytes = int(lib.b2s_panel_bytes(n_cols, nnz))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    build = lib.b2s_panel_build_global if global_cols else lib.b2s_panel_build
+    with torch.cuda.device(device):
+        st = build(vcode, icode, pcode_in, _lib.ptr(data), _lib.ptr(indices), _lib.ptr(indptr),
+                   n_rows, n_cols, nnz, n_panels, shift, _lib.ptr(p_data), _lib.ptr(p_cols),
+                   _lib.ptr(p_ptr), _lib.INDEX_CODE[ptr_dtype], _lib.ptr(panel_start),
+                   _lib.ptr(ws), nbytes, _lib.stream_handle(device))
+    _lib.check(st, "b2s_panel_build")
+    del ws
+    # drop the rows of the stack that have no entries (most short rows live in one panel)
+    n_stacked = n_panels * n_rows
+    subpos = None
+    if n_stacked <= INDEX_LIMIT_INT32:
+        subpos = torch.empty(n_stacked, dtype=torch.int32, device=device)
+        count = torch.zeros(1, dtype=torch.int64, device=device)
+        cbytes = int(lib.b2s_panel_compact_bytes(n_stacked))
+        ws = torch.empty(cbytes, dtype=torch.uint8, device=device)
+        pcode = _lib.INDEX_CODE[ptr_dtype]
+        with torch.cuda.device(device):
+            st = lib.b2s_panel_compact(_lib.ptr(p_ptr), pcode, n_stacked, _lib.ptr(subpos),
+                                       _lib.ptr(count), None, 0, _lib.ptr(ws), cbytes,
+                                       _lib.stream_handle(device))
+        _lib.check(st, "b2s_panel_compact")
+        n_compact = int(count.item())
+        c_ptr = torch.empty(n_compact + 1, dtype=ptr_dtype, device=device)
+        with torch.cuda.device(device):
+            st = lib.b2s_panel_compact(_lib.ptr(p_ptr), pcode, n_stacked, _lib.ptr(subpos),
+                                       None, _lib.ptr(c_ptr), n_compact, None, 0,
+                                       _lib.stream_handle(device))
+        _lib.check(st, "b2s_panel_compact")
+        del ws
+        p_ptr, n_stacked = c_ptr, n_compact
+    return p_data, p_cols, p_ptr, panel_start, n_stacked, subpos
+
+
 class PanelLayout:
     """The matrix as a stack of column panels (see include/b200sparse.h, b2s_panel_build)."""
 
@@ -67,6 +168,18 @@ class PanelLayout:
         self.subpos = subpos                # int32[n_panels * n_rows] or None (nothing dropped)
         self.pcode = _lib.INDEX_CODE[ptr.dtype]
         self.tiles = {}
+
+
+class LongRowSplit:
+    """A matrix cut in two for SpMM: `short` (all rows, the long ones emptied) and `stack` (the
+    long rows as a stack of column panels with global int32 columns; stacked row
+    subpos[p * n_long + j] holds the entries of long row j = rows[j] that fall into panel p)."""
+
+    def __init__(self, short, stack, rows, subpos, n_panels, shift):
+        self.short, self.stack = short, stack
+        self.rows, self.subpos = rows, subpos
+        self.n_long = int(rows.numel())
+        self.n_panels, self.shift = int(n_panels), int(shift)
 
 
 class CsrPlan:
@@ -90,6 +203,7 @@ class CsrPlan:
         self._scratch = {}                   # (tag, width, stream) -> tensor
         self._transposed = {}                # conj flag -> CsrPlan of the transpose
         self._panels = False                 # False: not decided yet; None: not used
+        self._long_rows = {}                 # panel shift -> LongRowSplit or None (SpMM)
         self._spmv_record = None             # prebuilt launch arguments (spmv.py)
         self._prepared = {}                  # memo of PreparedCsrSpmv handles (spmv.py)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -142,49 +256,61 @@ class CsrPlan:
         n_panels = ((self.n_cols - 1) >> shift) + 1
         if n_panels < 2 or n_panels > 256 or shift > 31:
             return None
-        lib = _lib.load()
-        ptr_dtype = torch.int32 if self.nnz <= INDEX_LIMIT_INT32 else torch.int64
-        p_data = torch.empty_like(self.data)
-        p_cols = torch.empty(self.nnz, dtype=torch.int32, device=self.device)
-        p_ptr = torch.empty(n_panels * self.n_rows + 1, dtype=ptr_dtype, device=self.device)
-        panel_start = torch.empty(n_panels + 1, dtype=torch.int64, device=self.device)
-        nbytes = int(lib.b2s_panel_bytes(self.n_cols, self.nnz))
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
-        with torch.cuda.device(self.device):
-            st = lib.b2s_panel_build(
-                self.vcode, self.icode, self.pcode, _lib.ptr(self.data), _lib.ptr(self.indices),
-                _lib.ptr(self.indptr), self.n_rows, self.n_cols, self.nnz, n_panels, shift,
-                _lib.ptr(p_data), _lib.ptr(p_cols), _lib.ptr(p_ptr),
-                _lib.INDEX_CODE[ptr_dtype], _lib.ptr(panel_start), _lib.ptr(ws), nbytes,
-                _lib.stream_handle(self.device))
-        _lib.check(st, "b2s_panel_build")
-        del ws
-        # drop the rows of the stack that have no entries (most short rows live in one panel)
-        n_stacked = n_panels * self.n_rows
-        subpos = None
-        if n_stacked <= INDEX_LIMIT_INT32:
-            subpos = torch.empty(n_stacked, dtype=torch.int32, device=self.device)
-            count = torch.zeros(1, dtype=torch.int64, device=self.device)
-            cbytes = int(lib.b2s_panel_compact_bytes(n_stacked))
-            ws = torch.empty(cbytes, dtype=torch.uint8, device=self.device)
-            pcode = _lib.INDEX_CODE[ptr_dtype]
-            with torch.cuda.device(self.device):
-                st = lib.b2s_panel_compact(_lib.ptr(p_ptr), pcode, n_stacked, _lib.ptr(subpos),
-                                           _lib.ptr(count), None, 0, _lib.ptr(ws), cbytes,
-                                           _lib.stream_handle(self.device))
-            _lib.check(st, "b2s_panel_compact")
-            n_compact = int(count.item())
-            c_ptr = torch.empty(n_compact + 1, dtype=ptr_dtype, device=self.device)
-            with torch.cuda.device(self.device):
-                st = lib.b2s_panel_compact(_lib.ptr(p_ptr), pcode, n_stacked, _lib.ptr(subpos),
-                                           None, _lib.ptr(c_ptr), n_compact, None, 0,
-                                           _lib.stream_handle(self.device))
-            _lib.check(st, "b2s_panel_compact")
-            del ws
-            p_ptr, n_stacked = c_ptr, n_compact
+        p_data, p_cols, p_ptr, panel_start, n_stacked, subpos = build_panel_stack(
+            self.data, self.indices, self.indptr, self.n_rows, self.n_cols, n_panels, shift,
+            global_cols=False)
         self._panels = PanelLayout(p_data, p_cols, p_ptr, panel_start, n_panels, shift,
                                    n_stacked, subpos)
         return self._panels
+
+    # -- long rows by column panel (SpMM) --------------------------------------------------------
+    def long_row_split(self, row_bytes):
+        """LongRowSplit for rows of B of `row_bytes` bytes when the policy asks for one for this
+        matrix, else None (decided and built once per panel width)."""
+        shift = long_row_shift(self.n_cols, row_bytes)
+        if shift is None or self.nnz < LONG_ROW_MIN_NNZ or self.n_cols > INDEX_LIMIT_INT32:
+            return None
+        if shift in self._long_rows:
+            return self._long_rows[shift]
+        self._long_rows[shift] = None
+        if 0 <= self.max_row_nnz <= LONG_ROW_MIN:
+            return None
+        ptr64 = self.indptr.to(torch.int64)
+        lens = ptr64[1:] - ptr64[:-1]
+        long_mask = lens > LONG_ROW_MIN
+        rows = torch.nonzero(long_mask).flatten()
+        n_long = int(rows.numel())
+        if n_long == 0:
+            return None
+        long_lens = lens[rows]
+        nnz_long = int(long_lens.sum().item())
+        n_panels = ((self.n_cols - 1) >> shift) + 1
+        if nnz_long < LONG_ROW_MIN_SHARE * self.nnz or n_panels * n_long > INDEX_LIMIT_INT32:
+            return None
+        # the long rows as a CSR matrix of their own, and the matrix without them
+        ptr_long = torch.zeros(n_long + 1, dtype=torch.int64, device=self.device)
+        torch.cumsum(long_lens, 0, out=ptr_long[1:])
+        gidx = torch.repeat_interleave(ptr64[rows] - ptr_long[:-1], long_lens)
+        gidx += torch.arange(nnz_long, dtype=torch.int64, device=self.device)
+        data_long, idx_long = self.data[gidx], self.indices[gidx]
+        keep = torch.ones(self.nnz, dtype=torch.bool, device=self.device)
+        keep[gidx] = False
+        del gidx
+        data_short, idx_short = self.data[keep], self.indices[keep]
+        del keep
+        ptr_short = torch.zeros(self.n_rows + 1, dtype=torch.int64, device=self.device)
+        torch.cumsum(lens.masked_fill(long_mask, 0), 0, out=ptr_short[1:])
+        ptr_short = ptr_short.to(self.indptr.dtype)
+        del lens, long_mask, ptr64
+        p_data, p_cols, p_ptr, _, n_stacked, subpos = build_panel_stack(
+            data_long, idx_long, ptr_long, n_long, self.n_cols, n_panels, shift, global_cols=True)
+        del data_long, idx_long
+        if subpos is None:
+            return None
+        short = CsrPlan(data_short, idx_short, ptr_short, self.shape, LONG_ROW_MIN)
+        stack = CsrPlan(p_data, p_cols, p_ptr, (n_stacked, self.n_cols), -1)
+        self._long_rows[shift] = LongRowSplit(short, stack, rows, subpos, n_panels, shift)
+        return self._long_rows[shift]
 
     def panel_tiles(self, items):
         lay = self._panels

@@ -732,3 +732,58 @@ extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void
   })));
   return B2S_ERR_DTYPE;
 }
+
+// ---- long rows by column panel ---------------------------------------------------------------
+// The long rows of a matrix, taken out and re-laid as a stack of column panels (one stacked row
+// per (panel, long row) that has entries), are multiplied by the same tile kernel into one
+// partial row of C per stacked row.  This kernel adds the partials of each long row in ascending
+// panel order and accumulates alpha times the sum into the row of C the long row belongs to
+// (which the product over the remaining rows has already set to beta * C_in).
+namespace b2s {
+
+template <class V>
+__global__ void spmm_rows_combine_kernel(const V* __restrict__ part,
+                                         const int32_t* __restrict__ subpos,
+                                         const int64_t* __restrict__ rows, int64_t n_long,
+                                         int n_panels, int64_t n_dense, V* C, int64_t ldc,
+                                         V alpha) {
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (idx >= n_long * n_dense) return;
+  const int64_t j = idx / n_dense;
+  const int64_t n = idx - j * n_dense;
+  V s = vt<V>::zero();
+  for (int p = 0; p < n_panels; ++p) {
+    const int32_t c = subpos[p * n_long + j];
+    if (c >= 0) s = s + part[c * n_dense + n];
+  }
+  V* out = C + rows[j] * ldc + n;
+  *out = *out + alpha * s;
+}
+
+}  // namespace b2s
+
+extern "C" int b2s_spmm_rows_combine(int val_type, const void* part_dev,
+                                     const int32_t* subpos_dev, const int64_t* rows_dev,
+                                     int64_t n_long, int n_panels, int64_t n_dense, void* C_dev,
+                                     int64_t ldc, const void* alpha, b2s_stream stream) {
+  if (n_long < 0 || n_dense < 0 || n_panels < 1 || n_panels > 256 || !alpha) return B2S_ERR_ARG;
+  if (n_long == 0 || n_dense == 0) return B2S_OK;
+  if (ldc < n_dense || !part_dev || !subpos_dev || !rows_dev || !C_dev) return B2S_ERR_ARG;
+  const size_t vs = b2s::vsize(val_type);
+  if (vs == 0) return B2S_ERR_DTYPE;
+  const uintptr_t m = vs - 1;
+  if ((reinterpret_cast<uintptr_t>(part_dev) & m) || (reinterpret_cast<uintptr_t>(C_dev) & m))
+    return B2S_ERR_ALIGNMENT;
+  const int64_t work = n_long * n_dense;
+  const int threads = 256;
+  const int64_t grid = (work + threads - 1) / threads;
+  if (grid > 0x7fffffffLL) return B2S_ERR_RANGE;
+  B2S_DISPATCH_V(val_type, {
+    (b2s::spmm_rows_combine_kernel<V><<<static_cast<unsigned>(grid), threads, 0,
+                                        static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const V*>(part_dev), subpos_dev, rows_dev, n_long, n_panels, n_dense,
+        static_cast<V*>(C_dev), ldc, *static_cast<const V*>(alpha)));
+    return b2s::launch_status();
+  });
+  return B2S_ERR_DTYPE;
+}

@@ -270,7 +270,7 @@ __global__ void panel_gather_kernel(const V* __restrict__ data, const P* __restr
                                     int64_t n_rows, const W* __restrict__ sorted_cols,
                                     const W* __restrict__ src_pos, int64_t nnz, int panel_shift,
                                     V* __restrict__ p_data, int32_t* __restrict__ p_cols,
-                                    int64_t* __restrict__ stacked_row) {
+                                    int64_t* __restrict__ stacked_row, int global_cols) {
   const int64_t k = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (k >= nnz) return;
   const int64_t j = static_cast<int64_t>(src_pos[k]);
@@ -284,7 +284,7 @@ __global__ void panel_gather_kernel(const V* __restrict__ data, const P* __restr
       hi = mid;
   }
   p_data[k] = data[j];
-  p_cols[k] = static_cast<int32_t>(c & ((int64_t{1} << panel_shift) - 1));
+  p_cols[k] = static_cast<int32_t>(global_cols ? c : (c & ((int64_t{1} << panel_shift) - 1)));
   stacked_row[k] = (c >> panel_shift) * n_rows + lo;
 }
 
@@ -343,7 +343,7 @@ template <class V, class I, class P, class PP, class W>
 int panel_build_run(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                     int64_t nnz, int n_panels, int panel_shift, void* p_data, int32_t* p_cols,
                     void* p_ptr, int64_t* panel_start, void* scratch, int64_t scratch_bytes,
-                    cudaStream_t s) {
+                    cudaStream_t s, int global_cols) {
   if (panel_scratch_bytes<W>(nnz) > scratch_bytes) return B2S_ERR_WORKSPACE;
   unsigned char* p = static_cast<unsigned char*>(scratch);
   W* keys = reinterpret_cast<W*>(p); p += align256(nnz * sizeof(W));
@@ -362,7 +362,7 @@ int panel_build_run(const void* data, const void* indices, const void* indptr, i
                                                          n_blocks);
   panel_gather_kernel<V, P, W><<<static_cast<unsigned>((nnz + 255) / 256), 256, 0, s>>>(
       static_cast<const V*>(data), static_cast<const P*>(indptr), n_rows, keys, vals, nnz,
-      panel_shift, static_cast<V*>(p_data), p_cols, stacked);
+      panel_shift, static_cast<V*>(p_data), p_cols, stacked, global_cols);
   csc_ptr_kernel<int64_t, PP><<<static_cast<unsigned>((nnz + 1 + 255) / 256), 256, 0, s>>>(
       stacked, nnz, n_rows * n_panels, static_cast<PP*>(p_ptr));
   panel_start_kernel<PP><<<(n_panels + 1 + 63) / 64, 64, 0, s>>>(static_cast<const PP*>(p_ptr),
@@ -417,13 +417,14 @@ extern "C" int64_t b2s_panel_bytes(int64_t n_cols, int64_t nnz) {
                                        : b2s::panel_scratch_bytes<uint32_t>(nnz);
 }
 
-extern "C" int b2s_panel_build(int val_type, int idx_type, int ptr_type, const void* data_dev,
-                               const void* indices_dev, const void* indptr_dev, int64_t n_rows,
-                               int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
-                               void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev,
-                               int p_ptr_type, int64_t* panel_start_dev, void* scratch_dev,
-                               int64_t scratch_bytes, b2s_stream stream) {
+static int panel_build_any(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                           const void* indices_dev, const void* indptr_dev, int64_t n_rows,
+                           int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                           void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev,
+                           int p_ptr_type, int64_t* panel_start_dev, void* scratch_dev,
+                           int64_t scratch_bytes, b2s_stream stream, int global_cols) {
   if (n_rows <= 0 || n_cols <= 0 || nnz <= 0) return B2S_ERR_ARG;
+  if (global_cols && n_cols > 0x7fffffffLL) return B2S_ERR_RANGE;
   if (n_panels < 1 || n_panels > 256 || panel_shift < 1 || panel_shift > 31) return B2S_ERR_ARG;
   if (((n_cols - 1) >> panel_shift) >= n_panels) return B2S_ERR_ARG;
   if (p_ptr_type == B2S_I32 && nnz > 0x7fffffffLL) return B2S_ERR_RANGE;
@@ -437,12 +438,35 @@ extern "C" int b2s_panel_build(int val_type, int idx_type, int ptr_type, const v
     if (wide)
       return (b2s::panel_build_run<V, I, P, PP, uint64_t>(
           data_dev, indices_dev, indptr_dev, n_rows, nnz, n_panels, panel_shift, p_data_dev,
-          p_cols_dev, p_ptr_dev, panel_start_dev, scratch_dev, scratch_bytes, s));
+          p_cols_dev, p_ptr_dev, panel_start_dev, scratch_dev, scratch_bytes, s, global_cols));
     return (b2s::panel_build_run<V, I, P, PP, uint32_t>(
         data_dev, indices_dev, indptr_dev, n_rows, nnz, n_panels, panel_shift, p_data_dev,
-        p_cols_dev, p_ptr_dev, panel_start_dev, scratch_dev, scratch_bytes, s));
+        p_cols_dev, p_ptr_dev, panel_start_dev, scratch_dev, scratch_bytes, s, global_cols));
   }))));
   return B2S_ERR_DTYPE;
+}
+
+extern "C" int b2s_panel_build(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                               const void* indices_dev, const void* indptr_dev, int64_t n_rows,
+                               int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
+                               void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev,
+                               int p_ptr_type, int64_t* panel_start_dev, void* scratch_dev,
+                               int64_t scratch_bytes, b2s_stream stream) {
+  return panel_build_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
+                         n_cols, nnz, n_panels, panel_shift, p_data_dev, p_cols_dev, p_ptr_dev,
+                         p_ptr_type, panel_start_dev, scratch_dev, scratch_bytes, stream, 0);
+}
+
+extern "C" int b2s_panel_build_global(int val_type, int idx_type, int ptr_type,
+                                      const void* data_dev, const void* indices_dev,
+                                      const void* indptr_dev, int64_t n_rows, int64_t n_cols,
+                                      int64_t nnz, int n_panels, int panel_shift,
+                                      void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev,
+                                      int p_ptr_type, int64_t* panel_start_dev, void* scratch_dev,
+                                      int64_t scratch_bytes, b2s_stream stream) {
+  return panel_build_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
+                         n_cols, nnz, n_panels, panel_shift, p_data_dev, p_cols_dev, p_ptr_dev,
+                         p_ptr_type, panel_start_dev, scratch_dev, scratch_bytes, stream, 1);
 }
 
 extern "C" int64_t b2s_csr2csc_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz) {

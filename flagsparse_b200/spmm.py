@@ -150,7 +150,33 @@ def _checked_spmm_plan(data, indices, indptr, shape):
 
 
 def _launch_spmm(plan: CsrPlan, B, C, C_in, alpha, beta):
-    """Enqueue C = alpha * A B + beta * C_in on the current stream (no synchronisation)."""
+    """Enqueue C = alpha * A B + beta * C_in on the current stream (no synchronisation).
+
+    When B is too large for L2 and the matrix has long rows that hold a good share of the
+    non-zeros, the product runs in three launches: the matrix without its long rows (which also
+    puts beta * C_in into the long rows of C), the long rows as a stack of column panels into
+    one partial row per (panel, long row), and the sum of those partials into C."""
+    n_dense = int(B.shape[1])
+    split = plan.long_row_split(n_dense * B.element_size())
+    if split is None:
+        _launch_spmm_plain(plan, B, C, C_in, alpha, beta)
+        return
+    lib = _lib.load()
+    _launch_spmm_plain(split.short, B, C, C_in, alpha, beta)
+    stack = split.stack
+    part = stack.scratch("spmm_long_part", stack.n_rows * n_dense).view(stack.n_rows, n_dense)
+    _launch_spmm_plain(stack, B, part, None, 1.0, 0.0)
+    a = _lib.scalar_buffer(alpha, plan.data.dtype)
+    with torch.cuda.device(plan.device):
+        st = lib.b2s_spmm_rows_combine(
+            plan.vcode, _lib.ptr(part), _lib.ptr(split.subpos), _lib.ptr(split.rows),
+            split.n_long, split.n_panels, n_dense, _lib.ptr(C), int(C.stride(0)), a,
+            _lib.stream_handle(plan.device))
+    _lib.check(st, "b2s_spmm_rows_combine")
+
+
+def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
+    """One b2s_spmm_csr launch for the matrix of `plan` as it is."""
     lib = _lib.load()
     n_dense = int(B.shape[1])
     items = lib.b2s_spmm_tile_items(plan.vcode, plan.icode)

@@ -170,6 +170,15 @@ int b2s_panel_build(int val_type, int idx_type, int ptr_type,
                     void* p_data_dev, int32_t* p_cols_dev, void* p_ptr_dev, int p_ptr_type,
                     int64_t* panel_start_dev, void* scratch_dev, int64_t scratch_bytes,
                     b2s_stream stream);
+/* The same re-layout with the caller's (global) column numbers kept, as int32 (n_cols must not
+ * exceed 2^31): the stack then is an ordinary CSR matrix whose rows are sorted by panel, which
+ * the SpMM kernel can multiply as it is (see b2s_spmm_rows_combine). */
+int b2s_panel_build_global(int val_type, int idx_type, int ptr_type,
+                           const void* data_dev, const void* indices_dev, const void* indptr_dev,
+                           int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels,
+                           int panel_shift, void* p_data_dev, int32_t* p_cols_dev,
+                           void* p_ptr_dev, int p_ptr_type, int64_t* panel_start_dev,
+                           void* scratch_dev, int64_t scratch_bytes, b2s_stream stream);
 int b2s_spmv_panels(int val_type, int ptr_type,
                     const void* p_data_dev, const int32_t* p_cols_dev, const void* p_ptr_dev,
                     int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
@@ -242,6 +251,19 @@ int b2s_spmm_csr(int val_type, int idx_type, int ptr_type,
                  const void* alpha, const void* beta,
                  const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
                  b2s_stream stream);
+
+/* Long rows of a power-law matrix by column panel (no counterpart in the reference).  On random
+ * columns SpMM gathers one row of B per non-zero from DRAM.  The host side splits the matrix:
+ * rows up to a length threshold stay as they are; the long rows are laid out by
+ * b2s_panel_build_global + b2s_panel_compact as a stack of column panels whose slice of B fits
+ * L2, and b2s_spmm_csr multiplies that stack into part_dev (one row of n_dense values per
+ * non-empty (panel, long row), leading dimension n_dense).  This call adds, for each long row j,
+ * the partials subpos_dev[p * n_long + j] >= 0 in ascending panel order and accumulates
+ * alpha * sum into row rows_dev[j] of C, which the product over the short rows has set to
+ * beta * C_in before. */
+int b2s_spmm_rows_combine(int val_type, const void* part_dev, const int32_t* subpos_dev,
+                          const int64_t* rows_dev, int64_t n_long, int n_panels, int64_t n_dense,
+                          void* C_dev, int64_t ldc, const void* alpha, b2s_stream stream);
 
 /* ---- CSR -> CSC (the transpose behind op = trans / conj) -----------------------------------
  * Replaces _transpose_csr_for_spmv (spmv_csr.py:477-515) and _transpose_csr_for_spmm

@@ -226,3 +226,77 @@ def test_spmm_does_not_touch_rows_of_B_it_does_not_reference():
                             (700, 400))
     assert np.isfinite(host(C)).all()
     assert_parity(host(C), expect, np.float32)
+
+
+@pytest.fixture
+def forced_long_row_split():
+    """Thresholds low enough that small matrices take the long-row / column-panel route."""
+    from flagsparse_b200 import _plan, clear_plan_cache, set_long_row_policy
+    saved = (_plan.LONG_ROW_POLICY, _plan.LONG_ROW_MIN, _plan.LONG_ROW_TRIGGER_BYTES,
+             _plan.LONG_ROW_TARGET_BYTES, _plan.LONG_ROW_MIN_SHARE, _plan.LONG_ROW_MIN_NNZ)
+    clear_plan_cache()
+    set_long_row_policy("auto", min_len=48, trigger_bytes=0, target_bytes=16 << 10,
+                        min_share=0.0, min_nnz=0)
+    yield
+    set_long_row_policy(saved[0], *saved[1:])
+    clear_plan_cache()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("n_dense", [4, 32, 70])
+@pytest.mark.parametrize("op", ["non", "trans"])
+def test_spmm_long_rows_by_column_panel(dtype, n_dense, op, forced_long_row_split):
+    """The three-launch route (short rows, long rows as a panel stack, combine) gives the oracle's
+    result, with alpha / beta and an `out` that holds C_in, and is bit-identical run to run."""
+    from flagsparse_b200 import _plan, flagsparse_spmm_csr, set_long_row_policy
+    rng = np.random.default_rng(77 + n_dense)
+    lengths = np.concatenate([[0, 49, 48, 3000, 1, 0, 700], rng.integers(0, 40, 600),
+                              [5000, 0, 0, 64], rng.integers(0, 6, 500), [2100]])
+    n_rows, n_cols = lengths.size, 2600
+    data, idx, ptr = csr_from_lengths(rng, lengths, n_cols, dtype, sort=False)
+    if op != "non":
+        # hand over the transpose of that matrix, so that op(A) is the one with the long rows
+        import scipy.sparse as sp
+        At = sp.csr_matrix((data, idx, ptr), shape=(n_rows, n_cols)).T.tocsr()
+        data, idx, ptr = At.data.astype(dtype), At.indices.astype(np.int64), At.indptr
+        n_rows, n_cols = n_cols, n_rows
+    k = n_rows if op != "non" else n_cols
+    m = n_cols if op != "non" else n_rows
+    B = random_values(rng, k * n_dense, dtype).reshape(k, n_dense)
+    C0 = random_values(rng, m * n_dense, dtype).reshape(m, n_dense)
+    d, i, p = dev(data), dev(idx, torch.int32), dev(ptr, torch.int64)
+    C = flagsparse_spmm_csr(d, i, p, dev(B), (n_rows, n_cols), op=op)
+    plan = _plan.cache_get(_plan.plan_key("spmm", d, i, p, (n_rows, n_cols)))
+    if op != "non":
+        plan = plan.transposed(conj=False)
+    split = plan.long_row_split(n_dense * B.itemsize)
+    assert split is not None and split.n_long >= 3 and split.n_panels >= 2
+    assert split.short.nnz + split.stack.nnz == data.size
+    assert_parity(host(C), oracle.spmm(data, idx, ptr, B, (n_rows, n_cols), op=op), dtype)
+    out = dev(C0)
+    got = flagsparse_spmm_csr(d, i, p, dev(B), (n_rows, n_cols), op=op, out=out, alpha=-0.75,
+                              beta=1.25)
+    assert got is out
+    expect = oracle.spmm(data, idx, ptr, B, (n_rows, n_cols), op=op, alpha=-0.75, beta=1.25,
+                         C0=C0)
+    assert_parity(host(out), expect, dtype)
+    again = flagsparse_spmm_csr(d, i, p, dev(B), (n_rows, n_cols), op=op)
+    assert torch.equal(C.view(torch.uint8), again.view(torch.uint8))
+    # the plain route on the same inputs agrees to rounding
+    set_long_row_policy("off")
+    from flagsparse_b200 import clear_plan_cache
+    clear_plan_cache()
+    plain = flagsparse_spmm_csr(d, i, p, dev(B), (n_rows, n_cols), op=op)
+    assert_parity(host(C), host(plain), dtype)
+
+
+def test_long_row_split_is_not_taken_for_small_or_uniform_matrices():
+    from flagsparse_b200 import _plan
+    assert _plan.long_row_shift(1 << 20, 64) is None            # B of 64 MB fits L2
+    assert _plan.long_row_shift(1 << 24, 256) == 17             # 2^17 rows x 256 B = 32 MB
+    assert _plan.long_row_shift(1 << 26, 64) == 19
+    assert _plan.long_row_shift((1 << 31) - 1, 4096) == 23      # never more than 256 panels
+    rng = np.random.default_rng(1)
+    data, idx, ptr = csr_from_lengths(rng, rng.integers(0, 20, 500), 300, np.float32)
+    plan = _plan.CsrPlan(dev(data), dev(idx, torch.int32), dev(ptr, torch.int64), (500, 300), 19)
+    assert plan.long_row_split(1 << 20) is None
