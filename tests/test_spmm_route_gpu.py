@@ -80,7 +80,7 @@ def test_route_column_major_matches_oracle(dtype, n_dense, op):
     C = flagsparse_spmm_csr_run(prepared, wide, dense_layout="F")
     assert_parity(host(C), expect, dtype)
     row = flagsparse_spmm_csr_run(prepared, dev(B), dense_layout="row")
-    assert torch.equal(C.contiguous().view(torch.uint8), row.view(torch.uint8))
+    assert torch.equal(C, row)  # same kernel, same order of additions: equal value by value
 
 
 def test_route_meta_and_timing_keys():
