@@ -17,8 +17,9 @@ OP_NAMES = {OP_NON: "non", OP_TRANS: "trans", OP_CONJ_TRANS: "conj"}
 _NAME_TO_OP = {v: k for k, v in OP_NAMES.items()}
 _OP_MESSAGE = "op must be one of: 0=non, 1=trans, 2=conj"
 
-# The value dtypes this build computes in.  FlagSparse additionally lists float16 / bfloat16
-# (_common.py:21-29); those raise the reference's TypeError text here.
+# The value dtypes the kernels compute in.  FlagSparse additionally lists float16 / bfloat16
+# (_common.py:21-29) and computes them in float32; here they are widened once and run through the
+# float32 kernels (_half.py).
 SUPPORTED_VALUE_DTYPES = (torch.float32, torch.float64, torch.complex64, torch.complex128)
 SUPPORTED_INDEX_DTYPES = (torch.int32, torch.int64)
 INDEX_LIMIT_INT32 = 2**31 - 1

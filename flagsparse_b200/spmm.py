@@ -16,7 +16,7 @@ import time
 
 import torch
 
-from . import _lib
+from . import _half, _lib
 from ._contract import (
     INDEX_LIMIT_INT32,
     OP_CONJ_TRANS,
@@ -225,6 +225,15 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
     if max_segments is not None and max_segments <= 0:
         raise ValueError("max_segments must be positive when provided")
 
+    # float16 / bfloat16: B and out are the caller's 16-bit tensors, the product is float32
+    half = data.dtype if _half.is_half(data) else None
+    half_out = None
+    if half is not None:
+        data = _half.widened_values(data)
+        if torch.is_tensor(B):
+            if B.dtype != half:
+                raise TypeError("B dtype must match data dtype")
+            B = B.to(torch.float32)
     plan = _checked_spmm_plan(data, indices, indptr, shape)
     if B.ndim != 2:
         raise ValueError("B must be a 2D dense tensor")
@@ -245,6 +254,10 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
     alpha = check_scalar(alpha, dtype, "alpha")
     beta = check_scalar(beta, dtype, "beta")
 
+    if half is not None and torch.is_tensor(out):
+        if out.shape != (eff_rows, n_dense) or out.dtype != half:
+            raise ValueError("out shape/dtype must match result")
+        half_out, out = out, (out.to(torch.float32) if beta != 0 else None)
     if out is not None:
         if not out.is_cuda:
             raise ValueError("out must be a CUDA tensor")
@@ -298,6 +311,8 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
         out.copy_(C)
     if out is not None:
         C = out
+    if half is not None:
+        C = _half.narrow_result(C, half, half_out)
     if do_timing:
         torch.cuda.synchronize()
         t2 = time.perf_counter()

@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _half, _lib
 from ._contract import OP_CONJ_TRANS, is_complex, normalize_op, op_name, op_transposes
 from .spmm import SUPPORTED_SPMM_VALUE_DTYPES, _checked_spmm_plan, _launch_spmm, _row_major_ok
 
@@ -32,7 +32,7 @@ class SpmmCsrAlgorithmUnavailable(RuntimeError):
 # name -> (display name, value dtypes the reference registers the route for)
 _REAL = (torch.float32, torch.float64)
 SPMM_CSR_ALGORITHMS = {
-    "csr_base": ("Base", SUPPORTED_SPMM_VALUE_DTYPES),
+    "csr_base": ("Base", _half.HALF_VALUE_DTYPES + SUPPORTED_SPMM_VALUE_DTYPES),
     "alpha_alg1_tle_opt": ("TLEOpt", _REAL),
     "alpha_alg1_tle_opt2": ("TLEOpt2", _REAL),
     "spmm_csr_alg1": ("Alg1", _REAL),
@@ -109,8 +109,11 @@ class PreparedCsrSpmmRoute:
     scratch buffers and -- once an ``op = trans / conj`` run has asked for it -- the transposed
     matrix live in the plan object kept here."""
 
-    def __init__(self, plan, shape, op, alg):
+    def __init__(self, plan, shape, op, alg, value_dtype=None):
         self._plan = plan
+        # dtype of the caller's values, of B and of C; float16 / bfloat16 matrices are kept and
+        # multiplied in float32 (plan.data)
+        self.value_dtype = plan.data.dtype if value_dtype is None else value_dtype
         self.data = plan.data
         self.kernel_indices = plan.indices
         self.kernel_indptr = plan.indptr
@@ -136,11 +139,14 @@ def prepare_spmm_csr_route(data, indices, indptr, shape, *, op="non", alg="auto"
     """Validate the matrix once (same contract and exceptions as ``flagsparse_spmm_csr``) and
     return the handle for ``flagsparse_spmm_csr_run``."""
     name = op_name(normalize_op(op))
+    value_dtype = data.dtype if torch.is_tensor(data) else None
+    if _half.is_half(data):
+        data = _half.widened_values(data)
     plan = _checked_spmm_plan(data, indices, indptr, shape)
     resolved = _normalize_spmm_csr_alg(alg)
     if resolved != "auto":
-        resolve_spmm_csr_algorithm(resolved, name, plan.data.dtype)
-    return PreparedCsrSpmmRoute(plan, shape, name, resolved)
+        resolve_spmm_csr_algorithm(resolved, name, value_dtype)
+    return PreparedCsrSpmmRoute(plan, shape, name, resolved, value_dtype)
 
 
 def _transpose_dense(src, rows, cols, ld_src, dst, ld_dst):
@@ -166,7 +172,8 @@ def flagsparse_spmm_csr_run(prepared, B, *, alg=None, op=None, dense_layout="aut
     name = op_name(op_code)
     alg_name = prepared.alg if alg is None else _normalize_spmm_csr_alg(alg)
     dtype = prepared.data.dtype
-    algorithm = resolve_spmm_csr_algorithm(alg_name, name, dtype)
+    value_dtype = prepared.value_dtype
+    algorithm = resolve_spmm_csr_algorithm(alg_name, name, value_dtype)
     layout = _normalize_dense_layout(dense_layout)
     if layout == "col" and algorithm != "csr_base":
         raise SpmmCsrAlgorithmUnavailable(
@@ -179,8 +186,10 @@ def flagsparse_spmm_csr_run(prepared, B, *, alg=None, op=None, dense_layout="aut
         raise ValueError("B must be a CUDA tensor")
     if B.device != prepared.data.device:
         raise ValueError("B must be on the same CUDA device as sparse matrix data")
-    if B.dtype != dtype:
+    if B.dtype != value_dtype:
         raise TypeError("B dtype must match sparse matrix dtype")
+    if value_dtype != dtype:
+        B = B.to(dtype)  # float16 / bfloat16 operand, float32 product
 
     want_ms = bool(return_time or return_meta)
     if want_ms:
@@ -246,6 +255,8 @@ def flagsparse_spmm_csr_run(prepared, B, *, alg=None, op=None, dense_layout="aut
         torch.cuda.synchronize()
         compute_ms = c0.elapsed_time(c1)
 
+    if value_dtype != dtype:
+        C = C.to(value_dtype)  # keeps the strides of a column-major C
     gpu_ms = None
     process_cpu_ms = 0.0
     if want_ms:

@@ -19,7 +19,7 @@ import time
 
 import torch
 
-from . import _lib
+from . import _half, _lib
 from ._contract import (
     INDEX_LIMIT_INT32,
     OP_CONJ_TRANS,
@@ -129,8 +129,12 @@ class PreparedCsrSpmv:
     def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, block_nnz,
                  max_segments, max_row_nnz, opt_buckets=None, opt_max_segments=None,
                  row_lengths=None, transpose=False, op=None, index_fallback_policy="auto",
-                 index_fallback_applied=False, index_fallback_reason=None, _plan=None):
+                 index_fallback_applied=False, index_fallback_reason=None, _plan=None,
+                 value_dtype=None):
         self.data = data
+        # dtype of the caller's values and results; differs from data.dtype for float16 /
+        # bfloat16 matrices, which are kept and multiplied in float32
+        self.value_dtype = data.dtype if value_dtype is None else value_dtype
         self.kernel_indices = kernel_indices
         self.kernel_indptr = kernel_indptr
         self.shape = (int(shape[0]), int(shape[1]))
@@ -180,6 +184,9 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
     op_code = normalize_op(op, transpose=transpose)
     if op is not None and bool(transpose) and op_code == OP_NON:
         raise ValueError("transpose=True conflicts with op=non")
+    value_dtype = data.dtype if torch.is_tensor(data) else None
+    if _half.is_half(data):
+        data = _half.widened_values(data)
     base_plan = _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy)
     memo_key = (op_code, block_nnz, max_segments, index_fallback_policy)
     memo = base_plan._prepared.get(memo_key)
@@ -207,7 +214,7 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
         n_rows=plan.n_rows, n_cols=plan.n_cols, block_nnz=block_nnz_use,
         max_segments=max_segments_use, opt_max_segments=max_segments, max_row_nnz=max_row_nnz,
         transpose=op_transposes(op_code), op=op_code,
-        index_fallback_policy=index_fallback_policy, _plan=plan)
+        index_fallback_policy=index_fallback_policy, _plan=plan, value_dtype=value_dtype)
     base_plan._prepared[memo_key] = prepared
     return prepared
 
@@ -482,10 +489,23 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
             raise ValueError(
                 f"transpose={bool(transpose)} does not match "
                 f"prepared.transpose={prepared.transpose}")
-    x = _validate_spmv_x(x, prepared)
     dtype = prepared.data.dtype
     alpha = check_scalar(alpha, dtype, "alpha")
     beta = check_scalar(beta, dtype, "beta")
+    half = getattr(prepared, "value_dtype", dtype)
+    half = half if half in _half.HALF_VALUE_DTYPES else None
+    half_out = None
+    if half is not None:
+        # float16 / bfloat16: x and out are the caller's 16-bit tensors, the product is float32
+        if torch.is_tensor(x):
+            if x.dtype != half:
+                raise TypeError("x dtype must match sparse matrix dtype")
+            x = x.to(torch.float32)
+        if torch.is_tensor(out):
+            if out.shape != (prepared.n_rows,) or out.dtype != half:
+                raise ValueError("out shape/dtype must match result")
+            half_out, out = out, (out.to(torch.float32) if beta != 0 else None)
+    x = _validate_spmv_x(x, prepared)
     if out is not None:
         if not torch.is_tensor(out) or not out.is_cuda:
             raise ValueError("out must be a CUDA tensor")
@@ -506,6 +526,8 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
         t1 = time.perf_counter()
     y = _run_spmv_prepared_with_fallback(prepared, x, use_opt=use_opt, out=out, alpha=alpha,
                                          beta=beta)
+    if half is not None:
+        y = _half.narrow_result(y, half, half_out)
     if do_timing:
         torch.cuda.synchronize()
         t2 = time.perf_counter()
@@ -564,7 +586,7 @@ def _check_coo(data, row, col, x=None):
         raise ValueError(f"{names} must all be CUDA tensors")
     if any(t.ndim != 1 for t in tensors):
         raise ValueError(f"{names} must all be 1D tensors")
-    if data.dtype not in SUPPORTED_SPMV_VALUE_DTYPES:
+    if data.dtype not in SUPPORTED_SPMV_VALUE_DTYPES and not _half.is_half(data):
         raise TypeError(_spmv_dtype_error_message())
 
 

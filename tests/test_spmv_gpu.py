@@ -190,7 +190,7 @@ def test_spmv_prepared_and_contract_errors():
     with pytest.raises(ValueError, match="x length must be n_cols=48"):
         flagsparse_spmv_csr(d, i, p, xt, (64, 48))
     with pytest.raises(TypeError, match="data dtype must be one of"):
-        flagsparse_spmv_csr(d.half(), i, p, x.half(), (64, 48))
+        flagsparse_spmv_csr(d.to(torch.int32), i, p, x.to(torch.int32), (64, 48))
     with pytest.raises(ValueError, match="must be CUDA tensors"):
         flagsparse_spmv_csr(d.cpu(), i.cpu(), p.cpu(), x, (64, 48))
     with pytest.raises(ValueError, match="indptr must start at zero"):
