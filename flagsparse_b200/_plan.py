@@ -296,7 +296,8 @@ class CsrPlan:
         keep = torch.ones(self.nnz, dtype=torch.bool, device=self.device)
         keep[gidx] = False
         del gidx
-        data_short, idx_short = self.data[keep], self.indices[keep]
+        # (columns fit int32 here; the narrower index halves that stream and the staging buffer)
+        data_short, idx_short = self.data[keep], self.indices[keep].to(torch.int32)
         del keep
         ptr_short = torch.zeros(self.n_rows + 1, dtype=torch.int64, device=self.device)
         torch.cumsum(lens.masked_fill(long_mask, 0), 0, out=ptr_short[1:])

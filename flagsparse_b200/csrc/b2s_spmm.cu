@@ -17,6 +17,12 @@ namespace b2s {
 #ifndef B2S_SPMM_GROUP_NNZ
 #define B2S_SPMM_GROUP_NNZ 32  // entries one group of lanes takes before a row is split over more groups
 #endif
+#ifndef B2S_SPMM_CHUNK_WIDE
+#define B2S_SPMM_CHUNK_WIDE 16  // chunk length of the chunk kernel when B rows take more than 4 lanes
+#endif
+#ifndef B2S_SPMM_MINBLOCKS
+#define B2S_SPMM_MINBLOCKS 1  // CTAs per SM the register allocation of the tile kernel aims at
+#endif
 #ifndef B2S_SPMM_THREADS
 #define B2S_SPMM_THREADS 128
 #endif
@@ -242,7 +248,7 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
 // G = lanes per B row (power of two, 1..32); blockIdx.y selects the dense-column tile of
 // G * Pack::N columns when N is wider than one tile.
 template <class V, class I, class P, int THREADS, int ITEMS, bool VEC>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, B2S_SPMM_MINBLOCKS)
 spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
                  int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,
@@ -657,7 +663,8 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   // against 35 ms; banded N = 32 float32: 1.4 ms against 3.1 ms).
   const bool chunked = B2S_SPMM_CHUNKED == 1 || (B2S_SPMM_CHUNKED == 2 && G <= 4);
   if (chunked) {
-    const int CH = G >= 4 ? 16 : 4 * G;  // shorter chunks for very narrow rows: all teams busy
+    // shorter chunks for very narrow rows: all teams busy
+    const int CH = G > 4 ? B2S_SPMM_CHUNK_WIDE : (G == 4 ? 16 : 4 * G);
     const size_t smem = spmm_chunk_smem_base<ITEMS, V, I>() +
                         static_cast<size_t>(ITEMS / CH) * 2 * G * sizeof(Pack<V>);
     constexpr size_t smem_max = spmm_chunk_smem_base<ITEMS, V, I>() +
