@@ -20,9 +20,6 @@ namespace b2s {
 #ifndef B2S_SPMM_CHUNK_WIDE
 #define B2S_SPMM_CHUNK_WIDE 16  // chunk length of the chunk kernel when B rows take more than 4 lanes
 #endif
-#ifndef B2S_SPMM_MINBLOCKS
-#define B2S_SPMM_MINBLOCKS 1  // CTAs per SM the register allocation of the tile kernel aims at
-#endif
 #ifndef B2S_SPMM_THREADS
 #define B2S_SPMM_THREADS 128
 #endif
@@ -245,10 +242,25 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
   }
 }
 
+// CTAs per SM the register allocation of the tile kernel aims at.  With 4-byte column indices and
+// values of up to 8 bytes, 12 CTAs (40 registers, a few bytes of spills) measured faster than
+// the 10 the compiler settles on by itself: banded float32 N = 32 1.27 -> 1.15 ms, transposed
+// Poisson matrix N = 64 0.95 -> 0.81 ms, both pieces of the long-row split of the power-law
+// matrix 3-6 % (same box).  With 8-byte indices the same limit made the one-launch product of
+// that matrix slower (13.6 -> 15.4 ms), so those instantiations stay unconstrained.
+template <class V, class I>
+constexpr int spmm_min_blocks() {
+#ifdef B2S_SPMM_MINBLOCKS
+  return B2S_SPMM_MINBLOCKS;
+#else
+  return (sizeof(I) == 4 && sizeof(V) <= 8) ? 12 : 1;
+#endif
+}
+
 // G = lanes per B row (power of two, 1..32); blockIdx.y selects the dense-column tile of
 // G * Pack::N columns when N is wider than one tile.
 template <class V, class I, class P, int THREADS, int ITEMS, bool VEC>
-__global__ void __launch_bounds__(THREADS, B2S_SPMM_MINBLOCKS)
+__global__ void __launch_bounds__(THREADS, spmm_min_blocks<V, I>())
 spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
                  int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,

@@ -26,6 +26,9 @@
 
 namespace b2s {
 
+#ifndef B2S_SPMV_PERSISTENT
+#define B2S_SPMV_PERSISTENT 0  // 1: one CTA per resident slot walks the tiles (see the kernel)
+#endif
 #ifndef B2S_SPMV_THREADS
 #define B2S_SPMV_THREADS 128
 #endif
@@ -117,13 +120,29 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  // an earlier CTA already gave up on a copy: do not queue more waits behind it
-  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
 #ifdef B2S_PHASES
   long long tick_ = clock64();
 #endif
+  // an earlier CTA already gave up on a copy: do not queue more waits behind it
+  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+#if B2S_SPMV_PERSISTENT
+  // one CTA per slot of the GPU walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...: the
+  // CTAs resident at any time still cover a contiguous window of tiles (the x slice of a panel
+  // stays the one in L2), no CTA is launched or retired between tiles, and the plan entries of
+  // the next tile are requested while the current one is multiplied
+  const int64_t n_tiles_all = (n_rows + nnz + ITEMS - 1) / ITEMS;
+  int64_t next_r0 = tile_row[blockIdx.x], next_r1 = tile_row[blockIdx.x + 1];
+  for (int64_t t = blockIdx.x; t < n_tiles_all; t += gridDim.x) {
+  const TileCoord tc = tile_coord_from(next_r0, next_r1, t, ITEMS, n_rows + nnz);
+  if (t + gridDim.x < n_tiles_all) {
+    next_r0 = tile_row[t + gridDim.x];
+    next_r1 = tile_row[t + gridDim.x + 1];
+  }
+#else
   const int64_t t = blockIdx.x;
   const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
+  {
+#endif
   const int n_nz = static_cast<int>(tc.j1 - tc.j0);
   const int n_end = static_cast<int>(tc.r1 - tc.r0);  // rows that end in this tile
 
@@ -163,11 +182,11 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
       }
     }
 #endif
+    const uint64_t once = policy_evict_first();
+    const uint64_t keep = policy_evict_last();
     for (int k = tid; k < n_end; k += THREADS)
       row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
     if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
-    const uint64_t once = policy_evict_first();
-    const uint64_t keep = policy_evict_last();
     // column-panel layout: the matrix is a stack of panels, columns are panel-local and the
     // non-zeros of panel p start at panel_start[p]; find the panel of the tile's first entry
     int p_lo = 0;
@@ -377,6 +396,10 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   }
   if (tid == 0 && open_row) carry[t] = rsum[n_end];
   B2S_TICK(4);
+#if B2S_SPMV_PERSISTENT
+  __syncthreads();  // the next tile reuses the shared-memory buffers
+#endif
+  }
 }
 
 // Adds to each row that began in an earlier tile the partial sums those tiles left behind,
@@ -416,6 +439,20 @@ int spmv_launch(const void* data, const void* indices, const void* indptr, int64
   ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(n_tiles));
+#if B2S_SPMV_PERSISTENT
+  {
+    // as many CTAs as the device keeps resident at once
+    static int slots = 0;
+    if (slots == 0) {
+      int dev = 0, sms = 0, per_sm = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem);
+      slots = sms * (per_sm > 0 ? per_sm : 1);
+    }
+    if (n_tiles > slots) cfg.gridDim = dim3(static_cast<unsigned>(slots));
+  }
+#endif
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;

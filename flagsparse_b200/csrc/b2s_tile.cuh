@@ -11,6 +11,21 @@ struct TileCoord {
   int64_t j0, j1;  // the tile holds non-zeros j0 .. j1-1
 };
 
+// from the two plan entries of tile t (r0 = tile_row[t], r1 = tile_row[t + 1])
+__device__ inline TileCoord tile_coord_from(int64_t r0, int64_t r1, int64_t t, int items,
+                                            int64_t total) {
+  TileCoord c;
+  c.r0 = r0;
+  c.r1 = r1;
+  int64_t d0 = t * (int64_t)items;
+  if (d0 > total) d0 = total;
+  int64_t d1 = d0 + items;
+  if (d1 > total) d1 = total;
+  c.j0 = d0 - c.r0;
+  c.j1 = d1 - c.r1;
+  return c;
+}
+
 __device__ inline TileCoord tile_coord(const int64_t* __restrict__ tile_row, int64_t t,
                                        int items, int64_t total) {
   TileCoord c;
