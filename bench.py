@@ -619,6 +619,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the SpMM N=32 side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--e2e-depth", type=int, default=2,
+                    help="independent steps kept in flight in the host-buffer leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -654,7 +656,8 @@ def main():
     if args.no_e2e:
         e2e_s, h2d, d2h = float("nan"), 0, 0
     else:
-        e2e_s, h2d, d2h = time_e2e(p, kind, max(4, min(args.steps, 12)), 4)
+        e2e_s, h2d, d2h = time_e2e(p, kind, max(6, min(args.steps, 12)), 4,
+                                   depth=max(1, args.e2e_depth))
 
     extra = {"gflops": flops / per_step / 1e9, "pct_of_8tbs_nominal": 100.0 * gbs / NOMINAL_HBM_GBS,
              "algorithmic_bytes_per_step": nbytes,
@@ -726,7 +729,8 @@ def main():
                      "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale)),
                      "peak_kind": peak_kind},
         "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps_in_flight": 2},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3,
+                "steps_in_flight": max(1, args.e2e_depth)},
         "gpu_launches": (launches_per_step + extra_launches(p, kind)) * args.steps,
         "clocks": sampler.summary(),
         "extra": extra,
