@@ -362,6 +362,8 @@ def host_cores():
 def cpu_baseline(p, kind, target_seconds=12.0):
     """The oracle port timed on the sample for about target_seconds (best run), plus scipy's
     single-threaded CSR product on the same sample."""
+    import oracle
+    threads = oracle.set_threads(host_cores())
     fn, nbytes, text, scipy_fn = cpu_sample(p, kind)
     fn()  # warm the caches and the thread pool
     reps, t_total, best = 0, 0.0, float("inf")
@@ -379,7 +381,7 @@ def cpu_baseline(p, kind, target_seconds=12.0):
             scipy_fn()
         scipy_gbs = nbytes / ((time.perf_counter() - t0) / 3) / 1e9
     return {
-        "value": nbytes / best / 1e9, "unit": "GB/s", "cores": host_cores(), "kind": "port",
+        "value": nbytes / best / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
         "sample": text + f", best of {reps} runs", "scipy_1core_gbs": scipy_gbs,
     }
 
@@ -392,6 +394,9 @@ def run_reference_arm(args, rank, world):
     if rank != 0:
         return
     dev = "cuda" if torch.cuda.is_available() else "cpu"
+    import oracle
+    # all host threads, also where the launcher exported OMP_NUM_THREADS=1 for its workers
+    threads = oracle.set_threads(host_cores())
     p, kind = make_problem(args.workload, dev, args.scale, args.seed)
     fn, nbytes, text, _ = cpu_sample(p, kind)
     for _ in range(max(1, args.warmup)):
@@ -403,7 +408,7 @@ def run_reference_arm(args, rank, world):
         times.append(time.perf_counter() - t0)
     per_step = statistics.median(times)
     value = nbytes / per_step / 1e9
-    base = {"value": value, "unit": "GB/s", "cores": host_cores(), "kind": "port",
+    base = {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": text + f", median of {len(times)} runs"}
     line = {
         "impl": "reference", "metric": "effective HBM GB/s (algorithmic bytes / time)",

@@ -53,11 +53,18 @@ def _load():
         lib.orc_spmm_cplx.argtypes = lib.orc_spmm_real.argtypes
         lib.orc_transpose.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64,
                                       c_int64, c_void_p, c_void_p, c_void_p]
+        lib.orc_set_threads.argtypes = [c_int]
+        lib.orc_set_threads.restype = c_int
         for f in (lib.orc_spmv_real, lib.orc_spmv_cplx, lib.orc_spmm_real, lib.orc_spmm_cplx,
                   lib.orc_transpose):
             f.restype = None
         _lib = lib
     return _lib
+
+
+def set_threads(n=0):
+    """Ask for n OpenMP threads in the row loops (0: leave as is); returns the number in use."""
+    return int(_load().orc_set_threads(int(n)))
 
 
 def _p(a):

@@ -32,6 +32,22 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Threads of the row loops.  A launcher may have exported OMP_NUM_THREADS=1 for its worker
+ * processes (torch.distributed.run does); the timed CPU baseline asks for the host's cores
+ * explicitly.  Returns the number of threads the next call will use. */
+int orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 /* tl.sum over one block of `n` lane products: modelled as a pairwise tree over a power-of-two
  * padded block, the shape a warp-shuffle / shared-memory reduction has. */
