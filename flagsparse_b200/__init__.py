@@ -19,6 +19,7 @@ from ._plan import (
     set_long_row_policy,
     set_panel_policy,
     set_plan_cache_capacity,
+    set_window_policy,
 )
 from .spmm import (
     SPMM_OP_CONJ_TRANS,
@@ -73,6 +74,7 @@ __all__ = [
     "set_plan_cache_capacity",
     "set_panel_policy",
     "set_long_row_policy",
+    "set_window_policy",
     "SUPPORTED_VALUE_DTYPES",
     "SUPPORTED_INDEX_DTYPES",
     "SPMV_OP_NON", "SPMV_OP_TRANS", "SPMV_OP_CONJ_TRANS",

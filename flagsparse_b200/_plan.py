@@ -170,6 +170,21 @@ class PanelLayout:
         self.tiles = {}
 
 
+# Shared-memory window of B rows for SpMM on banded / local matrices (b2s_spmm_csr_windowed).
+# "auto": used when the widest column span of a tile, times the bytes of a B row, fits the
+# window the kernel can hold; "off": never.
+WINDOW_POLICY = "auto"
+WINDOW_MAX_BYTES = 32 << 10
+
+
+def set_window_policy(policy="auto"):
+    """'auto' (default) or 'off': whether SpMM may gather B from a shared-memory window."""
+    global WINDOW_POLICY
+    if policy not in ("auto", "off"):
+        raise ValueError("window policy must be 'auto' or 'off'")
+    WINDOW_POLICY = policy
+
+
 class LongRowSplit:
     """A matrix cut in two for SpMM: `short` (all rows, the long ones emptied) and `stack` (the
     long rows as a stack of column panels with global int32 columns; stacked row
@@ -204,6 +219,7 @@ class CsrPlan:
         self._transposed = {}                # conj flag -> CsrPlan of the transpose
         self._panels = False                 # False: not decided yet; None: not used
         self._long_rows = {}                 # panel shift -> LongRowSplit or None (SpMM)
+        self._window = {}                    # tile_items -> widest column span of a tile (SpMM)
         self._spmv_record = None             # prebuilt launch arguments (spmv.py)
         self._prepared = {}                  # memo of PreparedCsrSpmv handles (spmv.py)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -312,6 +328,26 @@ class CsrPlan:
         stack = CsrPlan(p_data, p_cols, p_ptr, (n_stacked, self.n_cols), -1)
         self._long_rows[shift] = LongRowSplit(short, stack, rows, subpos, n_panels, shift)
         return self._long_rows[shift]
+
+    # -- widest column span of a tile (SpMM window) ----------------------------------------------
+    def window_rows(self, items):
+        """Largest (max column - min column + 1) over the tiles of `items` merge items, measured
+        once per matrix (one pass over the column indices, one scalar read back)."""
+        hit = self._window.get(items)
+        if hit is not None:
+            return hit
+        rows = 0
+        if self.nnz > 0 and self.n_rows > 0:
+            _, tile_row = self.tiles(items)
+            out = torch.zeros(1, dtype=torch.int64, device=self.device)
+            with torch.cuda.device(self.device):
+                st = _lib.load().b2s_spmm_window_stat(
+                    self.icode, _lib.ptr(self.indices), self.n_rows, self.nnz,
+                    _lib.ptr(tile_row), items, _lib.ptr(out), _lib.stream_handle(self.device))
+            _lib.check(st, "b2s_spmm_window_stat")
+            rows = int(out.item())
+        self._window[items] = rows
+        return rows
 
     def panel_tiles(self, items):
         lay = self._panels

@@ -33,6 +33,7 @@ struct SpmmCfg {
   static constexpr int ITEMS = B2S_SPMM_ITEMS;
 };
 
+constexpr size_t kSpmmWindowMaxBytes = 32 * 1024;  // largest shared-memory window of B rows
 constexpr int kSpmmWarpRowMax = 512;
 constexpr int kSpmmQueue2Cap = 256;
 constexpr int kSpmmQueue3Cap = 8;
@@ -123,7 +124,7 @@ __device__ inline void store_raw(V* out, int64_t e0, int64_t n_dense, const Pack
 }
 
 template <int THREADS, int ITEMS, class V, class I>
-constexpr size_t spmm_smem_bytes() {
+__host__ __device__ constexpr size_t spmm_smem_bytes() {
   return 16 + sizeof(int) * (ITEMS + 4) + sizeof(I) * ITEMS + 16 + sizeof(V) * ITEMS + 16 +
          sizeof(int) * (kSpmmQueue2Cap + kSpmmQueue3Cap + 4) + 16 * THREADS;
 }
@@ -132,12 +133,24 @@ constexpr size_t spmm_smem_bytes() {
 // Four gathers of B are in flight per lane before the first multiply.
 // VEC: every lane that owns columns owns a full, 16-byte aligned pack, so a B row slice is one
 // 128-bit read-only load at Bv + col * stride16 (Bv already points at the lane's columns).
-template <class V, class I, bool VEC>
+// WIN: the rows of B the tile touches have been copied to shared memory and Bv points into that
+// window, shifted so that Bv + col * stride still is the row of column col (see the kernel);
+// loads are then ordinary shared-memory reads and `mask_col` (the first column of the window)
+// replaces column 0 as the harmless address of a masked entry.
+template <bool WIN>
+__device__ inline uint4 load_b16(const uint4* p) {
+  if constexpr (WIN)
+    return *p;
+  else
+    return __ldg(p);
+}
+
+template <class V, class I, bool VEC, bool WIN = false>
 __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
                                   const V* __restrict__ sval, int s, int e, int first, int step,
                                   const V* __restrict__ B, int64_t ldb, int64_t e0,
-                                  int64_t n_dense, const uint4* __restrict__ Bv,
-                                  int64_t stride16) {
+                                  int64_t n_dense, const uint4* Bv, int64_t stride16,
+                                  uint32_t mask_col = 0) {
   int i = s + first;
   if constexpr (VEC) {
     if (e0 >= n_dense) return;  // lane beyond the last column: nothing to add
@@ -165,15 +178,17 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
             *reinterpret_cast<uint4*>(&a4) = *reinterpret_cast<const uint4*>(sval + a);
             const bool k0 = a >= first, k1 = a + 1 >= first && a + 1 < e,
                        k2 = a + 2 >= first && a + 2 < e, k3 = a + 3 < e;
-            if (!k0) c4.x = 0;  // masked entries read row 0 of B (a valid address) and are not added
-            if (!k1) c4.y = 0;
-            if (!k2) c4.z = 0;
-            if (!k3) c4.w = 0;
+            // masked entries read a row that certainly is there (row 0 of B, or the first row
+            // of the window) and are not added
+            if (!k0) c4.x = mask_col;
+            if (!k1) c4.y = mask_col;
+            if (!k2) c4.z = mask_col;
+            if (!k3) c4.w = mask_col;
             Pack<V> b0, b1, b2, b3;
-            *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + c4.x * s32);
-            *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + c4.y * s32);
-            *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + c4.z * s32);
-            *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + c4.w * s32);
+            *reinterpret_cast<uint4*>(&b0) = load_b16<WIN>(Bv + c4.x * s32);
+            *reinterpret_cast<uint4*>(&b1) = load_b16<WIN>(Bv + c4.y * s32);
+            *reinterpret_cast<uint4*>(&b2) = load_b16<WIN>(Bv + c4.z * s32);
+            *reinterpret_cast<uint4*>(&b3) = load_b16<WIN>(Bv + c4.w * s32);
             if (k0) fma_pack(acc, a4.e[0], b0);
             if (k1) fma_pack(acc, a4.e[1], b1);
             if (k2) fma_pack(acc, a4.e[2], b2);
@@ -188,10 +203,10 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
         const uint32_t o2 = static_cast<uint32_t>(scol[i + 2 * step]) * s32;
         const uint32_t o3 = static_cast<uint32_t>(scol[i + 3 * step]) * s32;
         Pack<V> b0, b1, b2, b3;
-        *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + o0);
-        *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + o1);
-        *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + o2);
-        *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + o3);
+        *reinterpret_cast<uint4*>(&b0) = load_b16<WIN>(Bv + o0);
+        *reinterpret_cast<uint4*>(&b1) = load_b16<WIN>(Bv + o1);
+        *reinterpret_cast<uint4*>(&b2) = load_b16<WIN>(Bv + o2);
+        *reinterpret_cast<uint4*>(&b3) = load_b16<WIN>(Bv + o3);
         fma_pack(acc, sval[i], b0);
         fma_pack(acc, sval[i + step], b1);
         fma_pack(acc, sval[i + 2 * step], b2);
@@ -199,7 +214,7 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
       }
       for (; i < e; i += step) {
         Pack<V> b;
-        *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<uint32_t>(scol[i]) * s32);
+        *reinterpret_cast<uint4*>(&b) = load_b16<WIN>(Bv + static_cast<uint32_t>(scol[i]) * s32);
         fma_pack(acc, sval[i], b);
       }
       return;
@@ -248,24 +263,31 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
 // Poisson matrix N = 64 0.95 -> 0.81 ms, both pieces of the long-row split of the power-law
 // matrix 3-6 % (same box).  With 8-byte indices the same limit made the one-launch product of
 // that matrix slower (13.6 -> 15.4 ms), so those instantiations stay unconstrained.
-template <class V, class I>
+// The windowed variant holds a window of B rows per CTA (about 7 CTAs fit an SM), so it is not
+// squeezed into 40 registers.
+template <class V, class I, bool WIN = false>
 constexpr int spmm_min_blocks() {
 #ifdef B2S_SPMM_MINBLOCKS
   return B2S_SPMM_MINBLOCKS;
 #else
-  return (sizeof(I) == 4 && sizeof(V) <= 8) ? 12 : 1;
+  return WIN ? 1 : ((sizeof(I) == 4 && sizeof(V) <= 8) ? 12 : 1);
 #endif
 }
 
 // G = lanes per B row (power of two, 1..32); blockIdx.y selects the dense-column tile of
 // G * Pack::N columns when N is wider than one tile.
-template <class V, class I, class P, int THREADS, int ITEMS, bool VEC>
-__global__ void __launch_bounds__(THREADS, spmm_min_blocks<V, I>())
+// WIN (needs VEC, one dense-column tile, 32-bit row offsets): the rows of B between the smallest
+// and the largest column of the tile are copied into shared memory by one bulk copy and every
+// gather of the tile is a shared-memory read; `win_rows_cap` rows fit the buffer behind the
+// other arrays (the host has checked that no tile of the matrix spans more).
+template <class V, class I, class P, int THREADS, int ITEMS, bool VEC, bool WIN = false>
+__global__ void __launch_bounds__(THREADS, spmm_min_blocks<V, I, WIN>())
 spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
                  int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,
                  int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int small_b,
-                 int vec_c, int32_t* status) {
+                 int vec_c, int32_t* status, int win_rows_cap = 0) {
+  static_assert(!WIN || VEC, "the shared-memory window is read with 16-byte loads");
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
   int* row_end = reinterpret_cast<int*>(smem + 16);
@@ -296,6 +318,11 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     qcount[0] = 0;
     qcount[1] = 0;
     if (tx) mbar_init(bar, 1);
+    if constexpr (WIN) {
+      qcount[2] = 0x7fffffff;
+      qcount[3] = -1;
+      mbar_init(bar + 1, 1);
+    }
   }
   __syncthreads();
   if (tid == 0 && tx) {
@@ -329,6 +356,59 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(V)) / 16 : 0;
   if (VEC && small_b) stride16 = -stride16;  // flag for 32-bit row offsets (see accumulate)
   V* carry_row = carry + t * n_dense;
+  uint32_t mask_col = 0;
+  if constexpr (WIN) {
+    // smallest and largest column of the tile (qcount[2], qcount[3] were set before the barrier)
+    int lo = 0x7fffffff, hi = -1;
+    for (int k = tid; k < n_nz; k += THREADS) {
+      const int c = static_cast<int>(scol[k]);
+      lo = min(lo, c);
+      hi = max(hi, c);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, m));
+      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, m));
+    }
+    if (lane == 0 && hi >= 0) {
+      atomicMin(&qcount[2], lo);
+      atomicMax(&qcount[3], hi);
+    }
+    __syncthreads();
+    lo = qcount[2];
+    hi = qcount[3];
+    const int rows = hi >= lo ? hi - lo + 1 : 0;
+    if (rows > win_rows_cap) {  // the host sized the buffer for the widest tile: never expected
+      if (status && tid == 0) atomicOr(status, 1 << B2S_ERR_WORKSPACE);
+      return;
+    }
+    constexpr size_t win_off =
+        (spmm_smem_bytes<THREADS, ITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
+    unsigned char* win_buf = smem + win_off;
+    uint64_t* bar2 = bar + 1;
+    const uint32_t pitch = static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(V)));
+    if (rows > 0) {
+      if (tid == 0) {
+        mbar_expect_tx(bar2, static_cast<uint32_t>(rows) * pitch);
+        bulk_g2s(win_buf, B + static_cast<int64_t>(lo) * ldb, static_cast<uint32_t>(rows) * pitch,
+                 bar2, policy_evict_last());
+      }
+      if (warp == 0) {
+        if (!mbar_wait(bar2, 0)) {
+          if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
+          mbar_wait(bar2, 0);  // second bounded wait: do not leave with a copy in flight
+        }
+      }
+      __syncthreads();
+    }
+    // base such that base + col * (pitch / 16) sixteen-byte units is the lane's slice of row col
+    const uintptr_t lane_bytes = static_cast<uintptr_t>(e0 < n_dense ? e0 : 0) * sizeof(V);
+    const uintptr_t base = reinterpret_cast<uintptr_t>(win_buf) + lane_bytes -
+                           static_cast<uintptr_t>(lo) * pitch;
+    Bv = reinterpret_cast<const uint4*>(base);
+    stride16 = -(static_cast<int64_t>(pitch) / 16);
+    mask_col = static_cast<uint32_t>(lo);
+  }
 
   // groups per row piece: power of two so that each group sees at most about 16 non-zeros
   const int groups_per_warp = 32 / G;
@@ -356,7 +436,8 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
       const int len = e - s;
       Pack<V> acc = pack_zero<V>();
       if (len <= p1max) {
-        accumulate<V, I, VEC>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, Bv, stride16);
+        accumulate<V, I, VEC, WIN>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, Bv,
+                                   stride16, mask_col);
       } else if ((tid % team) == 0) {
         if (len <= kSpmmWarpRowMax) {
           const int q = atomicAdd(&qcount[0], 1);
@@ -386,8 +467,8 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     const int s = k ? row_end[k - 1] : 0;
     const int e = row_end[k];
     Pack<V> acc = pack_zero<V>();
-    accumulate<V, I, VEC>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0, n_dense, Bv,
-                          stride16);
+    accumulate<V, I, VEC, WIN>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0,
+                               n_dense, Bv, stride16, mask_col);
     for (int m = 16; m >= G; m >>= 1) acc = add_pack(acc, shfl_xor_pack(acc, m));
     if (lane < G) {
       if (k < n_end) {
@@ -407,7 +488,8 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     const int s = k ? row_end[k - 1] : 0;
     const int e = row_end[k];
     Pack<V> acc = pack_zero<V>();
-    accumulate<V, I, VEC>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, Bv, stride16);
+    accumulate<V, I, VEC, WIN>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, Bv,
+                               stride16, mask_col);
     part[tid] = acc;
     __syncthreads();
     if (tid < G) {
@@ -643,7 +725,8 @@ template <class V, class I, class P>
 int spmm_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
                 void* C, int64_t ldc, const void* alpha, const void* beta,
-                const int64_t* tile_row, void* carry, int32_t* status, cudaStream_t stream) {
+                const int64_t* tile_row, void* carry, int32_t* status, cudaStream_t stream,
+                int64_t window_rows = 0) {
   using Cfg = SpmmCfg<V, I>;
   constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
   const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
@@ -693,6 +776,19 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, true>);
     else
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, false>);
+  } else if (window_rows > 0 && vec && small_b && col_tiles == 1 &&
+             static_cast<uint64_t>(window_rows) * static_cast<uint64_t>(ldb) * sizeof(V) <=
+                 kSpmmWindowMaxBytes) {
+    // the B rows of every tile fit a shared-memory window: gather from there
+    constexpr size_t base = (spmm_smem_bytes<THREADS, ITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
+    const size_t smem = base + static_cast<size_t>(window_rows) * static_cast<size_t>(ldb) * sizeof(V);
+    auto kern = spmm_tile_kernel<V, I, P, THREADS, ITEMS, true, true>;
+    ensure_dyn_smem(reinterpret_cast<const void*>(kern), base + kSpmmWindowMaxBytes);
+    kern<<<grid, THREADS, smem, stream>>>(
+        static_cast<const V*>(data), static_cast<const I*>(indices),
+        static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
+        static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
+        n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, static_cast<int>(window_rows));
   } else {
     constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
     auto launch = [&](auto kern) {
@@ -701,7 +797,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
           static_cast<const V*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
           static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-          n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status);
+          n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0);
     };
     if (vec)
       launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true>);
@@ -725,12 +821,107 @@ extern "C" int b2s_spmm_tile_items(int val_type, int idx_type) {
   return b2s::SpmmCfg<float, int32_t>::ITEMS;
 }
 
+namespace b2s {
+
+// Widest column span (largest - smallest column + 1) over the tiles of a matrix: one CTA per
+// tile, a block-wide min / max of the tile's column indices, one atomicMax per tile.
+template <class I>
+__global__ void __launch_bounds__(256)
+    spmm_window_stat_kernel(const I* __restrict__ col, const int64_t* __restrict__ tile_row,
+                            int64_t n_rows, int64_t nnz, int items,
+                            unsigned long long* __restrict__ widest) {
+  __shared__ long long s_lo[8], s_hi[8];
+  const TileCoord tc = tile_coord(tile_row, blockIdx.x, items, n_rows + nnz);
+  long long lo = INT64_MAX, hi = -1;
+  for (int64_t j = tc.j0 + threadIdx.x; j < tc.j1; j += blockDim.x) {
+    const long long c = static_cast<long long>(col[j]);
+    lo = c < lo ? c : lo;
+    hi = c > hi ? c : hi;
+  }
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) {
+    const long long ol = __shfl_xor_sync(0xffffffffu, lo, m);
+    const long long oh = __shfl_xor_sync(0xffffffffu, hi, m);
+    lo = ol < lo ? ol : lo;
+    hi = oh > hi ? oh : hi;
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_lo[threadIdx.x >> 5] = lo;
+    s_hi[threadIdx.x >> 5] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) {
+      lo = s_lo[w] < lo ? s_lo[w] : lo;
+      hi = s_hi[w] > hi ? s_hi[w] : hi;
+    }
+    if (hi >= lo) atomicMax(widest, static_cast<unsigned long long>(hi - lo + 1));
+  }
+}
+
+__global__ void spmm_window_zero_kernel(unsigned long long* widest) { *widest = 0ull; }
+
+}  // namespace b2s
+
+extern "C" int b2s_spmm_window_stat(int idx_type, const void* indices_dev, int64_t n_rows,
+                                    int64_t nnz, const int64_t* tile_row_dev, int tile_items,
+                                    int64_t* widest_dev, b2s_stream stream) {
+  if (n_rows < 0 || nnz < 0 || tile_items <= 0 || !widest_dev) return B2S_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned long long* out = reinterpret_cast<unsigned long long*>(widest_dev);
+  b2s::spmm_window_zero_kernel<<<1, 1, 0, s>>>(out);
+  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, tile_items);
+  if (n_tiles == 0 || nnz == 0) return b2s::launch_status();
+  if (!indices_dev || !tile_row_dev) return B2S_ERR_ARG;
+  if (n_tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
+  B2S_DISPATCH_I(idx_type, I, {
+    (b2s::spmm_window_stat_kernel<I><<<static_cast<unsigned>(n_tiles), 256, 0, s>>>(
+        static_cast<const I*>(indices_dev), tile_row_dev, n_rows, nnz, tile_items, out));
+  });
+  return b2s::launch_status();
+}
+
+static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                        const void* indices_dev, const void* indptr_dev, int64_t n_rows,
+                        int64_t n_cols, int64_t nnz, const void* B_dev, int64_t ldb,
+                        int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
+                        const void* alpha, const void* beta, const int64_t* tile_row_dev,
+                        void* carry_dev, int32_t* status_dev, b2s_stream stream,
+                        int64_t window_rows);
+
 extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void* data_dev,
                             const void* indices_dev, const void* indptr_dev, int64_t n_rows,
                             int64_t n_cols, int64_t nnz, const void* B_dev, int64_t ldb,
                             int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
                             const void* alpha, const void* beta, const int64_t* tile_row_dev,
                             void* carry_dev, int32_t* status_dev, b2s_stream stream) {
+  return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
+                      n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, alpha, beta,
+                      tile_row_dev, carry_dev, status_dev, stream, 0);
+}
+
+extern "C" int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
+                                     const void* data_dev, const void* indices_dev,
+                                     const void* indptr_dev, int64_t n_rows, int64_t n_cols,
+                                     int64_t nnz, const void* B_dev, int64_t ldb, int64_t n_dense,
+                                     const void* C_in_dev, void* C_dev, int64_t ldc,
+                                     const void* alpha, const void* beta,
+                                     const int64_t* tile_row_dev, void* carry_dev,
+                                     int32_t* status_dev, int64_t window_rows,
+                                     b2s_stream stream) {
+  if (window_rows < 0 || window_rows > 0x7fffffffLL) return B2S_ERR_ARG;
+  return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
+                      n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, alpha, beta,
+                      tile_row_dev, carry_dev, status_dev, stream, window_rows);
+}
+
+static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* data_dev,
+                        const void* indices_dev, const void* indptr_dev, int64_t n_rows,
+                        int64_t n_cols, int64_t nnz, const void* B_dev, int64_t ldb,
+                        int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
+                        const void* alpha, const void* beta, const int64_t* tile_row_dev,
+                        void* carry_dev, int32_t* status_dev, b2s_stream stream,
+                        int64_t window_rows) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0 || n_dense < 0 || !alpha || !beta) return B2S_ERR_ARG;
   if (n_rows == 0 || n_dense == 0) return B2S_OK;
   if (ldb < n_dense || ldc < n_dense) return B2S_ERR_ARG;
@@ -747,7 +938,7 @@ extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void
   B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
     return (b2s::spmm_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, B_dev, ldb,
                                       n_dense, C_in_dev, C_dev, ldc, alpha, beta, tile_row_dev,
-                                      carry_dev, status_dev, s));
+                                      carry_dev, status_dev, s, window_rows));
   })));
   return B2S_ERR_DTYPE;
 }

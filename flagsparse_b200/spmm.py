@@ -27,6 +27,7 @@ from ._contract import (
     op_name,
     op_transposes,
 )
+from . import _plan as _plan_mod
 from ._plan import (
     ST_DECREASING,
     ST_MAXCOL,
@@ -185,14 +186,22 @@ def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
     dtype = plan.data.dtype
     a = _lib.scalar_buffer(alpha, dtype)
     b = _lib.scalar_buffer(beta, dtype)
+    # banded / local matrices: when the B rows of every tile fit a shared-memory window the
+    # kernel copies them there once per tile and gathers from shared memory
+    window = 0
+    pitch = int(B.stride(0)) * B.element_size()
+    if _plan_mod.WINDOW_POLICY == "auto" and 0 < pitch <= _plan_mod.WINDOW_MAX_BYTES:
+        rows = plan.window_rows(items)
+        if 0 < rows * pitch <= _plan_mod.WINDOW_MAX_BYTES:
+            window = rows
     with torch.cuda.device(plan.device):
-        st = lib.b2s_spmm_csr(
+        st = lib.b2s_spmm_csr_windowed(
             plan.vcode, plan.icode, plan.pcode,
             _lib.ptr(plan.data), _lib.ptr(plan.indices), _lib.ptr(plan.indptr),
             plan.n_rows, plan.n_cols, plan.nnz,
             _lib.ptr(B), int(B.stride(0)), n_dense,
             _lib.ptr(C_in), _lib.ptr(C), int(C.stride(0)), a, b,
-            _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status),
+            _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status), window,
             _lib.stream_handle(plan.device))
     _lib.check(st, "b2s_spmm_csr")
     if not plan.status_checked:

@@ -300,3 +300,75 @@ def test_long_row_split_is_not_taken_for_small_or_uniform_matrices():
     data, idx, ptr = csr_from_lengths(rng, rng.integers(0, 20, 500), 300, np.float32)
     plan = _plan.CsrPlan(dev(data), dev(idx, torch.int32), dev(ptr, torch.int64), (500, 300), 19)
     assert plan.long_row_split(1 << 20) is None
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.complex64], ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("n_dense", [4, 32, 64])
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64], ids=["i32", "i64"])
+def test_spmm_banded_matrix_uses_the_shared_memory_window(dtype, n_dense, idx_dtype):
+    """A banded matrix (unsorted columns inside the band, empty rows, one dense row piece) whose
+    tiles span few columns: B rows come from the shared-memory window.  Same additions in the
+    same order as the plain kernel, so the two results are equal bit for bit."""
+    from flagsparse_b200 import _plan, clear_plan_cache, flagsparse_spmm_csr, set_window_policy
+    rng = np.random.default_rng(300 + n_dense)
+    n, band = 3000, 10
+    rows, cols = [], []
+    for r in range(n):
+        if r % 97 == 5:
+            continue                                   # empty row
+        lo, hi = max(0, r - band), min(n, r + band)
+        k = hi - lo if r == 1500 else int(rng.integers(8, 21))
+        c = rng.choice(np.arange(lo, hi), size=min(k, hi - lo), replace=False)
+        rows.append(np.full(c.size, r))
+        cols.append(c)                                 # not sorted
+    rows, cols = np.concatenate(rows), np.concatenate(cols)
+    ptr = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(np.bincount(rows, minlength=n), out=ptr[1:])
+    data = random_values(rng, cols.size, dtype)
+    B = random_values(rng, n * n_dense, dtype).reshape(n, n_dense)
+    C0 = random_values(rng, n * n_dense, dtype).reshape(n, n_dense)
+    d, i, p = dev(data), dev(cols, idx_dtype), dev(ptr, torch.int64)
+    clear_plan_cache()
+    set_window_policy("auto")
+    try:
+        out = dev(C0)
+        flagsparse_spmm_csr(d, i, p, dev(B), (n, n), out=out, alpha=0.5, beta=-1.5)
+        plan = _plan.cache_get(_plan.plan_key("spmm", d, i, p, (n, n)))
+        span = plan.window_rows(1024)
+        assert 0 < span < 200
+        if n_dense * data.itemsize <= 256:   # wider B rows do not fit and take the plain kernel
+            assert span * n_dense * data.itemsize <= _plan.WINDOW_MAX_BYTES
+        expect = oracle.spmm(data, cols, ptr, B, (n, n), alpha=0.5, beta=-1.5, C0=C0)
+        assert_parity(host(out), expect, dtype)
+        C = flagsparse_spmm_csr(d, i, p, dev(B), (n, n))
+        set_window_policy("off")
+        clear_plan_cache()
+        plain = flagsparse_spmm_csr(d, i, p, dev(B), (n, n))
+        assert torch.equal(C.view(torch.uint8), plain.view(torch.uint8))
+    finally:
+        set_window_policy("auto")
+        clear_plan_cache()
+
+
+def test_spmm_window_stat_entry_point():
+    from flagsparse_b200 import _lib as L
+    from flagsparse_b200._plan import CsrPlan
+    lib = L.load()
+    rng = np.random.default_rng(9)
+    data, idx, ptr = csr_from_lengths(rng, rng.integers(0, 9, 4000), 5000, np.float32)
+    plan = CsrPlan(dev(data), dev(idx, torch.int64), dev(ptr, torch.int64), (4000, 5000), 8)
+    n_tiles, tile_row = plan.tiles(1024)
+    widest = 0
+    tr = host(tile_row)
+    total = 4000 + data.size
+    for t in range(n_tiles):
+        j0 = min(t * 1024, total) - tr[t]
+        j1 = min((t + 1) * 1024, total) - tr[t + 1]
+        if j1 > j0:
+            widest = max(widest, int(idx[j0:j1].max() - idx[j0:j1].min() + 1))
+    assert plan.window_rows(1024) == widest
+    out = torch.zeros(1, dtype=torch.int64, device="cuda")
+    stream = L.stream_handle(out.device)
+    assert lib.b2s_spmm_window_stat(1, None, 0, 0, None, 1024, L.ptr(out), stream) == 0
+    assert lib.b2s_spmm_window_stat(1, None, 4, 4, None, 1024, L.ptr(out), stream) == 2
+    assert lib.b2s_spmm_window_stat(1, None, 4, 4, None, 1024, None, stream) == 2
