@@ -81,9 +81,9 @@ SIGNATURES = {
     "b2s_spmm_csr_windowed": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                       c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_int64, c_void_p]),
+                                      c_void_p, c_int64, c_void_p, c_void_p]),
     "b2s_spmm_window_stat": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p,
-                                     c_void_p]),
+                                     c_void_p, c_void_p]),
     "b2s_csr2csc_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "b2s_csr2csc": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                             c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

@@ -333,21 +333,29 @@ class CsrPlan:
     def window_rows(self, items):
         """Largest (max column - min column + 1) over the tiles of `items` merge items, measured
         once per matrix (one pass over the column indices, one scalar read back)."""
+        return self.window(items)[0]
+
+    def window(self, items):
+        """(widest span, int32[2 * tiles] table of first column and span per tile or None)."""
         hit = self._window.get(items)
         if hit is not None:
             return hit
-        rows = 0
+        rows, table = 0, None
         if self.nnz > 0 and self.n_rows > 0:
-            _, tile_row = self.tiles(items)
+            n_tiles, tile_row = self.tiles(items)
             out = torch.zeros(1, dtype=torch.int64, device=self.device)
+            table = torch.zeros(2 * n_tiles, dtype=torch.int32, device=self.device)
             with torch.cuda.device(self.device):
                 st = _lib.load().b2s_spmm_window_stat(
                     self.icode, _lib.ptr(self.indices), self.n_rows, self.nnz,
-                    _lib.ptr(tile_row), items, _lib.ptr(out), _lib.stream_handle(self.device))
+                    _lib.ptr(tile_row), items, _lib.ptr(out), _lib.ptr(table),
+                    _lib.stream_handle(self.device))
             _lib.check(st, "b2s_spmm_window_stat")
             rows = int(out.item())
-        self._window[items] = rows
-        return rows
+            if rows * 16 > WINDOW_MAX_BYTES:   # no B row is narrower than 16 bytes: never used
+                table = None
+        self._window[items] = (rows, table)
+        return self._window[items]
 
     def panel_tiles(self, items):
         lay = self._panels

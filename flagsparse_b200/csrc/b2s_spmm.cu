@@ -286,7 +286,8 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
                  const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
                  int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,
                  int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int small_b,
-                 int vec_c, int32_t* status, int win_rows_cap = 0) {
+                 int vec_c, int32_t* status, int win_rows_cap = 0,
+                 const int32_t* __restrict__ tile_win = nullptr) {
   static_assert(!WIN || VEC, "the shared-memory window is read with 16-byte loads");
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
@@ -317,19 +318,39 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   if (tid == 0) {
     qcount[0] = 0;
     qcount[1] = 0;
-    if (tx) mbar_init(bar, 1);
-    if constexpr (WIN) {
-      qcount[2] = 0x7fffffff;
-      qcount[3] = -1;
-      mbar_init(bar + 1, 1);
+    if (tx || WIN) mbar_init(bar, 1);
+  }
+  // WIN: first column and number of B rows of this tile's window, from the plan; the window is
+  // requested together with col / val, on the same barrier
+  int win_lo = 0, win_rows = 0;
+  uint32_t win_bytes = 0;
+  constexpr size_t win_off =
+      (spmm_smem_bytes<THREADS, ITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
+  if constexpr (WIN) {
+    win_lo = tile_win[2 * t];
+    win_rows = tile_win[2 * t + 1];
+    if (win_rows > win_rows_cap || win_rows < 0) {  // the host sized the buffer: never expected
+      if (status && tid == 0) atomicOr(status, 1 << B2S_ERR_WORKSPACE);
+      return;
     }
+    // whole rows but for the last one, of which only the n_dense values are read (B may be a
+    // view whose last row has nothing behind it)
+    if (win_rows > 0)
+      win_bytes = static_cast<uint32_t>(win_rows - 1) *
+                      static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(V))) +
+                  static_cast<uint32_t>(n_dense * static_cast<int64_t>(sizeof(V)));
   }
   __syncthreads();
-  if (tid == 0 && tx) {
+  if (tid == 0 && (tx || win_bytes)) {
     const uint64_t pol = policy_evict_first();
-    mbar_expect_tx(bar, tx);
+    mbar_expect_tx(bar, tx + win_bytes);
     stage_issue(sc, gcol, bar, pol);
     stage_issue(sv, gval, bar, pol);
+    if constexpr (WIN) {
+      if (win_bytes)
+        bulk_g2s(smem + win_off, B + static_cast<int64_t>(win_lo) * ldb, win_bytes, bar,
+                 policy_evict_last());
+    }
   }
   stage_edges(sc, gcol, n_nz, tid, THREADS);
   stage_edges(sv, gval, n_nz, tid, THREADS);
@@ -337,7 +358,7 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
   if (tid == 0) row_end[n_end] = n_nz;
   // one warp waits for the copies; the CTA barrier that follows releases everybody else
-  if (tx && warp == 0) {
+  if ((tx || win_bytes) && warp == 0) {
     if (!mbar_wait(bar, 0)) {
       if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
       mbar_wait(bar, 0);  // second bounded wait: do not leave with a copy in flight
@@ -358,56 +379,14 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   V* carry_row = carry + t * n_dense;
   uint32_t mask_col = 0;
   if constexpr (WIN) {
-    // smallest and largest column of the tile (qcount[2], qcount[3] were set before the barrier)
-    int lo = 0x7fffffff, hi = -1;
-    for (int k = tid; k < n_nz; k += THREADS) {
-      const int c = static_cast<int>(scol[k]);
-      lo = min(lo, c);
-      hi = max(hi, c);
-    }
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) {
-      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, m));
-      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, m));
-    }
-    if (lane == 0 && hi >= 0) {
-      atomicMin(&qcount[2], lo);
-      atomicMax(&qcount[3], hi);
-    }
-    __syncthreads();
-    lo = qcount[2];
-    hi = qcount[3];
-    const int rows = hi >= lo ? hi - lo + 1 : 0;
-    if (rows > win_rows_cap) {  // the host sized the buffer for the widest tile: never expected
-      if (status && tid == 0) atomicOr(status, 1 << B2S_ERR_WORKSPACE);
-      return;
-    }
-    constexpr size_t win_off =
-        (spmm_smem_bytes<THREADS, ITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
-    unsigned char* win_buf = smem + win_off;
-    uint64_t* bar2 = bar + 1;
     const uint32_t pitch = static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(V)));
-    if (rows > 0) {
-      if (tid == 0) {
-        mbar_expect_tx(bar2, static_cast<uint32_t>(rows) * pitch);
-        bulk_g2s(win_buf, B + static_cast<int64_t>(lo) * ldb, static_cast<uint32_t>(rows) * pitch,
-                 bar2, policy_evict_last());
-      }
-      if (warp == 0) {
-        if (!mbar_wait(bar2, 0)) {
-          if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
-          mbar_wait(bar2, 0);  // second bounded wait: do not leave with a copy in flight
-        }
-      }
-      __syncthreads();
-    }
     // base such that base + col * (pitch / 16) sixteen-byte units is the lane's slice of row col
     const uintptr_t lane_bytes = static_cast<uintptr_t>(e0 < n_dense ? e0 : 0) * sizeof(V);
-    const uintptr_t base = reinterpret_cast<uintptr_t>(win_buf) + lane_bytes -
-                           static_cast<uintptr_t>(lo) * pitch;
+    const uintptr_t base = reinterpret_cast<uintptr_t>(smem + win_off) + lane_bytes -
+                           static_cast<uintptr_t>(win_lo) * pitch;
     Bv = reinterpret_cast<const uint4*>(base);
     stride16 = -(static_cast<int64_t>(pitch) / 16);
-    mask_col = static_cast<uint32_t>(lo);
+    mask_col = static_cast<uint32_t>(win_lo);
   }
 
   // groups per row piece: power of two so that each group sees at most about 16 non-zeros
@@ -726,7 +705,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
                 int64_t n_cols, int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
                 void* C, int64_t ldc, const void* alpha, const void* beta,
                 const int64_t* tile_row, void* carry, int32_t* status, cudaStream_t stream,
-                int64_t window_rows = 0) {
+                int64_t window_rows = 0, const int32_t* tile_win = nullptr) {
   using Cfg = SpmmCfg<V, I>;
   constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
   const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
@@ -776,7 +755,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, true>);
     else
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, false>);
-  } else if (window_rows > 0 && vec && small_b && col_tiles == 1 &&
+  } else if (window_rows > 0 && tile_win != nullptr && vec && small_b && col_tiles == 1 &&
              static_cast<uint64_t>(window_rows) * static_cast<uint64_t>(ldb) * sizeof(V) <=
                  kSpmmWindowMaxBytes) {
     // the B rows of every tile fit a shared-memory window: gather from there
@@ -788,7 +767,8 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
         static_cast<const V*>(data), static_cast<const I*>(indices),
         static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
         static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-        n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, static_cast<int>(window_rows));
+        n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, static_cast<int>(window_rows),
+        tile_win);
   } else {
     constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
     auto launch = [&](auto kern) {
@@ -797,7 +777,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
           static_cast<const V*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
           static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-          n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0);
+          n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0, nullptr);
     };
     if (vec)
       launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true>);
@@ -829,7 +809,8 @@ template <class I>
 __global__ void __launch_bounds__(256)
     spmm_window_stat_kernel(const I* __restrict__ col, const int64_t* __restrict__ tile_row,
                             int64_t n_rows, int64_t nnz, int items,
-                            unsigned long long* __restrict__ widest) {
+                            unsigned long long* __restrict__ widest,
+                            int32_t* __restrict__ tile_win) {
   __shared__ long long s_lo[8], s_hi[8];
   const TileCoord tc = tile_coord(tile_row, blockIdx.x, items, n_rows + nnz);
   long long lo = INT64_MAX, hi = -1;
@@ -855,7 +836,14 @@ __global__ void __launch_bounds__(256)
       lo = s_lo[w] < lo ? s_lo[w] : lo;
       hi = s_hi[w] > hi ? s_hi[w] : hi;
     }
-    if (hi >= lo) atomicMax(widest, static_cast<unsigned long long>(hi - lo + 1));
+    const long long span = hi >= lo ? hi - lo + 1 : 0;
+    if (span > 0) atomicMax(widest, static_cast<unsigned long long>(span));
+    if (tile_win != nullptr) {  // first column and rows of the tile's window (0 rows: no entries)
+      const bool fits = span > 0 && hi <= 0x7fffffffLL;
+      tile_win[2 * static_cast<int64_t>(blockIdx.x)] = fits ? static_cast<int32_t>(lo) : 0;
+      tile_win[2 * static_cast<int64_t>(blockIdx.x) + 1] =
+          fits ? static_cast<int32_t>(span) : (span > 0 ? 0x7fffffff : 0);
+    }
   }
 }
 
@@ -865,7 +853,8 @@ __global__ void spmm_window_zero_kernel(unsigned long long* widest) { *widest = 
 
 extern "C" int b2s_spmm_window_stat(int idx_type, const void* indices_dev, int64_t n_rows,
                                     int64_t nnz, const int64_t* tile_row_dev, int tile_items,
-                                    int64_t* widest_dev, b2s_stream stream) {
+                                    int64_t* widest_dev, int32_t* tile_win_dev,
+                                    b2s_stream stream) {
   if (n_rows < 0 || nnz < 0 || tile_items <= 0 || !widest_dev) return B2S_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned long long* out = reinterpret_cast<unsigned long long*>(widest_dev);
@@ -876,7 +865,8 @@ extern "C" int b2s_spmm_window_stat(int idx_type, const void* indices_dev, int64
   if (n_tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
   B2S_DISPATCH_I(idx_type, I, {
     (b2s::spmm_window_stat_kernel<I><<<static_cast<unsigned>(n_tiles), 256, 0, s>>>(
-        static_cast<const I*>(indices_dev), tile_row_dev, n_rows, nnz, tile_items, out));
+        static_cast<const I*>(indices_dev), tile_row_dev, n_rows, nnz, tile_items, out,
+        tile_win_dev));
   });
   return b2s::launch_status();
 }
@@ -887,7 +877,7 @@ static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* da
                         int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
                         const void* alpha, const void* beta, const int64_t* tile_row_dev,
                         void* carry_dev, int32_t* status_dev, b2s_stream stream,
-                        int64_t window_rows);
+                        int64_t window_rows, const int32_t* tile_win_dev);
 
 extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void* data_dev,
                             const void* indices_dev, const void* indptr_dev, int64_t n_rows,
@@ -897,7 +887,7 @@ extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void
                             void* carry_dev, int32_t* status_dev, b2s_stream stream) {
   return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
                       n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, alpha, beta,
-                      tile_row_dev, carry_dev, status_dev, stream, 0);
+                      tile_row_dev, carry_dev, status_dev, stream, 0, nullptr);
 }
 
 extern "C" int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
@@ -908,11 +898,12 @@ extern "C" int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
                                      const void* alpha, const void* beta,
                                      const int64_t* tile_row_dev, void* carry_dev,
                                      int32_t* status_dev, int64_t window_rows,
-                                     b2s_stream stream) {
+                                     const int32_t* tile_win_dev, b2s_stream stream) {
   if (window_rows < 0 || window_rows > 0x7fffffffLL) return B2S_ERR_ARG;
+  if (window_rows > 0 && !tile_win_dev) return B2S_ERR_ARG;
   return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
                       n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, alpha, beta,
-                      tile_row_dev, carry_dev, status_dev, stream, window_rows);
+                      tile_row_dev, carry_dev, status_dev, stream, window_rows, tile_win_dev);
 }
 
 static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* data_dev,
@@ -921,7 +912,7 @@ static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* da
                         int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
                         const void* alpha, const void* beta, const int64_t* tile_row_dev,
                         void* carry_dev, int32_t* status_dev, b2s_stream stream,
-                        int64_t window_rows) {
+                        int64_t window_rows, const int32_t* tile_win_dev) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0 || n_dense < 0 || !alpha || !beta) return B2S_ERR_ARG;
   if (n_rows == 0 || n_dense == 0) return B2S_OK;
   if (ldb < n_dense || ldc < n_dense) return B2S_ERR_ARG;
@@ -938,7 +929,7 @@ static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* da
   B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
     return (b2s::spmm_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, B_dev, ldb,
                                       n_dense, C_in_dev, C_dev, ldc, alpha, beta, tile_row_dev,
-                                      carry_dev, status_dev, s, window_rows));
+                                      carry_dev, status_dev, s, window_rows, tile_win_dev));
   })));
   return B2S_ERR_DTYPE;
 }

@@ -188,11 +188,11 @@ def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
     b = _lib.scalar_buffer(beta, dtype)
     # banded / local matrices: when the B rows of every tile fit a shared-memory window the
     # kernel copies them there once per tile and gathers from shared memory
-    window = 0
+    window, table = 0, None
     pitch = int(B.stride(0)) * B.element_size()
     if _plan_mod.WINDOW_POLICY == "auto" and 0 < pitch <= _plan_mod.WINDOW_MAX_BYTES:
-        rows = plan.window_rows(items)
-        if 0 < rows * pitch <= _plan_mod.WINDOW_MAX_BYTES:
+        rows, table = plan.window(items)
+        if table is not None and 0 < rows * pitch <= _plan_mod.WINDOW_MAX_BYTES:
             window = rows
     with torch.cuda.device(plan.device):
         st = lib.b2s_spmm_csr_windowed(
@@ -202,7 +202,7 @@ def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
             _lib.ptr(B), int(B.stride(0)), n_dense,
             _lib.ptr(C_in), _lib.ptr(C), int(C.stride(0)), a, b,
             _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status), window,
-            _lib.stream_handle(plan.device))
+            _lib.ptr(table) if window else None, _lib.stream_handle(plan.device))
     _lib.check(st, "b2s_spmm_csr")
     if not plan.status_checked:
         plan.check_status()

@@ -256,13 +256,14 @@ int b2s_spmm_csr(int val_type, int idx_type, int ptr_type,
  * tile_items merge items lie within a narrow span, the rows of B a tile needs are one contiguous
  * block; b2s_spmm_csr_windowed copies that block into shared memory with one bulk copy per tile
  * and gathers from there instead of from L1 / L2.  b2s_spmm_window_stat writes to *widest_dev
- * the widest column span (largest - smallest column + 1) over the tiles of the matrix; the
- * caller passes it (or 0 = no window) as window_rows.  The window is used when it fits
+ * the widest column span (largest - smallest column + 1) over the tiles of the matrix and, when
+ * tile_win_dev is not NULL, to tile_win_dev[2t], [2t + 1] the first column and the span of
+ * tile t (b2s_tile_count tiles); the caller passes both on (window_rows = 0: no window).  The window is used when it fits
  * (window_rows * ldb * value size <= 32 KB), B and C are 16-byte aligned with whole 16-byte
  * packs per row, and N fits one dense-column tile; otherwise the call is b2s_spmm_csr. */
 int b2s_spmm_window_stat(int idx_type, const void* indices_dev, int64_t n_rows, int64_t nnz,
                          const int64_t* tile_row_dev, int tile_items, int64_t* widest_dev,
-                         b2s_stream stream);
+                         int32_t* tile_win_dev, b2s_stream stream);
 int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
                           const void* data_dev, const void* indices_dev, const void* indptr_dev,
                           int64_t n_rows, int64_t n_cols, int64_t nnz,
@@ -270,7 +271,7 @@ int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
                           const void* C_in_dev, void* C_dev, int64_t ldc,
                           const void* alpha, const void* beta,
                           const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
-                          int64_t window_rows, b2s_stream stream);
+                          int64_t window_rows, const int32_t* tile_win_dev, b2s_stream stream);
 
 /* Long rows of a power-law matrix by column panel (no counterpart in the reference).  On random
  * columns SpMM gathers one row of B per non-zero from DRAM.  The host side splits the matrix:
