@@ -735,7 +735,11 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   // power-law matrix, N = 16: 30 ms against 40 ms).  Wider rows: the team-per-row kernel, whose
   // smaller footprint keeps more CTAs resident (N = 32 float64 on the 2^24-row matrix: 18.5 ms
   // against 35 ms; banded N = 32 float32: 1.4 ms against 3.1 ms).
-  const bool chunked = B2S_SPMM_CHUNKED == 1 || (B2S_SPMM_CHUNKED == 2 && G <= 4);
+  // With 4-byte column indices the team-per-row kernel (12 CTAs per SM) is the faster one for
+  // narrow rows too: the two pieces of the long-row split of that matrix, N = 16, take
+  // 18.7 + 4.8 ms against 21.1 + 9.8 ms with the chunk kernel.
+  const bool chunked =
+      B2S_SPMM_CHUNKED == 1 || (B2S_SPMM_CHUNKED == 2 && G <= 4 && sizeof(I) == 8);
   if (chunked) {
     // shorter chunks for very narrow rows: all teams busy
     const int CH = G > 4 ? B2S_SPMM_CHUNK_WIDE : (G == 4 ? 16 : 4 * G);
