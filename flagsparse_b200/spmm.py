@@ -144,6 +144,10 @@ def _checked_spmm_plan(data, indices, indptr, shape):
             # kept for drop-in behaviour (spmm_csr.py:280-283); the kernels themselves take int64
             raise ValueError(
                 "column indices exceed the int32 range supported by the Triton kernel")
+    if i.dtype == torch.int64:
+        # the columns fit int32 (checked above); like the reference (spmm_csr.py:289) the kernels
+        # read a narrowed copy: half the index stream, smaller staging buffers, more CTAs per SM
+        i = i.to(torch.int32)
     plan = CsrPlan(d, i, p, (n_rows, n_cols), stats[ST_MAXLEN],
                    keepalive=(data, indices, indptr))
     cache_put(key, plan)
