@@ -341,6 +341,12 @@ def test_spmm_banded_matrix_uses_the_shared_memory_window(dtype, n_dense, idx_dt
         expect = oracle.spmm(data, cols, ptr, B, (n, n), alpha=0.5, beta=-1.5, C0=C0)
         assert_parity(host(out), expect, dtype)
         C = flagsparse_spmm_csr(d, i, p, dev(B), (n, n))
+        # B as a view with a wider pitch (whole 16-byte packs): the window copies pitch-sized
+        # rows but for the last one
+        pad = 16 // data.itemsize
+        wide = torch.zeros((n, n_dense + pad), dtype=C.dtype, device="cuda")
+        wide[:, :n_dense] = dev(B)
+        assert torch.equal(flagsparse_spmm_csr(d, i, p, wide[:, :n_dense], (n, n)), C)
         set_window_policy("off")
         clear_plan_cache()
         plain = flagsparse_spmm_csr(d, i, p, dev(B), (n, n))
