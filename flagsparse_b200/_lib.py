@@ -54,9 +54,6 @@ SIGNATURES = {
     "b2s_panel_build_global": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_int64, c_void_p]),
-    "b2s_panel_pack": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
-    "b2s_panel_combine_packed": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int,
-                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2s_spmv_panels": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

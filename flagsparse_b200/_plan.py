@@ -166,7 +166,6 @@ class PanelLayout:
         self.n_panels, self.shift = n_panels, shift
         self.n_stacked = int(n_stacked)     # rows of the stack the kernel sees
         self.subpos = subpos                # int32[n_panels * n_rows] or None (nothing dropped)
-        self.mask = self.base = None        # packed form of subpos (b2s_panel_pack), if built
         self.pcode = _lib.INDEX_CODE[ptr.dtype]
         self.tiles = {}
 
@@ -278,17 +277,6 @@ class CsrPlan:
             global_cols=False)
         self._panels = PanelLayout(p_data, p_cols, p_ptr, panel_start, n_panels, shift,
                                    n_stacked, subpos)
-        if subpos is not None:
-            # the combine reads the positions packed as a bit mask and a base per 32 rows
-            words = (self.n_rows + 31) // 32
-            mask = torch.empty(n_panels * words, dtype=torch.int32, device=self.device)
-            base = torch.empty(n_panels * words, dtype=torch.int32, device=self.device)
-            with torch.cuda.device(self.device):
-                st = _lib.load().b2s_panel_pack(_lib.ptr(subpos), self.n_rows, n_panels,
-                                                _lib.ptr(mask), _lib.ptr(base),
-                                                _lib.stream_handle(self.device))
-            _lib.check(st, "b2s_panel_pack")
-            self._panels.mask, self._panels.base = mask, base
         return self._panels
 
     # -- long rows by column panel (SpMM) --------------------------------------------------------

@@ -564,49 +564,6 @@ __global__ void peer_scatter_kernel(const uint4* __restrict__ src, int64_t n16, 
   }
 }
 
-// The position table packed: for panel p and the 32 rows of word w, mask[p * W + w] has bit b set
-// when (p, row 32 w + b) is a non-empty stacked row, and base[p * W + w] is the position of the
-// first such row; the position of any other is base + (number of set bits below b).  8 bytes
-// per 32 rows and panel instead of 128: the combine reads 16 MB instead of 268 MB of table on
-// the 2^24-row matrix with 4 panels.
-__global__ void __launch_bounds__(256)
-    panel_pack_kernel(const int32_t* __restrict__ subpos, int64_t n_rows, int n_panels,
-                      int64_t words, uint32_t* __restrict__ mask, int32_t* __restrict__ base) {
-  const int64_t warp_id = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp_id >= words * n_panels) return;  // whole warps leave together
-  const int64_t p = warp_id / words, w = warp_id - p * words;
-  const int64_t r = w * 32 + lane;
-  const int32_t c = r < n_rows ? subpos[p * n_rows + r] : -1;
-  const uint32_t m = __ballot_sync(0xffffffffu, c >= 0);
-  const int first = m ? __ffs(m) - 1 : 0;
-  const int32_t c0 = __shfl_sync(0xffffffffu, c, first);
-  if (lane == 0) {
-    mask[warp_id] = m;
-    base[warp_id] = m ? c0 : 0;
-  }
-}
-
-template <class V>
-__global__ void __launch_bounds__(256)
-    panel_combine_packed_kernel(const V* __restrict__ ypart, const uint32_t* __restrict__ mask,
-                                const int32_t* __restrict__ base, int64_t n_rows, int n_panels,
-                                int64_t words, const V* y_in, V* y, V alpha, V beta,
-                                int has_beta) {
-  const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-  if (r >= n_rows) return;
-  const int64_t w = r >> 5;
-  const uint32_t bit = 1u << (r & 31);
-  V s = vt<V>::zero();
-  for (int p = 0; p < n_panels; ++p) {
-    const uint32_t m = mask[p * words + w];
-    if (m & bit) s = s + ypart[base[p * words + w] + __popc(m & (bit - 1))];
-  }
-  V out = alpha * s;
-  if (has_beta) out = out + beta * y_in[r];
-  y[r] = out;
-}
-
 template <class V, class P>
 int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_ptr,
                        int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
@@ -667,47 +624,6 @@ extern "C" int b2s_spmv_tile_items(int val_type, int idx_type) {
   (void)val_type;
   (void)idx_type;
   return b2s::SpmvCfg<float, int32_t>::ITEMS;
-}
-
-extern "C" int b2s_panel_pack(const int32_t* subpos_dev, int64_t n_rows, int n_panels,
-                              uint32_t* mask_dev, int32_t* base_dev, b2s_stream stream) {
-  if (n_rows < 0 || n_panels < 1 || n_panels > 256) return B2S_ERR_ARG;
-  if (n_rows == 0) return B2S_OK;
-  if (!subpos_dev || !mask_dev || !base_dev) return B2S_ERR_ARG;
-  const int64_t words = (n_rows + 31) / 32;
-  const int64_t threads_total = words * n_panels * 32;
-  const int64_t grid = (threads_total + 255) / 256;
-  if (grid > 0x7fffffffLL) return B2S_ERR_RANGE;
-  b2s::panel_pack_kernel<<<static_cast<unsigned>(grid), 256, 0,
-                           static_cast<cudaStream_t>(stream)>>>(subpos_dev, n_rows, n_panels,
-                                                                words, mask_dev, base_dev);
-  return b2s::launch_status();
-}
-
-extern "C" int b2s_panel_combine_packed(int val_type, const void* ypart_dev,
-                                        const uint32_t* mask_dev, const int32_t* base_dev,
-                                        int64_t n_rows, int n_panels, const void* y_in_dev,
-                                        void* y_dev, const void* alpha, const void* beta,
-                                        b2s_stream stream) {
-  if (n_rows < 0 || n_panels < 1 || n_panels > 256 || !alpha || !beta) return B2S_ERR_ARG;
-  if (n_rows == 0) return B2S_OK;
-  if (!ypart_dev || !mask_dev || !base_dev || !y_dev) return B2S_ERR_ARG;
-  const size_t vs = b2s::vsize(val_type);
-  if (vs == 0) return B2S_ERR_DTYPE;
-  const int64_t words = (n_rows + 31) / 32;
-  const int threads = 256;
-  const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
-  B2S_DISPATCH_V(val_type, {
-    const V a = *static_cast<const V*>(alpha);
-    const V b = *static_cast<const V*>(beta);
-    const int has_beta = b2s::vt<V>::is_zero(b) ? 0 : 1;
-    if (has_beta && y_in_dev == nullptr) return B2S_ERR_ARG;
-    (b2s::panel_combine_packed_kernel<V><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const V*>(ypart_dev), mask_dev, base_dev, n_rows, n_panels, words,
-        static_cast<const V*>(y_in_dev), static_cast<V*>(y_dev), a, b, has_beta));
-    return b2s::launch_status();
-  });
-  return B2S_ERR_DTYPE;
 }
 
 extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_dev,

@@ -299,18 +299,8 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
             st = fn(*head, *tail, status_p, stream)
         else:
             ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
-            if lay.mask is not None:
-                # partials only (y = NULL), then the combine that reads the packed position table
-                one, zero = _scalar(1.0, dtype), _scalar(0.0, dtype)
-                st = fn(*head, _lib.ptr(x), None, None, one, zero, tile_row_p, _lib.ptr(carry),
-                        _lib.ptr(ypart), status_p, stream, lay.n_stacked, _lib.ptr(lay.subpos))
-                if st == 0:
-                    st = _lib.load().b2s_panel_combine_packed(
-                        plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.mask), _lib.ptr(lay.base),
-                        plan.n_rows, lay.n_panels, _lib.ptr(y_in), _lib.ptr(y), a, b, stream)
-            else:
-                st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream, lay.n_stacked,
-                        _lib.ptr(lay.subpos))
+            st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream, lay.n_stacked,
+                    _lib.ptr(lay.subpos))
     finally:
         if switch:
             torch.cuda.set_device(prev)

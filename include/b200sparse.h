@@ -179,18 +179,6 @@ int b2s_panel_build_global(int val_type, int idx_type, int ptr_type,
                            int panel_shift, void* p_data_dev, int32_t* p_cols_dev,
                            void* p_ptr_dev, int p_ptr_type, int64_t* panel_start_dev,
                            void* scratch_dev, int64_t scratch_bytes, b2s_stream stream);
-/* The position table packed for the combine: words = ceil(n_rows / 32); mask_dev[p * words + w]
- * has bit b set when (panel p, row 32 w + b) is a non-empty stacked row, base_dev[p * words + w]
- * is the position of the first such row of the word (8 bytes per 32 rows and panel instead of
- * 128).  b2s_panel_pack fills both from subpos_dev; b2s_panel_combine_packed is the combine of
- * b2s_spmv_panels (y = alpha * sum over the panels of ypart + beta * y_in, ascending panel
- * order) reading them, for use after b2s_spmv_panels called with y_dev == NULL. */
-int b2s_panel_pack(const int32_t* subpos_dev, int64_t n_rows, int n_panels, uint32_t* mask_dev,
-                   int32_t* base_dev, b2s_stream stream);
-int b2s_panel_combine_packed(int val_type, const void* ypart_dev, const uint32_t* mask_dev,
-                             const int32_t* base_dev, int64_t n_rows, int n_panels,
-                             const void* y_in_dev, void* y_dev, const void* alpha,
-                             const void* beta, b2s_stream stream);
 int b2s_spmv_panels(int val_type, int ptr_type,
                     const void* p_data_dev, const int32_t* p_cols_dev, const void* p_ptr_dev,
                     int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,

@@ -249,49 +249,3 @@ def test_gather_probe_runs_and_checks_its_arguments():
     assert float(sink.item()) == 7.0
     assert lib.b2s_probe_gather(L.ptr(idx), -1, L.ptr(x), 64, L.ptr(sink), stream) == 2
     assert lib.b2s_probe_gather(None, 8, L.ptr(x), 64, L.ptr(sink), stream) == 2
-
-
-def test_panel_pack_and_packed_combine_match_the_position_table():
-    """b2s_panel_pack turns the int32 position table into mask / base words from which every
-    position can be recovered; b2s_panel_combine_packed adds the same partials in the same
-    order as the table-driven combine."""
-    lib, L = _lib()
-    rng = np.random.default_rng(11)
-    n_rows, n_panels = 1000, 5          # 1000 is not a multiple of 32: ragged last word
-    present = rng.random((n_panels, n_rows)) < 0.4
-    present[:, 64:96] = False           # a word without any row
-    present[2, 128:160] = True          # a full word
-    subpos = np.full((n_panels, n_rows), -1, dtype=np.int32)
-    subpos[present] = np.arange(int(present.sum()), dtype=np.int32)   # panel-major positions
-    words = (n_rows + 31) // 32
-    sp = torch.from_numpy(subpos.ravel()).cuda()
-    mask = torch.zeros(n_panels * words, dtype=torch.int32, device="cuda")
-    base = torch.zeros(n_panels * words, dtype=torch.int32, device="cuda")
-    stream = L.stream_handle(sp.device)
-    assert lib.b2s_panel_pack(L.ptr(sp), n_rows, n_panels, L.ptr(mask), L.ptr(base), stream) == 0
-    m = mask.cpu().numpy().view(np.uint32).reshape(n_panels, words)
-    b = base.cpu().numpy().reshape(n_panels, words)
-    for p in range(n_panels):
-        for r in range(n_rows):
-            w, bit = divmod(r, 32)
-            if (m[p, w] >> bit) & 1:
-                below = bin(int(m[p, w]) & ((1 << bit) - 1)).count("1")
-                assert b[p, w] + below == subpos[p, r]
-            else:
-                assert subpos[p, r] == -1
-    ypart = torch.randn(int(present.sum()), dtype=torch.float64, device="cuda")
-    y0 = torch.randn(n_rows, dtype=torch.float64, device="cuda")
-    y = torch.empty_like(y0)
-    a, bt = L.scalar_buffer(1.5, torch.float64), L.scalar_buffer(-0.5, torch.float64)
-    st = lib.b2s_panel_combine_packed(L.B2S_F64, L.ptr(ypart), L.ptr(mask), L.ptr(base), n_rows,
-                                      n_panels, L.ptr(y0), L.ptr(y), a, bt, stream)
-    assert st == 0
-    yp = ypart.cpu().numpy()
-    expect = np.zeros(n_rows)
-    for p in range(n_panels):                      # ascending panel order, as the kernel adds
-        sel = subpos[p] >= 0
-        expect[sel] = expect[sel] + yp[subpos[p][sel]]
-    expect = 1.5 * expect + (-0.5) * y0.cpu().numpy()
-    assert np.allclose(y.cpu().numpy(), expect, rtol=1e-14, atol=1e-14)  # fused multiply-add
-    assert lib.b2s_panel_pack(None, n_rows, n_panels, L.ptr(mask), L.ptr(base), stream) == 2
-    assert lib.b2s_panel_pack(L.ptr(sp), n_rows, 0, L.ptr(mask), L.ptr(base), stream) == 2
