@@ -7,7 +7,7 @@ RuntimeError is raised.  Build it with ``python -m flagsparse_b200._build``.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p
+from ctypes import c_char_p, c_int, c_int64, c_void_p
 from pathlib import Path
 
 import torch

@@ -12,7 +12,6 @@ extended to SpMM, which there re-validates and re-transposes on every call
 
 from __future__ import annotations
 
-import ctypes
 from collections import OrderedDict
 
 import torch

@@ -28,7 +28,6 @@ from ._contract import (
     SUPPORTED_INDEX_DTYPES,
     SUPPORTED_VALUE_DTYPES,
     check_scalar,
-    is_complex,
     normalize_op,
     op_name,
     op_transposes,

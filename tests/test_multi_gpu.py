@@ -6,7 +6,6 @@ import os
 import sys
 from pathlib import Path
 
-import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
