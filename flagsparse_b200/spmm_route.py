@@ -40,15 +40,20 @@ SPMM_CSR_ALGORITHMS = {
 }
 
 
+_ALG_ALIASES = {
+    "base": "csr_base", "csr": "csr_base", "csr_base": "csr_base",
+    "alg1": "spmm_csr_alg1", "csr_alg1": "spmm_csr_alg1", "spmm_csr_alg1": "spmm_csr_alg1",
+    "alg2": "spmm_csr_alg2", "csr_alg2": "spmm_csr_alg2", "spmm_csr_alg2": "spmm_csr_alg2",
+}
+
+
 def _normalize_spmm_csr_alg(alg):
-    token = "auto" if alg is None else str(alg).strip().lower()
-    if token in ("base", "csr", "csr_base"):
-        return "csr_base"
-    if token in ("alg1", "csr_alg1", "spmm_csr_alg1"):
-        return "spmm_csr_alg1"
-    if token in ("alg2", "csr_alg2", "spmm_csr_alg2"):
-        return "spmm_csr_alg2"
-    return token
+    """Alias table of the reference (spmm_csr.py:571-583); unknown tokens pass through so that
+    the registry lookup reports them."""
+    if alg is None:
+        return "auto"
+    token = str(alg).strip().lower()
+    return _ALG_ALIASES.get(token, token)
 
 
 def resolve_spmm_csr_algorithm(alg, op, dtype):
@@ -73,12 +78,17 @@ def list_spmm_csr_algorithms(op=None, dtype=None):
                  if dtype is None or dtype in dtypes)
 
 
+_ROW_LAYOUT_NAMES = frozenset(("auto", "default", "row", "row_major", "row-major", "c", "c_order"))
+_COL_LAYOUT_NAMES = frozenset(("col", "column", "col_major", "column_major", "col-major",
+                               "column-major", "f", "fortran"))
+
+
 def _normalize_dense_layout(layout):
+    """'row' or 'col' from the spellings the reference accepts (spmm_csr.py:586-594)."""
     token = "row" if layout is None else str(layout).strip().lower()
-    if token in ("auto", "default", "row", "row_major", "row-major", "c", "c_order"):
+    if token in _ROW_LAYOUT_NAMES:
         return "row"
-    if token in ("col", "column", "col_major", "column_major", "col-major", "column-major", "f",
-                 "fortran"):
+    if token in _COL_LAYOUT_NAMES:
         return "col"
     raise ValueError("dense_layout must be one of: auto, row, col")
 
