@@ -564,6 +564,17 @@ def run_multi_gpu(args, rank, world, local_rank, device):
            + world * (out_local.numel() * out_local.element_size() if y0_host is not None else 0))
     d2h = out_full.numel() * out_full.element_size()
 
+    # kernels per rank and step: every stage launches the tile kernel and the carry fix-up, on
+    # the column-panel layout also the combine; the peer route without panels adds the scatter
+    from flagsparse_b200 import _plan as plan_mod
+    n_stage = args.stages if staged else 1
+    panels = (kind == "spmv" and plan_mod.PANEL_POLICY == "auto"
+              and dense.numel() * dense.element_size() > plan_mod.PANEL_TRIGGER_BYTES
+              and p.nnz // n_stage >= plan_mod.PANEL_MIN_NNZ)
+    per_stage = 3 if (panels or gather_mode == "peer") else 2
+    if kind == "spmm":
+        per_stage = 2 + extra_launches(p, kind) + (1 if gather_mode == "peer" else 0)
+    launches_per_rank_step = n_stage * per_stage
     if rank == 0:
         gbs = job_bytes / per_step / 1e9
         kernel_gbs = job_bytes / (phases["kernel_ms"] / 1e3) / 1e9
@@ -588,7 +599,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                          "note": "per-GPU rate of the local kernel phase alone"},
             "e2e": {"value": job_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": world * args.steps * (2 + extra_launches(p, kind)),
+            "gpu_launches": world * args.steps * launches_per_rank_step,
             "clocks": sampler.summary(),
             "extra": {"gflops": job_flops / per_step / 1e9,
                       "pct_of_8tbs_nominal_per_gpu": 100.0 * gbs / world / NOMINAL_HBM_GBS,
