@@ -13,6 +13,9 @@ rows up to 100,000 entries, y = 1.5 * A x + 0.5 * y.  A step is one such product
                 y copied back, copies inside the timed region
   cpu_baseline  the CPU oracle (oracle/, a restatement of the reference's arithmetic) timed on
                 a bounded row slice of the same matrix, all host cores
+  extra         GFLOP/s, gathered bytes (x / B counted once per non-zero) and their rate, the
+                SpMM N = 32 product on the same matrix, the measured divergent-gather ceiling
+                of the GPU and the SpMV's fraction of it
   --impl reference   only that CPU measurement, as its own line
 
 With N > 1 (launched by torchrun, one rank per GPU) every rank owns one row block of the same
