@@ -429,10 +429,16 @@ def run_reference_arm(args, rank, world):
 
 def gather_ceiling(device, spmv_gathers_per_s):
     """The rate of divergent 8-byte gathers from an L2-resident array (32 MB, 2^26 random
-    indices), measured with the library's probe kernel: the bound the x gather of SpMV runs
-    against when the column indices have no locality."""
-    from flagsparse_b200 import _lib
-    lib = _lib.load()
+    indices), measured with the probe kernel of libb2sprobe.so (built from
+    flagsparse_b200/csrc/probe/, not part of the product library): the bound the x gather of
+    SpMV runs against when the column indices have no locality."""
+    import ctypes
+
+    from flagsparse_b200 import _build
+    lib = ctypes.CDLL(str(_build.PROBE_LIB_PATH))
+    lib.b2s_probe_gather.restype = ctypes.c_int
+    lib.b2s_probe_gather.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                                     ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
     n, n_x = 1 << 26, 1 << 22
     idx = torch.randint(0, n_x, (n,), dtype=torch.int32, device=device)
     x = torch.zeros(n_x, dtype=torch.float64, device=device)
@@ -440,8 +446,9 @@ def gather_ceiling(device, spmv_gathers_per_s):
     stream = torch.cuda.current_stream(device)
 
     def launch():
-        _lib.check(lib.b2s_probe_gather(idx.data_ptr(), n, x.data_ptr(), n_x, sink.data_ptr(),
-                                        stream.cuda_stream), "b2s_probe_gather")
+        if lib.b2s_probe_gather(idx.data_ptr(), n, x.data_ptr(), n_x, sink.data_ptr(),
+                                stream.cuda_stream) != 0:
+            raise RuntimeError("b2s_probe_gather failed")
 
     per = time_device(launch, 10, 3) / 10
     rate = n / per

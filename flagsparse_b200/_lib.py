@@ -7,17 +7,22 @@ RuntimeError is raised.  Build it with ``python -m flagsparse_b200._build``.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_int, c_int64, c_void_p
 from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "libb200sparse.so"
+# B200SPARSE_CHECKED=1 selects the bounds-checked build of the same sources (see _build.py)
+CHECKED = os.environ.get("B200SPARSE_CHECKED", "") not in ("", "0")
+LIB_PATH = Path(__file__).resolve().parent / (
+    "libb200sparse_checked.so" if CHECKED else "libb200sparse.so")
 
 # dtype codes of include/b200sparse.h
 B2S_F32, B2S_F64, B2S_C64, B2S_C128 = 0, 1, 2, 3
 B2S_I32, B2S_I64 = 0, 1
 B2S_ERR_TIMEOUT = 5
+B2S_ERR_BOUNDS = 9
 
 VALUE_CODE = {
     torch.float32: B2S_F32,
@@ -31,9 +36,7 @@ INDEX_CODE = {torch.int32: B2S_I32, torch.int64: B2S_I64}
 SIGNATURES = {
     "b2s_version": (c_int, []),
     "b2s_status_string": (c_char_p, [c_int]),
-    "b2s_tune": (c_int, [c_int, c_int64]),
     "b2s_selftest_wait_timeout": (c_int, [c_void_p, c_int, c_void_p]),
-    "b2s_probe_gather": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     "b2s_csr_inspect": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p,
                                 c_void_p]),
     "b2s_tile_count": (c_int64, [c_int64, c_int64, c_int]),
@@ -57,12 +60,12 @@ SIGNATURES = {
     "b2s_spmv_panels": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_int64, c_void_p]),
+                                c_void_p, c_int64, c_void_p, c_void_p]),
     "b2s_spmv_panels_peers": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_int64, c_void_p]),
+                                      c_int64, c_void_p, c_void_p]),
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_int, c_void_p]),

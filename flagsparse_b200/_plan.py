@@ -369,7 +369,12 @@ class CsrPlan:
             st = lib.b2s_tile_plan(_lib.ptr(lay.ptr), lay.pcode, rows, self.nnz, items,
                                    _lib.ptr(tile_row), _lib.stream_handle(self.device))
         _lib.check(st, "b2s_tile_plan")
-        lay.tiles[items] = (n_tiles, tile_row)
+        # panel of each tile's first non-zero (first non-zero of tile t: t * items - tile_row[t])
+        first_nz = (torch.arange(n_tiles, dtype=torch.int64, device=self.device) * items
+                    - tile_row[:n_tiles])
+        tile_panel = (torch.searchsorted(lay.panel_start, first_nz, right=True) - 1).clamp_(
+            0, lay.n_panels - 1).to(torch.int32)
+        lay.tiles[items] = (n_tiles, tile_row, tile_panel)
         return lay.tiles[items]
 
     # -- transpose ----------------------------------------------------------------------------

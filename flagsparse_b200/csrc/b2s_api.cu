@@ -6,8 +6,6 @@
 
 namespace b2s {
 
-int64_t g_knobs[KNOB_COUNT] = {0};
-
 void ensure_dyn_smem(const void* kernel, size_t bytes) {
   struct Seen {
     const void* k;
@@ -129,64 +127,9 @@ __global__ void tile_plan_kernel(const P* __restrict__ ptr, int64_t n_rows, int6
   tile_row[t] = lo;
 }
 
-// ---- gather-rate probe ------------------------------------------------------------------------
-// 128 threads x 8 gathers per pass, grid-stride over whole passes; the tail of fewer than 1024
-// indices is taken by the first CTA one index per thread.
-__global__ void __launch_bounds__(128, 12)
-    probe_gather_kernel(const int32_t* __restrict__ idx, int64_t n, const double* __restrict__ x,
-                        double* __restrict__ sink) {
-  constexpr int U = 8;
-  const int64_t pass = 128 * U;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * pass;
-  double acc = 0.0;
-  for (int64_t b = blockIdx.x * pass; b + pass <= n; b += stride) {
-    int32_t c[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) c[u] = __ldcs(idx + b + u * 128 + threadIdx.x);
-    double v[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) v[u] = __ldg(x + c[u]);
-#pragma unroll
-    for (int u = 0; u < U; ++u) acc += v[u];
-  }
-  if (blockIdx.x == 0)
-    for (int64_t i = n - n % pass + threadIdx.x; i < n; i += 128) acc += __ldg(x + idx[i]);
-  if (acc == -1.2345678e300) *sink = acc;
-}
-
 }  // namespace b2s
 
-extern "C" int b2s_probe_gather(const int32_t* idx_dev, int64_t n, const double* x_dev,
-                                int64_t n_x, double* sink_dev, b2s_stream stream) {
-  if (n < 0 || n_x <= 0) return B2S_ERR_ARG;
-  if (n == 0) return B2S_OK;
-  if (!idx_dev || !x_dev || !sink_dev) return B2S_ERR_ARG;
-  const int64_t want = (n + 1023) / 1024;
-  const unsigned grid = static_cast<unsigned>(want > 148 * 12 ? 148 * 12 : want);
-  b2s::probe_gather_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(idx_dev, n, x_dev,
-                                                                                sink_dev);
-  return b2s::launch_status();
-}
-
 extern "C" int b2s_version(void) { return B2S_VERSION; }
-
-extern "C" int b2s_tune(int knob, int64_t value) {
-  if (knob < 0 || knob >= b2s::KNOB_COUNT) return B2S_ERR_ARG;
-  b2s::g_knobs[knob] = value;
-  if (knob == b2s::KNOB_L2_FETCH && value > 0)
-    if (cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, static_cast<size_t>(value)) !=
-        cudaSuccess) {
-      cudaGetLastError();
-      return B2S_ERR_ARG;
-    }
-  if (knob == b2s::KNOB_PERSIST_BYTES)
-    if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, static_cast<size_t>(value)) !=
-        cudaSuccess) {
-      cudaGetLastError();
-      return B2S_ERR_ARG;
-    }
-  return B2S_OK;
-}
 
 extern "C" const char* b2s_status_string(int status) {
   switch (status) {
@@ -199,6 +142,7 @@ extern "C" const char* b2s_status_string(int status) {
     case B2S_ERR_WORKSPACE: return "scratch buffer too small";
     case B2S_ERR_RANGE: return "size does not fit the index dtype";
     case B2S_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of b2s_spmv_csr_fixed";
+    case B2S_ERR_BOUNDS: return "an index read from the matrix points outside its array";
   }
   return "unknown status";
 }

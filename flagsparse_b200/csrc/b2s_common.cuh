@@ -105,37 +105,6 @@ __device__ inline c128 ldg_val(const c128* p, uint64_t pol) {
   return v;
 }
 
-// gather of one value with a selectable cache path:
-//   0 ld.global.nc (read-only path)   1 nc + L2 evict-last hint   2 ld.global.cg (L2 only)
-//   3 nc + L1::no_allocate            4 ld.global.ca
-template <class V>
-__device__ inline V gather_val(const V* p, int mode, uint64_t pol) {
-  if (mode == 0) return ldg_val(p);
-  if (mode == 1) return ldg_val(p, pol);
-  V v;
-  if constexpr (sizeof(V) == 4) {
-    uint32_t r;
-    if (mode == 2) asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(r) : "l"(p));
-    else if (mode == 3) asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(r) : "l"(p));
-    else asm volatile("ld.global.ca.b32 %0, [%1];" : "=r"(r) : "l"(p));
-    memcpy(&v, &r, 4);
-  } else if constexpr (sizeof(V) == 8) {
-    uint64_t r;
-    if (mode == 2) asm volatile("ld.global.cg.b64 %0, [%1];" : "=l"(r) : "l"(p));
-    else if (mode == 3) asm volatile("ld.global.nc.L1::no_allocate.b64 %0, [%1];" : "=l"(r) : "l"(p));
-    else asm volatile("ld.global.ca.b64 %0, [%1];" : "=l"(r) : "l"(p));
-    memcpy(&v, &r, 8);
-  } else {
-    uint64_t a, b;
-    if (mode == 2) asm volatile("ld.global.cg.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
-    else if (mode == 3) asm volatile("ld.global.nc.L1::no_allocate.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
-    else asm volatile("ld.global.ca.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
-    uint64_t t[2] = {a, b};
-    memcpy(&v, t, 16);
-  }
-  return v;
-}
-
 // load of one element of a stream that is read exactly once: read-only path, no L1 allocation,
 // L2 eviction priority given by `pol` (evict-first keeps the stream from displacing x)
 template <class T>
@@ -179,6 +148,16 @@ __device__ inline c64 shfl_xor(c64 v, int m) {
 }
 __device__ inline c128 shfl_xor(c128 v, int m) {
   return {__shfl_xor_sync(0xffffffffu, v.re, m), __shfl_xor_sync(0xffffffffu, v.im, m)};
+}
+
+// value of the lane `d` below (the caller ignores what lanes < d receive)
+__device__ inline float shfl_up(float v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+__device__ inline double shfl_up(double v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+__device__ inline c64 shfl_up(c64 v, int d) {
+  return {__shfl_up_sync(0xffffffffu, v.re, d), __shfl_up_sync(0xffffffffu, v.im, d)};
+}
+__device__ inline c128 shfl_up(c128 v, int d) {
+  return {__shfl_up_sync(0xffffffffu, v.re, d), __shfl_up_sync(0xffffffffu, v.im, d)};
 }
 
 // butterfly sum over aligned groups of `width` lanes (width a power of two <= 32); every lane of
@@ -288,10 +267,6 @@ inline size_t isize(int itype) { return itype == B2S_I32 ? 4 : (itype == B2S_I64
     case B2S_I64: { using NAME = int64_t; __VA_ARGS__; } break; \
     default: return B2S_ERR_DTYPE;                             \
   }
-
-// run-time tuning knobs (b2s_tune)
-enum { KNOB_GATHER_POLICY = 0, KNOB_L2_FETCH = 1, KNOB_PERSIST_BYTES = 2, KNOB_COUNT = 16 };
-extern int64_t g_knobs[KNOB_COUNT];
 
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();

@@ -1,404 +1,289 @@
 // CSR SpMV for sm_100a: y = alpha * A x + beta * y_in.
 //
-// One CTA per merge-path tile (b2s_tile_plan).  The tile's col / val range is read straight from
-// global memory, coalesced, a batch of independent loads per thread, followed by the gathers of x;
-// the products go to shared memory.  The row pieces of the tile are then binned by length and
-// reduced out of shared memory:
-//   <= 8 entries   one thread per row, serial sum;
-//   9 .. 64        vector-per-row: 8 lanes per row, butterfly (__shfl_xor) reduction;
-//   65 .. 1024     warp-per-row, 32-lane butterfly;
-//   longer         the whole CTA; a row that crosses tile borders leaves one partial sum per
-//                  tile in `carry`, and a second kernel adds those partials to the row in
-//                  ascending tile order.
-// Row sums are staged in shared memory and written with a coalesced alpha / beta epilogue.
-// No floating-point atomics: every sum has a fixed shape, so results repeat bit for bit.
+// One CTA of 128 threads per merge-path tile (b2s_tile_plan).  The non-zeros of a tile occupy
+// consecutive "slots"; slot 0 is moved back to a 32-byte boundary of the col / val arrays, so
+// every thread owns SPT consecutive slots that it reads with 32-byte vector loads, coalesced
+// across the warp, straight into registers.  The gathers of x follow (SPT per thread in
+// flight) and the products never leave the register file:
+//   1. the rows that end in the tile mark the slot after their last non-zero in a shared-memory
+//      bit map ("heads": the slot starts a new row piece);
+//   2. each thread sums its slots serially, cutting at its head bits; a piece that begins and
+//      ends inside the thread is finished on the spot;
+//   3. a warp-wide segmented scan (shuffles, keyed on the ballot of the head bits) carries the
+//      open sums across lanes, four words of shared memory carry them across warps;
+//   4. the sum of each piece is stored at the slot of the head that ends it, and the rows read
+//      them back for a coalesced alpha / beta epilogue.
+// A row that crosses tile borders leaves one partial sum per tile in `carry`; a second kernel
+// adds those partials to the row in ascending tile order.  No floating-point atomics and only
+// fixed trees: results repeat bit for bit for a given matrix and build.
 //
 // Column-panel layout (b2s_spmv_panels): the same kernel runs over a stack of CSR matrices, one
 // per panel of columns, with panel-local int32 columns; partial results per (panel, row) are
 // added in ascending panel order by panel_combine_kernel.
-//
-// B2S_SPMV_DIRECT=0 selects the earlier variant that stages col / val with cp.async.bulk and an
-// mbarrier; it is kept for comparison (measured slower: the bulk-copy fills and the re-reads of
-// shared memory load the same L1 data pipe the gathers need).
 #include <mutex>
 
 #include "b2s_tile.cuh"
 
 namespace b2s {
 
-#ifndef B2S_SPMV_PERSISTENT
-#define B2S_SPMV_PERSISTENT 0  // 1: one CTA per resident slot walks the tiles (see the kernel)
-#endif
-#ifndef B2S_SPMV_THREADS
-#define B2S_SPMV_THREADS 128
-#endif
-#ifndef B2S_SPMV_ITEMS
-#define B2S_SPMV_ITEMS 1024
-#endif
-#ifndef B2S_SPMV_DIRECT
-#define B2S_SPMV_DIRECT 1  // 1: col / val straight from global memory; 0: staged by bulk copies
-#endif
-#ifndef B2S_SPMV_PREFETCH_AHEAD
-#define B2S_SPMV_PREFETCH_AHEAD 0  // tiles ahead whose col / val are prefetched into L2 (0 = off)
-#endif
-#ifndef B2S_SPMV_UNROLL
-#define B2S_SPMV_UNROLL 8
-#endif
-
-template <class V, class I>
-struct SpmvCfg {
-  static constexpr int THREADS = B2S_SPMV_THREADS;
-  static constexpr int ITEMS = B2S_SPMV_ITEMS;
+// Tile geometry.  SPT slots per thread: 8 consecutive non-zeros for values up to 8 bytes, 4 for
+// complex128.  A tile holds ITEMS merge items = SLOTS - SPT, which leaves room to begin the
+// slots on the vector boundary below the tile's first non-zero.
+template <class V>
+struct SpmvShape {
+  static constexpr int THREADS = 128;
+  static constexpr int SPT = sizeof(V) <= 8 ? 8 : 4;
+  static constexpr int SLOTS = THREADS * SPT;
+  static constexpr int ITEMS = SLOTS - SPT;
 };
 
-#ifdef B2S_PHASES
-__device__ unsigned long long g_phase_cycles[8];
-__device__ unsigned long long g_s1_by_T[16];
-#define B2S_TICK(n)                                                             \
-  do {                                                                          \
-    if (threadIdx.x == 0) {                                                     \
-      const long long now_ = clock64();                                         \
-      atomicAdd(&g_phase_cycles[n], static_cast<unsigned long long>(now_ - tick_)); \
-      tick_ = now_;                                                             \
-    }                                                                           \
-  } while (0)
-#else
-#define B2S_TICK(n)
-#endif
-
-static_assert(B2S_SPMV_ITEMS <= 4096, "queue capacities below assume at most 4096 items per tile");
-constexpr int kSpmvUnroll = B2S_SPMV_UNROLL;  // gathers in flight per thread
-constexpr int kThreadRowMax = 8;    // longest in-tile row piece one thread sums serially
-constexpr int kGroupRowMax = 64;    // longest piece a group of 8 lanes takes
-constexpr int kWarpRowMax = 1024;   // longest piece a single warp takes
-constexpr int kQueueACap = 512;     // pieces of 9..64 entries (at most ITEMS / 9)
-constexpr int kQueueBCap = 64;      // pieces of 65..1024 entries (at most ITEMS / 65)
-constexpr int kQueueCCap = 8;       // longer pieces (at most ITEMS / 1025 + 1)
-
-template <int THREADS, int ITEMS, class V, class I>
-constexpr size_t spmv_smem_bytes() {
-  return 16                                   // mbarrier
-         + sizeof(int) * (ITEMS + 4)          // row_end (+ padding to keep 16-byte alignment)
-         + (B2S_SPMV_DIRECT ? 0 : sizeof(I) * ITEMS + 16)  // staged columns
-         + sizeof(V) * ITEMS + 32             // staged values -> products, then row sums
-         + sizeof(int) * (kQueueACap + kQueueBCap + kQueueCCap + 4)  // queues + counters
-         + sizeof(V) * (THREADS / 32);        // per-warp partials
-}
-
-// CTAs per SM the register allocation aims at.  12 x 128 threads (<= 42 registers) measured 13 %
-// faster than the 10 the compiler settles on by itself (more gathers in flight); 16-byte values
-// and 8-byte column indices need more registers and would spill at that limit.
-template <class V, class I, int THREADS>
+// CTAs per SM the register allocation aims at.
+template <class V, class I>
 constexpr int spmv_min_blocks() {
 #ifdef B2S_SPMV_MINBLOCKS
   return B2S_SPMV_MINBLOCKS;
 #else
-  constexpr int want = (sizeof(V) <= 8 && sizeof(I) == 4) ? 12 : (sizeof(V) <= 8 ? 10 : 8);
-  constexpr int fit = 2048 / THREADS;  // resident threads per SM
-  return want < fit ? want : fit;
+  return (sizeof(V) <= 8 && sizeof(I) == 4) ? 10 : 8;
 #endif
 }
 
-template <class V, class I, class P, int THREADS, int ITEMS>
-__global__ void __launch_bounds__(THREADS, spmv_min_blocks<V, I, THREADS>())
+// Bytes of one vector load of a thread's run of N elements of T: 32, or 16 when the whole run
+// is only 16 bytes long (4 int32 columns beside 4 complex128 values).
+template <class T, int N>
+__host__ __device__ constexpr int run_chunk_bytes() {
+  return N * static_cast<int>(sizeof(T)) >= 32 ? 32 : 16;
+}
+
+// N consecutive elements starting at p (p aligned to the chunk size) with 32-byte loads through
+// the read-only path, no L1 allocation, L2 evict-first: col / val are read exactly once.  Only
+// the chunks that hold a live element (index in [lo, hi)) are requested, so a load never leaves
+// the aligned 32-byte sector of an element that belongs to the arrays.
+template <class T, int N>
+__device__ inline void load_run(const T* p, T (&out)[N], int lo, int hi, uint64_t pol) {
+  constexpr int BYTES = N * static_cast<int>(sizeof(T));
+  constexpr int CB = run_chunk_bytes<T, N>();
+  static_assert(BYTES % CB == 0, "a thread's run is a whole number of chunks");
+  constexpr int CHUNKS = BYTES / CB;
+  constexpr int EPC = N / CHUNKS;  // elements per chunk
+  constexpr int WPC = CB / 8;      // 8-byte words per chunk
+  uint64_t w[BYTES / 8];
+#pragma unroll
+  for (int q = 0; q < CHUNKS; ++q) {
+#pragma unroll
+    for (int k = 0; k < WPC; ++k) w[WPC * q + k] = 0;
+    if ((q + 1) * EPC > lo && q * EPC < hi) {
+      const char* src = reinterpret_cast<const char*>(p) + CB * q;
+      if constexpr (CB == 32)
+        asm volatile(
+            "ld.global.nc.L1::no_allocate.L2::cache_hint.v4.b64 {%0,%1,%2,%3}, [%4], %5;"
+            : "=l"(w[4 * q]), "=l"(w[4 * q + 1]), "=l"(w[4 * q + 2]), "=l"(w[4 * q + 3])
+            : "l"(src), "l"(pol));
+      else
+        asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.b64 {%0,%1}, [%2], %3;"
+                     : "=l"(w[2 * q]), "=l"(w[2 * q + 1])
+                     : "l"(src), "l"(pol));
+    }
+  }
+  memcpy(out, w, BYTES);
+}
+
+template <class V, class I, class P>
+__global__ void __launch_bounds__(SpmvShape<V>::THREADS, spmv_min_blocks<V, I>())
 spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ x, const V* y_in, V* y, V* __restrict__ carry,
-                 const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t nnz, V alpha,
-                 V beta, int has_beta, int gather_policy, int32_t* status,
-                 const int64_t* __restrict__ panel_start, int n_panels, int panel_shift) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
-  int* row_end = reinterpret_cast<int*>(smem + 16);
-  unsigned char* col_buf = smem + 16 + sizeof(int) * (ITEMS + 4);
-  unsigned char* val_buf = col_buf + (B2S_SPMV_DIRECT ? 0 : sizeof(I) * ITEMS + 16);
-  int* queueA = reinterpret_cast<int*>(val_buf + sizeof(V) * ITEMS + 32);
-  int* queueB = queueA + kQueueACap;
-  int* queueC = queueB + kQueueBCap;
-  int* qcount = queueC + kQueueCCap;  // number of entries in queues A, B, C
-  V* wpart = reinterpret_cast<V*>(qcount + 4);
+                 const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t n_cols,
+                 int64_t nnz, V alpha, V beta, int has_beta, int phase, int32_t* status,
+                 const int64_t* __restrict__ panel_start,
+                 const int32_t* __restrict__ tile_panel, int n_panels, int panel_shift) {
+  using S = SpmvShape<V>;
+  constexpr int THREADS = S::THREADS, SPT = S::SPT, SLOTS = S::SLOTS, ITEMS = S::ITEMS;
+  constexpr int WARPS = THREADS / 32;
+  __shared__ uint32_t head[SLOTS / 32];
+  __shared__ __align__(16) unsigned char seg_raw[sizeof(V) * SLOTS];
+  __shared__ __align__(16) unsigned char wtail_raw[sizeof(V) * WARPS];
+  __shared__ int whead[WARPS];
+  V* seg_at = reinterpret_cast<V*>(seg_raw);    // sum of the piece that ends before a head slot
+  V* wtail = reinterpret_cast<V*>(wtail_raw);   // open sum at the end of each warp
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-#ifdef B2S_PHASES
-  long long tick_ = clock64();
-#endif
-  // an earlier CTA already gave up on a copy: do not queue more waits behind it
-  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
-#if B2S_SPMV_PERSISTENT
-  // one CTA per slot of the GPU walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...: the
-  // CTAs resident at any time still cover a contiguous window of tiles (the x slice of a panel
-  // stays the one in L2), no CTA is launched or retired between tiles, and the plan entries of
-  // the next tile are requested while the current one is multiplied
-  const int64_t n_tiles_all = (n_rows + nnz + ITEMS - 1) / ITEMS;
-  int64_t next_r0 = tile_row[blockIdx.x], next_r1 = tile_row[blockIdx.x + 1];
-  for (int64_t t = blockIdx.x; t < n_tiles_all; t += gridDim.x) {
-  const TileCoord tc = tile_coord_from(next_r0, next_r1, t, ITEMS, n_rows + nnz);
-  if (t + gridDim.x < n_tiles_all) {
-    next_r0 = tile_row[t + gridDim.x];
-    next_r1 = tile_row[t + gridDim.x + 1];
-  }
-#else
   const int64_t t = blockIdx.x;
   const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
-  {
-#endif
   const int n_nz = static_cast<int>(tc.j1 - tc.j0);
   const int n_end = static_cast<int>(tc.r1 - tc.r0);  // rows that end in this tile
 
-  const I* gcol = col + tc.j0;
-  const V* gval = val + tc.j0;
-  V* prod_w;  // products of the tile, in shared memory
-  if (tid == 0) {
-    qcount[0] = 0;
-    qcount[1] = 0;
-    qcount[2] = 0;
-  }
-  if constexpr (B2S_SPMV_DIRECT) {
-    // col / val are read straight from global memory, coalesced, with all loads of a batch in
-    // flight before the gathers; measured cheaper for the load/store pipe than staging them
-    // (bulk-copy fills of shared memory and the re-reads count against the same data pipe)
-    prod_w = reinterpret_cast<V*>(val_buf);
-#if B2S_SPMV_PREFETCH_AHEAD > 0
-    // pull the col / val range of the tile that will run in this CTA's slot one wave from now
-    // into L2, so that its loads find them there instead of waiting on DRAM
-    {
-      const int64_t ta = t + B2S_SPMV_PREFETCH_AHEAD;
-      if (ta < static_cast<int64_t>(gridDim.x)) {
-        const int64_t total = n_rows + nnz;
-        int64_t da = ta * static_cast<int64_t>(ITEMS);
-        if (da > total) da = total;
-        const int64_t ja = da - tile_row[ta];
-        int64_t na = nnz - ja;
-        if (na > ITEMS) na = ITEMS;
-        const char* pc = reinterpret_cast<const char*>(col + ja);
-        const char* pv = reinterpret_cast<const char*>(val + ja);
-        const int64_t bc = na * static_cast<int64_t>(sizeof(I));
-        const int64_t bv = na * static_cast<int64_t>(sizeof(V));
-        for (int64_t o = tid * 128LL; o < bc; o += THREADS * 128LL)
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + o));
-        for (int64_t o = tid * 128LL; o < bv; o += THREADS * 128LL)
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(pv + o));
-      }
-    }
-#endif
-    const uint64_t once = policy_evict_first();
-    const uint64_t keep = policy_evict_last();
-    for (int k = tid; k < n_end; k += THREADS)
-      row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
-    if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
-    // column-panel layout: the matrix is a stack of panels, columns are panel-local and the
-    // non-zeros of panel p start at panel_start[p]; find the panel of the tile's first entry
-    int p_lo = 0;
-    int64_t p_next = INT64_MAX;  // first non-zero (global index) of the panel after p_lo
-    if (panel_start != nullptr && n_nz > 0) {
-      int lo = 0, hi = n_panels - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (panel_start[mid] <= tc.j0) lo = mid; else hi = mid - 1;
-      }
-      p_lo = lo;
-      p_next = panel_start[p_lo + 1];
-    }
-    for (int base = tid; base < n_nz; base += kSpmvUnroll * THREADS) {
-      I c[kSpmvUnroll];
-      V a[kSpmvUnroll];
-#pragma unroll
-      for (int u = 0; u < kSpmvUnroll; ++u) {
-        const int i = base + u * THREADS;
-        if (i < n_nz) {
-          c[u] = stream_val(gcol + i, once);
-          a[u] = stream_val(gval + i, once);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kSpmvUnroll; ++u) {
-        const int i = base + u * THREADS;
-        if (i < n_nz) {
-          int64_t xc = static_cast<int64_t>(c[u]);
-          if (panel_start != nullptr) {
-            int pp = p_lo;
-            if (tc.j0 + i >= p_next) {  // rare: the tile straddles a panel border
-              ++pp;
-              while (pp + 1 < n_panels && tc.j0 + i >= panel_start[pp + 1]) ++pp;
-            }
-            xc += static_cast<int64_t>(pp) << panel_shift;
-          }
-          a[u] = a[u] * gather_val(x + xc, gather_policy, keep);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kSpmvUnroll; ++u) {
-        const int i = base + u * THREADS;
-        if (i < n_nz) prod_w[i] = a[u];
-      }
-    }
-    __syncthreads();
-    B2S_TICK(1);
-  } else {
-    const Staged<I> sc = stage_layout<I>(col_buf, gcol, n_nz);
-    const Staged<V> sv = stage_layout<V>(val_buf, gval, n_nz);
-    const uint32_t tx = stage_bytes(sc) + stage_bytes(sv);
-    if (tid == 0 && tx) mbar_init(bar, 1);
-    __syncthreads();
-    if (tid == 0 && tx) {
-      const uint64_t pol = policy_evict_first();  // col / val are read once
-      mbar_expect_tx(bar, tx);
-      stage_issue(sc, gcol, bar, pol);
-      stage_issue(sv, gval, bar, pol);
-    }
-    // while the copies fly: ragged edges and the row ends of this tile
-    stage_edges(sc, gcol, n_nz, tid, THREADS);
-    stage_edges(sv, gval, n_nz, tid, THREADS);
-    for (int k = tid; k < n_end; k += THREADS)
-      row_end[k] = static_cast<int>(static_cast<int64_t>(ptr[tc.r0 + 1 + k]) - tc.j0);
-    if (tid == 0) row_end[n_end] = n_nz;  // the open row runs to the end of the tile
-    // one warp waits for the copies; the CTA barrier that follows releases everybody else
-    if (tx && warp == 0) {
-      if (!mbar_wait(bar, 0)) {
-        if (status && lane == 0) atomicOr(status, 1 << B2S_ERR_TIMEOUT);
-        mbar_wait(bar, 0);  // second bounded wait: do not leave with a copy in flight
-      }
-    }
-    __syncthreads();
-    B2S_TICK(0);
-    const I* scol = sc.s;
-    V* sval = sv.s;
-    prod_w = sv.s;
-    const uint64_t keep = policy_evict_last();
-    for (int base = tid; base < n_nz; base += kSpmvUnroll * THREADS) {
-      V xv[kSpmvUnroll];
-#pragma unroll
-      for (int u = 0; u < kSpmvUnroll; ++u) {
-        const int i = base + u * THREADS;
-        if (i < n_nz)
-          xv[u] = gather_val(x + static_cast<int64_t>(scol[i]), gather_policy, keep);
-      }
-#pragma unroll
-      for (int u = 0; u < kSpmvUnroll; ++u) {
-        const int i = base + u * THREADS;
-        if (i < n_nz) sval[i] = sval[i] * xv[u];
-      }
-    }
-    __syncthreads();
-    B2S_TICK(1);
-  }
+  // slot 0 sits on a vector boundary at or below the first non-zero of the tile; `phase` is the
+  // element offset of the arrays' base addresses from such a boundary (-1: no common one, the
+  // arrays are then read element by element)
+  const int a = static_cast<int>((tc.j0 + (phase > 0 ? phase : 0)) & (SPT - 1));
+  const int64_t jb = tc.j0 - a;       // non-zero index of slot 0 (may lie below the tile)
+  const int sb = tid * SPT;           // first slot of this thread
+  const int64_t jt = jb + sb;
+  const int lo = a - sb;              // this thread's live elements are lo <= i < hi
+  const int hi = a + n_nz - sb;
+  const bool live = hi > 0 && lo < SPT;
 
-  const V* prod = prod_w;
-  V* rsum = prod_w + n_nz;  // row sums live behind the products (n_nz + n_end + 1 <= ITEMS + 1)
-  const bool open_row = tc.r1 < n_rows;
-  const int n_seg = n_end + 1;  // row pieces in the tile; the last one is the open row
-
-  // ---- bin the row pieces of the tile by length; the shortest are summed on the spot ----------
-  //   <= kThreadRowMax : one thread per piece, serial sum
-  //   <= kGroupRowMax  : queue A, a group of 8 lanes per piece (vector-per-row)
-  //   <= kWarpRowMax   : queue B, a warp per piece
-  //   longer           : queue C, the whole CTA per piece
-  for (int k = tid; k < n_seg; k += THREADS) {
-    const int s = k ? row_end[k - 1] : 0;
-    const int e = row_end[k];
-    const int len = e - s;
-    if (len <= kThreadRowMax) {
-      V acc = vt<V>::zero();
-      for (int i = s; i < e; ++i) acc = acc + prod[i];
-      rsum[k] = acc;
-    } else if (len <= kGroupRowMax) {
-      const int q = atomicAdd(&qcount[0], 1);
-      if (q < kQueueACap) queueA[q] = k;
-    } else if (len <= kWarpRowMax) {
-      const int q = atomicAdd(&qcount[1], 1);
-      if (q < kQueueBCap) queueB[q] = k;
+  // column-panel layout: the matrix is a stack of panels with panel-local columns; the non-zeros
+  // of panel p start at panel_start[p].  Panel of the tile's first non-zero:
+  int p_lo = 0;
+  int straddle = SPT;  // first element of this thread that lies in a later panel (rare)
+  if (panel_start != nullptr && n_nz > 0) {
+    if (tile_panel != nullptr) {
+      p_lo = tile_panel[t];
     } else {
-      const int q = atomicAdd(&qcount[2], 1);
-      if (q < kQueueCCap) queueC[q] = k;
+      int l = 0, h = n_panels - 1;
+      while (l < h) {
+        const int mid = (l + h + 1) >> 1;
+        if (panel_start[mid] <= tc.j0) l = mid; else h = mid - 1;
+      }
+      p_lo = l;
+    }
+    const int64_t left = panel_start[p_lo + 1] - jt;
+    straddle = left < 0 ? 0 : (left < SPT ? static_cast<int>(left) : SPT);
+  }
+
+  // ---- col / val of this thread's slots, and the first row end, all in flight together --------
+  I c[SPT];
+  V v[SPT];
+#pragma unroll
+  for (int i = 0; i < SPT; ++i) {
+    c[i] = 0;
+    v[i] = vt<V>::zero();
+  }
+  if (live) {
+    if (phase >= 0) {
+      const uint64_t once = policy_evict_first();
+      load_run(col + jt, c, lo, hi, once);
+      load_run(val + jt, v, lo, hi, once);
+    } else {
+#pragma unroll
+      for (int i = 0; i < SPT; ++i)
+        if (i >= lo && i < hi) {
+          c[i] = col[jt + i];
+          v[i] = val[jt + i];
+        }
     }
   }
+  int64_t e_first = 0;
+  if (tid < n_end) e_first = static_cast<int64_t>(ptr[tc.r0 + 1 + tid]);
+  if (tid < SLOTS / 32) head[tid] = 0;
   __syncthreads();
-  B2S_TICK(2);
 
-  // ---- queue A: vector-per-row, 8 lanes per piece, butterfly reduction ------------------------
+  // ---- gathers of x ---------------------------------------------------------------------------
+  V xv[SPT];
   {
-    const int nA = min(qcount[0], kQueueACap);
-    const int sub = tid & 7;
-    const int grp = tid >> 3;
-    for (int qb = 0; qb < nA; qb += THREADS / 8) {  // uniform trip count: shuffles stay converged
-      const int q = qb + grp;
-      const bool live = q < nA;
-      int k = 0, s = 0, e = 0;
-      if (live) {
-        k = queueA[q];
-        s = k ? row_end[k - 1] : 0;
-        e = row_end[k];
-      }
-      V acc = vt<V>::zero();
-      for (int i = s + sub; i < e; i += 8) acc = acc + prod[i];
-      acc = group_sum(acc, 8);
-      if (live && sub == 0) rsum[k] = acc;
-    }
-  }
-
-  // ---- queue B: warp-per-row -------------------------------------------------------------------
-  {
-    const int nB = min(qcount[1], kQueueBCap);
-    for (int q = warp; q < nB; q += THREADS / 32) {
-      const int k = queueB[q];
-      const int s = k ? row_end[k - 1] : 0;
-      const int e = row_end[k];
-      V acc = vt<V>::zero();
-      for (int i = s + lane; i < e; i += 32) acc = acc + prod[i];
-      acc = group_sum(acc, 32);
-      if (lane == 0) rsum[k] = acc;
-    }
-  }
-
-  // ---- queue C: CTA-per-row --------------------------------------------------------------------
-  {
-    const int nC = min(qcount[2], kQueueCCap);
-    for (int q = 0; q < nC; ++q) {
-      const int k = queueC[q];
-      const int s = k ? row_end[k - 1] : 0;
-      const int e = row_end[k];
-      V acc = vt<V>::zero();
-      for (int i = s + tid; i < e; i += THREADS) acc = acc + prod[i];
-      acc = group_sum(acc, 32);
-      if (lane == 0) wpart[warp] = acc;
-      __syncthreads();
-      if (tid == 0) {
-        V tot = wpart[0];
+    const V* xp = x + (static_cast<int64_t>(p_lo) << panel_shift);
 #pragma unroll
-        for (int w = 1; w < THREADS / 32; ++w) tot = tot + wpart[w];
-        rsum[k] = tot;
-      }
-      __syncthreads();
-    }
-  }
-  __syncthreads();
-  B2S_TICK(3);
-
-  // ---- epilogue: the rows that end in this tile are consecutive, so y is read and written
-  // coalesced, with every load of a batch issued before the first store
-  for (int kb = 0; kb < n_end; kb += 4 * THREADS) {
-    V old[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int k = kb + u * THREADS + tid;
-      old[u] = (has_beta && k < n_end) ? y_in[tc.r0 + k] : vt<V>::zero();
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int k = kb + u * THREADS + tid;
-      if (k < n_end) {
-        V r = alpha * rsum[k];
-        if (has_beta) r = r + beta * old[u];
-        y[tc.r0 + k] = r;
-      }
-    }
-  }
-  if (tid == 0 && open_row) carry[t] = rsum[n_end];
-  B2S_TICK(4);
-#if B2S_SPMV_PERSISTENT
-  __syncthreads();  // the next tile reuses the shared-memory buffers
+    for (int i = 0; i < SPT; ++i) {
+      xv[i] = vt<V>::zero();
+      if (i >= lo && i < hi) {
+        const V* src = xp + static_cast<int64_t>(c[i]);
+        if (i >= straddle) {  // the tile straddles a panel border
+          int pp = p_lo + 1;
+          while (pp + 1 < n_panels && jt + i >= panel_start[pp + 1]) ++pp;
+          src = x + (static_cast<int64_t>(pp) << panel_shift) + static_cast<int64_t>(c[i]);
+        }
+#ifdef B2S_CHECKED
+        if (src < x || src >= x + n_cols) {  // never dereference a column outside x
+          if (status) atomicOr(status, 1 << B2S_ERR_BOUNDS);
+          continue;
+        }
 #endif
+        xv[i] = ldg_val(src);
+      }
+    }
+  }
+
+  // ---- heads: the slot after the last non-zero of every row that ends here ----------------------
+  // (a row end at or below slot a closes an empty piece and needs no bit; rows that end on the
+  // same slot share one)
+  for (int k = tid; k < n_end; k += THREADS) {
+    const int64_t e64 = (k == tid ? e_first : static_cast<int64_t>(ptr[tc.r0 + 1 + k])) - jb;
+#ifdef B2S_CHECKED
+    if (e64 < a || e64 > a + n_nz) {  // row pointers that disagree with the tile plan
+      if (status) atomicOr(status, 1 << B2S_ERR_BOUNDS);
+      continue;
+    }
+#endif
+    const int e = static_cast<int>(e64);
+    if (e > a) atomicOr(&head[e >> 5], 1u << (e & 31));
+  }
+  if (tid == 0) atomicOr(&head[(a + n_nz) >> 5], 1u << ((a + n_nz) & 31));  // end of the tile
+  __syncthreads();
+
+  uint32_t flags;
+  if constexpr (SPT == 8)
+    flags = reinterpret_cast<const unsigned char*>(head)[tid];
+  else
+    flags = (head[tid >> 3] >> ((tid & 7) * 4)) & 15u;
+
+  // ---- serial pass over this thread's slots -----------------------------------------------------
+  // first: sum before the thread's first head (continues a piece from the lanes below);
+  // acc at the end: sum after its last head (continues into the lanes above)
+  V acc = vt<V>::zero(), first = vt<V>::zero();
+  bool seen = false;
+#pragma unroll
+  for (int i = 0; i < SPT; ++i) {
+    if ((flags >> i) & 1u) {
+      if (!seen) {
+        first = acc;
+        seen = true;
+      } else {
+        seg_at[sb + i] = acc;
+      }
+      acc = vt<V>::zero();
+    }
+    if (i >= lo && i < hi) acc = acc + v[i] * xv[i];
+  }
+
+  // ---- open sums across the lanes of the warp ---------------------------------------------------
+  const uint32_t heads_w = __ballot_sync(0xffffffffu, seen);
+  const uint32_t upto = heads_w & (0xffffffffu >> (31 - lane));  // head lanes <= this lane
+  const int reach = upto ? lane - (31 - __clz(upto)) : lane;     // lanes below in the same piece
+  V incl = acc;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const V below = shfl_up(incl, d);
+    if (d <= reach) incl = below + incl;
+  }
+  V cin = shfl_up(incl, 1);  // open sum that enters this lane
+  if (lane == 0) cin = vt<V>::zero();
+  if (lane == 31) {
+    wtail[warp] = incl;
+    whead[warp] = heads_w != 0;
+  }
+  __syncthreads();
+  if (seen) {
+    V total = cin;
+    if ((heads_w & ((1u << lane) - 1u)) == 0) {  // the piece began in an earlier warp
+      V wc = vt<V>::zero();
+      for (int w = 0; w < warp; ++w) wc = whead[w] ? wtail[w] : wc + wtail[w];
+      total = wc + cin;
+    }
+    seg_at[sb + __ffs(flags) - 1] = total + first;
+  }
+  __syncthreads();
+
+  // ---- epilogue: the rows that end in this tile are consecutive, y is read and written coalesced
+  for (int k = tid; k < n_end; k += THREADS) {
+    const int64_t s64 = static_cast<int64_t>(ptr[tc.r0 + k]) - jb;
+    const int s = s64 < a ? a : static_cast<int>(s64);
+    const int e = static_cast<int>(
+        (k == tid ? e_first : static_cast<int64_t>(ptr[tc.r0 + 1 + k])) - jb);
+#ifdef B2S_CHECKED
+    if (e < a || e > a + n_nz) continue;
+#endif
+    const V sum = e > s ? seg_at[e] : vt<V>::zero();
+    V r = alpha * sum;
+    if (has_beta) r = r + beta * y_in[tc.r0 + k];
+    y[tc.r0 + k] = r;
+  }
+  if (tid == 0 && tc.r1 < n_rows) {  // the row still open at the end of the tile
+    const int64_t s64 = static_cast<int64_t>(ptr[tc.r1]) - jb;
+    const int s = s64 < a ? a : static_cast<int>(s64);
+    const int e = a + n_nz;
+    carry[t] = e > s ? seg_at[e] : vt<V>::zero();
   }
 }
 
@@ -419,63 +304,40 @@ __global__ void spmv_fixup_kernel(V* y, const V* __restrict__ carry,
   y[r] = y[r] + alpha * s;
 }
 
+// Element offset of the two arrays from a common vector boundary, or -1 when they have
+// none (then the kernel reads element by element).  Slices taken at the same element offset of
+// two aligned allocations, as a row block of a larger matrix is, do have one.
+template <class V, class I>
+int spmv_vector_phase(const void* data, const void* indices) {
+  constexpr int SPT = SpmvShape<V>::SPT;
+  const uintptr_t d = reinterpret_cast<uintptr_t>(data), c = reinterpret_cast<uintptr_t>(indices);
+  if (d % sizeof(V) || c % sizeof(I)) return -1;
+  constexpr uintptr_t vb = run_chunk_bytes<V, SPT>(), cb = run_chunk_bytes<I, SPT>();
+  for (int o = 0; o < SPT; ++o)
+    if ((d - o * sizeof(V)) % vb == 0 && (c - o * sizeof(I)) % cb == 0) return o;
+  return -1;
+}
+
 template <class V, class I, class P>
 int spmv_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* x, const void* y_in, void* y, const void* alpha,
                 const void* beta, const int64_t* tile_row, void* carry, int32_t* status,
                 cudaStream_t stream, const int64_t* panel_start = nullptr, int n_panels = 0,
-                int panel_shift = 0) {
-  using Cfg = SpmvCfg<V, I>;
-  constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
-  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
+                int panel_shift = 0, const int32_t* tile_panel = nullptr) {
+  using S = SpmvShape<V>;
+  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, S::ITEMS);
   if (n_tiles == 0) return B2S_OK;
   if (n_tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
   const V a = *static_cast<const V*>(alpha);
   const V b = *static_cast<const V*>(beta);
   const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
   if (has_beta && y_in == nullptr) return B2S_ERR_ARG;
-  auto kern = spmv_tile_kernel<V, I, P, THREADS, ITEMS>;
-  constexpr size_t smem = spmv_smem_bytes<THREADS, ITEMS, V, I>();
-  ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(n_tiles));
-#if B2S_SPMV_PERSISTENT
-  {
-    // as many CTAs as the device keeps resident at once
-    static int slots = 0;
-    if (slots == 0) {
-      int dev = 0, sms = 0, per_sm = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem);
-      slots = sms * (per_sm > 0 ? per_sm : 1);
-    }
-    if (n_tiles > slots) cfg.gridDim = dim3(static_cast<unsigned>(slots));
-  }
-#endif
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  if (g_knobs[KNOB_PERSIST_BYTES] > 0 && n_cols > 0) {
-    // keep as much of x as the persisting carve-out holds; the rest is treated as streaming
-    const double x_bytes = static_cast<double>(n_cols) * sizeof(V);
-    attr[0].id = cudaLaunchAttributeAccessPolicyWindow;
-    attr[0].val.accessPolicyWindow.base_ptr = const_cast<void*>(x);
-    attr[0].val.accessPolicyWindow.num_bytes = static_cast<size_t>(x_bytes);
-    double ratio = static_cast<double>(g_knobs[KNOB_PERSIST_BYTES]) / x_bytes;
-    attr[0].val.accessPolicyWindow.hitRatio = static_cast<float>(ratio > 1.0 ? 1.0 : ratio);
-    attr[0].val.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
-    attr[0].val.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  }
-  cudaLaunchKernelEx(&cfg, kern, static_cast<const V*>(data), static_cast<const I*>(indices),
-                     static_cast<const P*>(indptr), static_cast<const V*>(x),
-                     static_cast<const V*>(y_in), static_cast<V*>(y), static_cast<V*>(carry),
-                     tile_row, n_rows, nnz, a, b, has_beta,
-                     static_cast<int>(g_knobs[KNOB_GATHER_POLICY]), status, panel_start, n_panels,
-                     panel_shift);
+  const int phase = nnz > 0 ? spmv_vector_phase<V, I>(data, indices) : 0;
+  spmv_tile_kernel<V, I, P><<<static_cast<unsigned>(n_tiles), S::THREADS, 0, stream>>>(
+      static_cast<const V*>(data), static_cast<const I*>(indices), static_cast<const P*>(indptr),
+      static_cast<const V*>(x), static_cast<const V*>(y_in), static_cast<V*>(y),
+      static_cast<V*>(carry), tile_row, n_rows, n_cols, nnz, a, b, has_beta, phase, status,
+      panel_start, tile_panel, n_panels, panel_shift);
   if (n_tiles > 1) {
     const int fb = 256;
     spmv_fixup_kernel<V><<<static_cast<unsigned>((n_tiles + fb - 1) / fb), fb, 0, stream>>>(
@@ -571,14 +433,14 @@ int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_
                        const void* alpha, const void* beta, const int64_t* tile_row, void* carry,
                        void* ypart, int32_t* status, cudaStream_t stream,
                        int64_t n_stacked, const int32_t* subpos,
-                       const PeerList* peers = nullptr, int n_peers = 0,
-                       int64_t row_offset = 0) {
+                       const int32_t* tile_panel, const PeerList* peers = nullptr,
+                       int n_peers = 0, int64_t row_offset = 0) {
   // 1) the stacked matrix (n_panels * n_rows rows, panel-local int32 columns) times x with
   //    alpha = 1, beta = 0 -> one partial result per (panel, row)
   const V one = vt<V>::one(), zero = vt<V>::zero();
   int st = spmv_launch<V, int32_t, P>(p_data, p_cols, p_ptr, n_stacked, n_cols, nnz, x,
                                       nullptr, ypart, &one, &zero, tile_row, carry, status,
-                                      stream, panel_start, n_panels, panel_shift);
+                                      stream, panel_start, n_panels, panel_shift, tile_panel);
   if (st != B2S_OK) return st;
   if (y == nullptr && peers == nullptr) return launch_status();  // caller combines separately
   // 2) add the panels of each row and apply alpha / beta
@@ -605,25 +467,10 @@ int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_
 
 }  // namespace b2s
 
-#ifdef B2S_PHASES
-extern "C" int b2s_debug_phases(unsigned long long* out8, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out8, b2s::g_phase_cycles, sizeof(unsigned long long) * 8);
-  cudaMemcpyFromSymbol(out8 + 8, b2s::g_s1_by_T, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long z[8] = {0};
-    cudaMemcpyToSymbol(b2s::g_phase_cycles, z, sizeof(z));
-    unsigned long long z2[16] = {0};
-    cudaMemcpyToSymbol(b2s::g_s1_by_T, z2, sizeof(z2));
-  }
-  return 0;
-}
-#endif
-
 extern "C" int b2s_spmv_tile_items(int val_type, int idx_type) {
-  (void)val_type;
   (void)idx_type;
-  return b2s::SpmvCfg<float, int32_t>::ITEMS;
+  B2S_DISPATCH_V(val_type, { return b2s::SpmvShape<V>::ITEMS; });
+  return 0;
 }
 
 extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_dev,
@@ -633,7 +480,8 @@ extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_de
                                const void* y_in_dev, void* y_dev, const void* alpha,
                                const void* beta, const int64_t* tile_row_dev, void* carry_dev,
                                void* ypart_dev, int32_t* status_dev, b2s_stream stream,
-                               int64_t n_stacked, const int32_t* subpos_dev) {
+                               int64_t n_stacked, const int32_t* subpos_dev,
+                               const int32_t* tile_panel_dev) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0 || !alpha || !beta) return B2S_ERR_ARG;
   if (subpos_dev == nullptr) n_stacked = n_rows * n_panels;
   if (n_stacked < 0 || n_stacked > n_rows * n_panels) return B2S_ERR_ARG;
@@ -654,7 +502,7 @@ extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_de
     return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
                                           n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
                                           y_dev, alpha, beta, tile_row_dev, carry_dev, ypart_dev,
-                                          status_dev, s, n_stacked, subpos_dev));
+                                          status_dev, s, n_stacked, subpos_dev, tile_panel_dev));
   }));
   return B2S_ERR_DTYPE;
 }
@@ -680,7 +528,8 @@ extern "C" int b2s_spmv_panels_peers(int val_type, int ptr_type, const void* p_d
                                      int64_t peer_rows, const void* alpha, const void* beta,
                                      const int64_t* tile_row_dev, void* carry_dev,
                                      void* ypart_dev, int32_t* status_dev, b2s_stream stream,
-                                     int64_t n_stacked, const int32_t* subpos_dev) {
+                                     int64_t n_stacked, const int32_t* subpos_dev,
+                                     const int32_t* tile_panel_dev) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0 || row_offset < 0 || !alpha || !beta) return B2S_ERR_ARG;
   if (row_offset + n_rows > peer_rows) return B2S_ERR_ARG;  // block must fit the peers' buffers
   if (subpos_dev == nullptr) n_stacked = n_rows * n_panels;
@@ -700,8 +549,8 @@ extern "C" int b2s_spmv_panels_peers(int val_type, int ptr_type, const void* p_d
     return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
                                           n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
                                           nullptr, alpha, beta, tile_row_dev, carry_dev,
-                                          ypart_dev, status_dev, s, n_stacked, subpos_dev, &peers,
-                                          n_peers, row_offset));
+                                          ypart_dev, status_dev, s, n_stacked, subpos_dev,
+                                          tile_panel_dev, &peers, n_peers, row_offset));
   }));
   return B2S_ERR_DTYPE;
 }
@@ -791,14 +640,17 @@ extern "C" int b2s_spmv_csr(int val_type, int idx_type, int ptr_type, const void
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-constexpr int64_t kFixedMaxTiles = 1 << 16;  // 65,536 tiles = 67,108,864 rows + non-zeros
+constexpr int64_t kFixedMaxItems = 1 << 26;  // rows + non-zeros one call may bring
+// tiles of the narrowest tile shape (complex128) that many items make
+constexpr int64_t kFixedMaxTiles =
+    (kFixedMaxItems + b2s::SpmvShape<b2s::c128>::ITEMS - 1) / b2s::SpmvShape<b2s::c128>::ITEMS;
 
 struct FixedScratch {
   int64_t tile_row[kFixedMaxTiles + 1];
   alignas(16) unsigned char carry[kFixedMaxTiles * 16];  // one value of the widest dtype per tile
 };
 
-// About 1.5 MB of device memory on every GPU that loads the library, held until exit.
+// About 3.2 MB of device memory on every GPU that loads the library, held until exit.
 static __device__ __align__(256) unsigned char g_fixed_scratch[sizeof(FixedScratch)];
 
 // In host code the name g_fixed_scratch is only a stand-in for the device array, not its
@@ -825,7 +677,7 @@ int fixed_scratch_for_current_device(FixedScratch** out) {
 }  // namespace
 
 extern "C" int64_t b2s_spmv_csr_fixed_max_items(void) {
-  return kFixedMaxTiles * static_cast<int64_t>(b2s::SpmvCfg<float, int32_t>::ITEMS);
+  return kFixedMaxItems;
 }
 
 extern "C" int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type, const void* data_dev,
@@ -835,7 +687,9 @@ extern "C" int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type, cons
                                   const void* beta, b2s_stream stream) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0) return B2S_ERR_ARG;
   const int items = b2s_spmv_tile_items(val_type, idx_type);
-  if (b2s_tile_count(n_rows, nnz, items) > kFixedMaxTiles) return B2S_ERR_TOO_LARGE;
+  if (items <= 0) return B2S_ERR_DTYPE;
+  if (n_rows + nnz > kFixedMaxItems || b2s_tile_count(n_rows, nnz, items) > kFixedMaxTiles)
+    return B2S_ERR_TOO_LARGE;
   if (n_rows == 0) return B2S_OK;
   FixedScratch* fs = nullptr;
   int st = fixed_scratch_for_current_device(&fs);

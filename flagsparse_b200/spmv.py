@@ -267,21 +267,22 @@ def _spmv_launch_record(plan: CsrPlan):
         n_tiles, tile_row = plan.tiles(items)
         head = (plan.vcode, plan.icode, plan.pcode, _lib.ptr(plan.data), _lib.ptr(plan.indices),
                 _lib.ptr(plan.indptr), plan.n_rows, plan.n_cols, plan.nnz)
-        rec = (lib.b2s_spmv_csr, head, _lib.ptr(tile_row), n_tiles, None, _lib.ptr(plan.status))
+        rec = (lib.b2s_spmv_csr, head, _lib.ptr(tile_row), n_tiles, None, _lib.ptr(plan.status),
+               None)
     else:
-        n_tiles, tile_row = plan.panel_tiles(items)
+        n_tiles, tile_row, tile_panel = plan.panel_tiles(items)
         head = (plan.vcode, lay.pcode, _lib.ptr(lay.data), _lib.ptr(lay.cols), _lib.ptr(lay.ptr),
                 plan.n_rows, plan.n_cols, plan.nnz, lay.n_panels, lay.shift,
                 _lib.ptr(lay.panel_start))
         rec = (lib.b2s_spmv_panels, head, _lib.ptr(tile_row), n_tiles, lay,
-               _lib.ptr(plan.status))
+               _lib.ptr(plan.status), _lib.ptr(tile_panel))
     plan._spmv_record = rec
     return rec
 
 
 def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
     """Enqueue y = alpha * A x + beta * y_in on the current stream (no synchronisation)."""
-    fn, head, tile_row_p, n_tiles, lay, status_p = _spmv_launch_record(plan)
+    fn, head, tile_row_p, n_tiles, lay, status_p, tile_panel_p = _spmv_launch_record(plan)
     dtype = plan.data.dtype
     a = _scalar(alpha, dtype)
     b = _scalar(beta, dtype)
@@ -299,7 +300,7 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
         else:
             ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
             st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream, lay.n_stacked,
-                    _lib.ptr(lay.subpos))
+                    _lib.ptr(lay.subpos), tile_panel_p)
     finally:
         if switch:
             torch.cuda.set_device(prev)
@@ -327,7 +328,7 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     store_stream a small grid runs beside the next block's tile kernel."""
     plan = prepared.plan()
     lib = _lib.load()
-    fn, head, tile_row_p, n_tiles, lay, status_p = _spmv_launch_record(plan)
+    fn, head, tile_row_p, n_tiles, lay, status_p, tile_panel_p = _spmv_launch_record(plan)
     dtype = plan.data.dtype
     itemsize = plan.data.element_size()
     if row_offset < 0 or row_offset + plan.n_rows > peer_rows:
@@ -343,7 +344,8 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
             one, zero = _scalar(1.0, dtype), _scalar(0.0, dtype)
             st = lib.b2s_spmv_panels(
                 *head, _lib.ptr(x), None, None, one, zero, tile_row_p, _lib.ptr(carry),
-                _lib.ptr(ypart), status_p, stream, lay.n_stacked, _lib.ptr(lay.subpos))
+                _lib.ptr(ypart), status_p, stream, lay.n_stacked, _lib.ptr(lay.subpos),
+                tile_panel_p)
             _lib.check(st, "b2s_spmv_panels")
             done = torch.cuda.Event()
             done.record(torch.cuda.current_stream(plan.device))
@@ -358,7 +360,7 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
             st = lib.b2s_spmv_panels_peers(
                 *head, _lib.ptr(x), _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows,
                 a, b, tile_row_p, _lib.ptr(carry), _lib.ptr(ypart), status_p, stream,
-                lay.n_stacked, _lib.ptr(lay.subpos))
+                lay.n_stacked, _lib.ptr(lay.subpos), tile_panel_p)
             _lib.check(st, "b2s_spmv_panels_peers")
         else:
             tmp = plan.scratch_on("spmv_peer_block", plan.n_rows, stream)

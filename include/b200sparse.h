@@ -35,7 +35,10 @@ typedef enum {
   B2S_ERR_TIMEOUT = 5,    /* (device status word) a bounded wait in a kernel ran out */
   B2S_ERR_WORKSPACE = 6,  /* scratch buffer smaller than *_bytes() asked for      */
   B2S_ERR_RANGE = 7,      /* a size does not fit the requested index dtype        */
-  B2S_ERR_TOO_LARGE = 8   /* problem exceeds the fixed scratch of b2s_spmv_csr_fixed */
+  B2S_ERR_TOO_LARGE = 8,  /* problem exceeds the fixed scratch of b2s_spmv_csr_fixed */
+  B2S_ERR_BOUNDS = 9      /* (device status word, bounds-checked build only) a column index or
+                             row pointer read from the matrix points outside its array; the
+                             access was skipped                                       */
 } b2s_status;
 
 /* value dtypes (order follows FlagSparse's SUPPORTED_VALUE_DTYPES, _common.py:21-29) */
@@ -49,25 +52,11 @@ typedef void* b2s_stream;
 int b2s_version(void);
 const char* b2s_status_string(int status);
 
-/* Run-time tuning knobs of the kernels (no counterpart in the reference, whose tuning lives in
- * Python keyword arguments such as block_nnz, spmv_csr.py:819-820).  Knob 0: L2 eviction hint on
- * the x gather (0 none, 1 evict-last).  Knob 1: L2 fetch granularity in bytes for this context.
- * Knob 2: bytes of x kept in the persisting part of L2 (0 = off). */
-int b2s_tune(int knob, int64_t value);
-
 /* Failure-path self-test (no counterpart in the reference): launches one warp that waits, with
  * `spin_limit` (1..100000) bounded tries of about a microsecond each, on a barrier nothing
  * completes.  The wait runs out, bit B2S_ERR_TIMEOUT is ORed into *status_dev and the kernel
  * returns normally -- the behaviour every bounded wait in the library has when a copy is lost. */
 int b2s_selftest_wait_timeout(int32_t* status_dev, int spin_limit, b2s_stream stream);
-
-/* Measurement aid (no counterpart in the reference): n divergent 8-byte gathers x[idx[i]] and
- * nothing else -- idx read coalesced, eight gathers per thread in flight, sums discarded.  Timed
- * by the caller over an L2-resident x it gives the ceiling the SpMV gather of x runs against
- * (one gather per clock per SM on B200).  idx values must lie in [0, n_x); *sink_dev (one
- * double) is written only if a sum takes a value it cannot take. */
-int b2s_probe_gather(const int32_t* idx_dev, int64_t n, const double* x_dev, int64_t n_x,
-                     double* sink_dev, b2s_stream stream);
 
 /* ---- input contract ------------------------------------------------------------------------
  * Replaces the device reductions behind the `.item()` checks of _prepare_spmv_csr_matrix
@@ -121,7 +110,7 @@ int b2s_spmv_csr(int val_type, int idx_type, int ptr_type,
  * arena at start-up, a solver loop under a no-allocation-after-initialisation rule, a plug-in
  * whose host owns the allocator.  b2s_spmv_csr_fixed computes the same y = alpha * A x +
  * beta * y_in with the same kernels and takes both scratch areas from one fixed array inside the
- * library (about 1.5 MB per GPU, held from library load to process exit).  It calls no
+ * library (about 3.2 MB per GPU, held from library load to process exit).  It calls no
  * cudaMalloc / cudaFree and no allocating library routine.
  *   - Limit: n_rows + nnz <= b2s_spmv_csr_fixed_max_items() (67,108,864); larger problems return
  *     B2S_ERR_TOO_LARGE and launch nothing.
@@ -157,6 +146,9 @@ int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type,
  * takes the compacted pointers as p_ptr_dev, n_stacked = count and subpos_dev (or
  * n_stacked = n_panels * n_rows and subpos_dev = NULL for the uncompacted stack); tile_row /
  * carry / ypart are sized for n_stacked rows (b2s_tile_count(n_stacked, nnz, items)).
+ * tile_panel_dev (may be NULL): int32 per tile, the panel of the tile's first non-zero, i.e. the
+ * largest p with panel_start[p] <= t * items - tile_row[t]; without it every CTA searches
+ * panel_start itself.
  */
 int64_t b2s_panel_compact_bytes(int64_t n_stacked);
 int b2s_panel_compact(const void* p_ptr_dev, int p_ptr_type, int64_t n_stacked,
@@ -187,7 +179,8 @@ int b2s_spmv_panels(int val_type, int ptr_type,
                     const void* alpha, const void* beta,
                     const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
                     int32_t* status_dev, b2s_stream stream,
-                    int64_t n_stacked, const int32_t* subpos_dev);
+                    int64_t n_stacked, const int32_t* subpos_dev,
+                    const int32_t* tile_panel_dev);
 
 /* ---- all-gather fused into the last kernel (several GPUs, no counterpart in the reference) ----
  * In a row-partitioned product every rank owns rows [row_offset, row_offset + n_rows) of the
@@ -210,7 +203,8 @@ int b2s_spmv_panels_peers(int val_type, int ptr_type,
                           const void* alpha, const void* beta,
                           const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
                           int32_t* status_dev, b2s_stream stream,
-                          int64_t n_stacked, const int32_t* subpos_dev);
+                          int64_t n_stacked, const int32_t* subpos_dev,
+                          const int32_t* tile_panel_dev);
 int b2s_peer_scatter(const void* src_dev, int64_t bytes, void* const* peer_dst, int n_peers,
                      int64_t dst_offset_bytes, int64_t peer_bytes, b2s_stream stream);
 /* The combine + store step alone: b2s_spmv_panels called with y_dev == NULL stops after the

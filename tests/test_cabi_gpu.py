@@ -233,19 +233,3 @@ def test_csr2csc_with_more_than_2_31_columns_uses_the_64_bit_sort():
     assert bool((t_ptr[1:200_000] >= t_ptr[:199_999]).all())
     del ws, t_ptr
     torch.cuda.empty_cache()
-
-
-def test_gather_probe_runs_and_checks_its_arguments():
-    """The measurement aid reads n indices and gathers from x without touching the sink; it
-    covers whole 1024-index passes and the ragged tail, and rejects bad arguments."""
-    lib, L = _lib()
-    x = torch.arange(64, dtype=torch.float64, device="cuda")
-    sink = torch.full((1,), 7.0, dtype=torch.float64, device="cuda")
-    stream = L.stream_handle(x.device)
-    for n in (0, 1, 1023, 1024, 5000):
-        idx = torch.randint(0, 64, (max(n, 1),), dtype=torch.int32, device="cuda")
-        assert lib.b2s_probe_gather(L.ptr(idx), n, L.ptr(x), 64, L.ptr(sink), stream) == 0
-    torch.cuda.synchronize()
-    assert float(sink.item()) == 7.0
-    assert lib.b2s_probe_gather(L.ptr(idx), -1, L.ptr(x), 64, L.ptr(sink), stream) == 2
-    assert lib.b2s_probe_gather(None, 8, L.ptr(x), 64, L.ptr(sink), stream) == 2
