@@ -17,6 +17,7 @@ from ._contract import (
 from ._plan import (
     clear_plan_cache,
     set_long_row_policy,
+    set_long_spmv_policy,
     set_panel_policy,
     set_plan_cache_capacity,
     set_window_policy,
@@ -74,6 +75,7 @@ __all__ = [
     "set_plan_cache_capacity",
     "set_panel_policy",
     "set_long_row_policy",
+    "set_long_spmv_policy",
     "set_window_policy",
     "SUPPORTED_VALUE_DTYPES",
     "SUPPORTED_INDEX_DTYPES",

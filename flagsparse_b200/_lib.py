@@ -57,15 +57,19 @@ SIGNATURES = {
     "b2s_panel_build_global": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_int64, c_void_p]),
-    "b2s_spmv_panels": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                                c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_int64, c_void_p, c_void_p]),
-    "b2s_spmv_panels_peers": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
-                                      c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
-                                      c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p,
-                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_int64, c_void_p, c_void_p]),
+    "b2s_spmv_stack_tile_items": (c_int, [c_int]),
+    "b2s_spmv_stack_shared_cols": (c_int, [c_int]),
+    "b2s_spmv_stack": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p]),
+    "b2s_spmv_stack_shared": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                      c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p]),
+    "b2s_spmv_stack_rows_combine": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                            c_void_p]),
+    "b2s_panel_combine": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p]),
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_int, c_void_p]),

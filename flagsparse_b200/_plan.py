@@ -48,6 +48,32 @@ PANEL_TARGET_BYTES = 40 << 20    # largest x slice of one panel
 PANEL_MIN_NNZ = 1 << 22          # below this the conversion is not worth its memory
 
 
+# Long rows of SpMV from shared memory (b2s_spmv_stack_shared): rows with at least
+# LONG_SPMV_MIN_PER_PANEL entries per narrow panel on average are taken out of the wide-panel
+# stack and multiplied with their x slices held in shared memory.  Used only together with the
+# panel layout, and only when those rows hold at least LONG_SPMV_MIN_SHARE of the non-zeros.
+LONG_SPMV_POLICY = "auto"
+LONG_SPMV_MIN_PER_PANEL = 4
+LONG_SPMV_MIN_SHARE = 0.1
+LONG_SPMV_TILES_PER_UNIT = 128
+
+
+def set_long_spmv_policy(policy="auto", min_per_panel=None, min_share=None, tiles_per_unit=None):
+    """'auto' (default) or 'off': whether SpMV may multiply the long rows of a panel-layout
+    matrix from shared-memory slices of x.  The other arguments override the thresholds."""
+    global LONG_SPMV_POLICY, LONG_SPMV_MIN_PER_PANEL, LONG_SPMV_MIN_SHARE
+    global LONG_SPMV_TILES_PER_UNIT
+    if policy not in ("auto", "off"):
+        raise ValueError("long-row policy must be 'auto' or 'off'")
+    LONG_SPMV_POLICY = policy
+    if min_per_panel is not None:
+        LONG_SPMV_MIN_PER_PANEL = float(min_per_panel)
+    if min_share is not None:
+        LONG_SPMV_MIN_SHARE = float(min_share)
+    if tiles_per_unit is not None:
+        LONG_SPMV_TILES_PER_UNIT = max(1, int(tiles_per_unit))
+
+
 def set_panel_policy(policy):
     """'auto' (default) or 'off': whether SpMV may keep a column-panel copy of large matrices."""
     global PANEL_POLICY
@@ -157,16 +183,148 @@ def build_panel_stack(data, indices, indptr, n_rows, n_cols, n_panels, shift, gl
     return p_data, p_cols, p_ptr, panel_start, n_stacked, subpos
 
 
-class PanelLayout:
-    """The matrix as a stack of column panels (see include/b200sparse.h, b2s_panel_build)."""
+STACK_END = -(1 << 31)   # bit 31 of a column word: last entry of its stacked row
+STACK_PAD = 1 << 30      # bit 30: padding entry
 
-    def __init__(self, data, cols, ptr, panel_start, n_panels, shift, n_stacked, subpos):
-        self.data, self.cols, self.ptr, self.panel_start = data, cols, ptr, panel_start
-        self.n_panels, self.shift = n_panels, shift
-        self.n_stacked = int(n_stacked)     # rows of the stack the kernel sees
-        self.subpos = subpos                # int32[n_panels * n_rows] or None (nothing dropped)
-        self.pcode = _lib.INDEX_CODE[ptr.dtype]
-        self.tiles = {}
+
+class StackLayout:
+    """The matrix as a stack of wide column panels in end-flag form (include/b200sparse.h,
+    b2s_spmv_stack): values and flagged panel-local columns padded to whole tiles, the ordinal
+    of the stacked row active at each tile start, the panel of each tile, and the position
+    table the combine uses."""
+
+    def __init__(self, vals, cols, n_stacked, tile_ord, tile_panel, panel_start, n_panels, shift,
+                 subpos, tile):
+        self.vals, self.cols = vals, cols
+        self.n_entries = int(vals.numel())
+        self.n_stacked = int(n_stacked)
+        self.tile_ord, self.tile_panel, self.panel_start = tile_ord, tile_panel, panel_start
+        self.n_panels, self.shift = int(n_panels), int(shift)
+        self.subpos = subpos                # int32[n_panels * n_rows]
+        self.n_tiles = self.n_entries // int(tile)
+        self.long_rows = None               # LongRowStack when the long rows were taken out
+
+
+class LongRowStack:
+    """The long rows of a matrix as a stack of narrow column panels in end-flag form
+    (b2s_spmv_stack_shared): every panel padded to whole tiles, `units` = (panel, first tile,
+    tiles) triples, one per CTA; `rows` the matrix rows they came from and, per long row, the
+    list of its stacked rows in ascending panel order (seg_ptr / seg_ids)."""
+
+    def __init__(self, vals, cols, n_stacked, tile_ord, units, rows, seg_ptr, seg_ids, shift,
+                 tile):
+        self.vals, self.cols = vals, cols
+        self.n_entries = int(vals.numel())
+        self.n_stacked = int(n_stacked)
+        self.tile_ord, self.units = tile_ord, units
+        self.n_units = int(units.numel()) // 3
+        self.rows, self.seg_ptr, self.seg_ids = rows, seg_ptr, seg_ids
+        self.n_long = int(rows.numel())
+        self.shift = int(shift)
+        self.n_tiles = self.n_entries // int(tile)
+
+
+def _exclusive_cumsum(counts):
+    out = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=counts.device)
+    torch.cumsum(counts, 0, out=out[1:])
+    return out
+
+
+def row_entry_positions(ptr64, rows):
+    """Positions (int64) of the entries of rows `rows` in the CSR arrays, row after row."""
+    lens = ptr64[rows + 1] - ptr64[rows]
+    ptr_l = _exclusive_cumsum(lens)
+    total = int(ptr_l[-1].item())
+    gidx = torch.repeat_interleave(ptr64[rows] - ptr_l[:-1], lens)
+    gidx += torch.arange(total, dtype=torch.int64, device=ptr64.device)
+    return gidx, lens
+
+
+def build_stack_layout(data, indices, indptr, n_rows, n_cols, n_panels, shift):
+    """End-flag stack of wide panels from a CSR matrix, or None when the stack cannot be
+    compacted (more than 2^31 stacked rows)."""
+    lib = _lib.load()
+    p_data, p_cols, p_ptr, panel_start, n_stacked, subpos = build_panel_stack(
+        data, indices, indptr, n_rows, n_cols, n_panels, shift, global_cols=False)
+    if subpos is None:
+        return None
+    device = data.device
+    nnz = int(p_data.numel())
+    tile = int(lib.b2s_spmv_stack_tile_items(_lib.VALUE_CODE[data.dtype]))
+    n_tiles = (nnz + tile - 1) // tile
+    n_entries = n_tiles * tile
+    vals = torch.zeros(n_entries, dtype=data.dtype, device=device)
+    vals[:nnz] = p_data
+    del p_data
+    cols = torch.full((n_entries,), STACK_PAD, dtype=torch.int32, device=device)
+    cols[:nnz] = p_cols
+    del p_cols
+    ptr64 = p_ptr.to(torch.int64)
+    del p_ptr
+    if n_stacked > 0:
+        cols[ptr64[1:] - 1] |= STACK_END          # every stacked row is non-empty
+    starts = torch.arange(n_tiles + 1, dtype=torch.int64, device=device) * tile
+    # rows whose last entry lies before the tile start = ordinal of the row active there
+    tile_ord = torch.searchsorted(ptr64[1:].contiguous(), starts, right=True)
+    tile_panel = (torch.searchsorted(panel_start, starts[:n_tiles].contiguous(), right=True)
+                  - 1).clamp_(0, n_panels - 1).to(torch.int32)
+    return StackLayout(vals, cols, n_stacked, tile_ord, tile_panel, panel_start, n_panels, shift,
+                       subpos, tile)
+
+
+def build_long_row_stack(data, indices, indptr, rows, n_cols, shift, tiles_per_unit):
+    """End-flag stack of narrow panels (2^shift columns) from rows `rows` (int64, ascending) of a
+    CSR matrix; the one-off sort runs in torch."""
+    lib = _lib.load()
+    device = data.device
+    tile = int(lib.b2s_spmv_stack_tile_items(_lib.VALUE_CODE[data.dtype]))
+    n_long = int(rows.numel())
+    gidx, lens = row_entry_positions(indptr.to(torch.int64), rows)
+    nnz_l = int(gidx.numel())
+    rid = torch.repeat_interleave(torch.arange(n_long, dtype=torch.int64, device=device), lens)
+    col = indices[gidx].to(torch.int64)
+    key = (col >> shift) * n_long + rid            # (panel, long row); stable: row order kept
+    key, order = torch.sort(key, stable=True)
+    del rid
+    vals_sorted = data[gidx[order]]
+    lcol = (col[order] & ((1 << shift) - 1)).to(torch.int32)
+    del col, gidx, order
+    end = torch.ones(nnz_l, dtype=torch.bool, device=device)
+    end[:-1] = key[1:] != key[:-1]
+    lcol[end] |= STACK_END
+    panel = key // n_long
+    n_panels = ((n_cols - 1) >> shift) + 1
+    cnt = torch.bincount(panel, minlength=n_panels)
+    padded = (cnt + tile - 1) // tile * tile
+    pstart, qstart = _exclusive_cumsum(cnt), _exclusive_cumsum(padded)
+    pos = qstart[panel] + (torch.arange(nnz_l, dtype=torch.int64, device=device) - pstart[panel])
+    n_entries = int(qstart[-1].item())
+    cols = torch.full((n_entries,), STACK_PAD, dtype=torch.int32, device=device)
+    cols[pos] = lcol
+    vals = torch.zeros(n_entries, dtype=data.dtype, device=device)
+    vals[pos] = vals_sorted
+    del lcol, vals_sorted
+    end_pos = pos[end]                             # ascending
+    seg_key = key[end]                             # (panel, long row) of each stacked row
+    del key, pos, end, panel
+    n_seg = int(seg_key.numel())
+    n_tiles = n_entries // tile
+    starts = torch.arange(n_tiles + 1, dtype=torch.int64, device=device) * tile
+    tile_ord = torch.searchsorted(end_pos, starts, right=False)
+    # one CTA per run of at most tiles_per_unit tiles of one panel
+    tiles_p = (padded // tile).tolist()
+    tile0_p = (qstart[:-1] // tile).tolist()
+    units = []
+    for p, (t0, nt) in enumerate(zip(tile0_p, tiles_p)):
+        for k in range(0, nt, tiles_per_unit):
+            units += [p, t0 + k, min(tiles_per_unit, nt - k)]
+    units = torch.tensor(units, dtype=torch.int32, device=device)
+    # stacked rows of each long row, ascending panel
+    seg_rid = seg_key % n_long
+    order2 = torch.argsort(seg_rid * n_panels + seg_key // n_long)
+    seg_ids = order2.to(torch.int32)
+    seg_ptr = _exclusive_cumsum(torch.bincount(seg_rid, minlength=n_long))
+    return LongRowStack(vals, cols, n_seg, tile_ord, units, rows, seg_ptr, seg_ids, shift, tile)
 
 
 # Shared-memory window of B rows for SpMM on banded / local matrices (b2s_spmm_csr_windowed).
@@ -217,12 +375,15 @@ class CsrPlan:
         self._scratch = {}                   # (tag, width, stream) -> tensor
         self._transposed = {}                # conj flag -> CsrPlan of the transpose
         self._panels = False                 # False: not decided yet; None: not used
+        self.allow_long_rows = True          # SpMV may take the long rows out (see panels())
         self._long_rows = {}                 # panel shift -> LongRowSplit or None (SpMM)
         self._window = {}                    # tile_items -> widest column span of a tile (SpMM)
         self._spmv_record = None             # prebuilt launch arguments (spmv.py)
         self._prepared = {}                  # memo of PreparedCsrSpmv handles (spmv.py)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.status_checked = False
+        self._launches = 0                   # launches since the status word was last read
+        self._status_probe = None            # (pinned host copy, event) of a read in flight
 
     # -- tile plans ---------------------------------------------------------------------------
     def tiles(self, items):
@@ -257,7 +418,9 @@ class CsrPlan:
 
     # -- column panels ------------------------------------------------------------------------
     def panels(self):
-        """PanelLayout when the policy asks for one for this matrix, else None (built once)."""
+        """StackLayout when the policy asks for a column-panel layout of this matrix, else None
+        (built once).  Its `long_rows` holds the LongRowStack when the long rows were taken out
+        for the shared-memory kernel."""
         if self._panels is not False:
             return self._panels
         self._panels = None
@@ -269,14 +432,50 @@ class CsrPlan:
         while (2 << shift) * vbytes <= PANEL_TARGET_BYTES:
             shift += 1
         n_panels = ((self.n_cols - 1) >> shift) + 1
-        if n_panels < 2 or n_panels > 256 or shift > 31:
+        if n_panels < 2 or n_panels > 256 or shift > 29:
             return None
-        p_data, p_cols, p_ptr, panel_start, n_stacked, subpos = build_panel_stack(
-            self.data, self.indices, self.indptr, self.n_rows, self.n_cols, n_panels, shift,
-            global_cols=False)
-        self._panels = PanelLayout(p_data, p_cols, p_ptr, panel_start, n_panels, shift,
-                                   n_stacked, subpos)
-        return self._panels
+        data, indices, indptr = self.data, self.indices, self.indptr
+        long_stack = self._long_rows_for_spmv()
+        if long_stack is not None:
+            # the wide-panel stack keeps every row but the long ones, which become empty
+            ptr64 = indptr.to(torch.int64)
+            lens = ptr64[1:] - ptr64[:-1]
+            keep = torch.ones(self.nnz, dtype=torch.bool, device=self.device)
+            rows = long_stack.rows
+            keep[row_entry_positions(ptr64, rows)[0]] = False
+            data, indices = data[keep], indices[keep]
+            del keep
+            lens[rows] = 0
+            indptr = _exclusive_cumsum(lens)
+            del lens, ptr64
+        lay = build_stack_layout(data, indices, indptr, self.n_rows, self.n_cols, n_panels, shift)
+        if lay is None:
+            return None
+        lay.long_rows = long_stack
+        self._panels = lay
+        return lay
+
+    def _long_rows_for_spmv(self):
+        """LongRowStack of the rows long enough for the shared-memory kernel, or None."""
+        if LONG_SPMV_POLICY != "auto" or not self.allow_long_rows:
+            return None
+        lib = _lib.load()
+        width = int(lib.b2s_spmv_stack_shared_cols(self.vcode))
+        shift = width.bit_length() - 1
+        n_panels = ((self.n_cols - 1) >> shift) + 1
+        min_len = max(int(LONG_SPMV_MIN_PER_PANEL * n_panels), 2)
+        if 0 <= self.max_row_nnz < min_len:
+            return None
+        ptr64 = self.indptr.to(torch.int64)
+        lens = ptr64[1:] - ptr64[:-1]
+        rows = torch.nonzero(lens >= min_len).flatten()
+        if rows.numel() == 0 or rows.numel() > 65536:
+            return None
+        if int(lens[rows].sum().item()) < LONG_SPMV_MIN_SHARE * self.nnz:
+            return None
+        del lens, ptr64
+        return build_long_row_stack(self.data, self.indices, self.indptr, rows, self.n_cols,
+                                    shift, LONG_SPMV_TILES_PER_UNIT)
 
     # -- long rows by column panel (SpMM) --------------------------------------------------------
     def long_row_split(self, row_bytes):
@@ -356,27 +555,6 @@ class CsrPlan:
         self._window[items] = (rows, table)
         return self._window[items]
 
-    def panel_tiles(self, items):
-        lay = self._panels
-        hit = lay.tiles.get(items)
-        if hit is not None:
-            return hit
-        lib = _lib.load()
-        rows = lay.n_stacked
-        n_tiles = int(lib.b2s_tile_count(rows, self.nnz, items))
-        tile_row = torch.empty(n_tiles + 1, dtype=torch.int64, device=self.device)
-        with torch.cuda.device(self.device):
-            st = lib.b2s_tile_plan(_lib.ptr(lay.ptr), lay.pcode, rows, self.nnz, items,
-                                   _lib.ptr(tile_row), _lib.stream_handle(self.device))
-        _lib.check(st, "b2s_tile_plan")
-        # panel of each tile's first non-zero (first non-zero of tile t: t * items - tile_row[t])
-        first_nz = (torch.arange(n_tiles, dtype=torch.int64, device=self.device) * items
-                    - tile_row[:n_tiles])
-        tile_panel = (torch.searchsorted(lay.panel_start, first_nz, right=True) - 1).clamp_(
-            0, lay.n_panels - 1).to(torch.int32)
-        lay.tiles[items] = (n_tiles, tile_row, tile_panel)
-        return lay.tiles[items]
-
     # -- transpose ----------------------------------------------------------------------------
     def transposed(self, conj):
         """CsrPlan of A^T (conj=False) or A^H (conj=True), built once by b2s_csr2csc."""
@@ -405,15 +583,45 @@ class CsrPlan:
         self._transposed[conj] = plan
         return plan
 
+    STATUS_EVERY = 64   # launches between two non-blocking reads of the status word
+
+    def note_launch(self):
+        """Called after every launch that passed the status word.  The first launch of a plan
+        reads the word at once (synchronises, like the reference's validation does for a new
+        matrix); afterwards a non-blocking copy is started every STATUS_EVERY launches and
+        examined at the next call, so that an error bit set later (a bounded wait that ran
+        out, a bounds violation in the checked build) still raises, without a host
+        synchronisation on the steady-state path."""
+        if not self.status_checked:
+            self.check_status()
+            return
+        probe = self._status_probe
+        if probe is not None and probe[1].query():
+            self._status_probe = None
+            self._raise_for(int(probe[0].item()))
+        self._launches += 1
+        if self._launches >= self.STATUS_EVERY and self._status_probe is None:
+            self._launches = 0
+            host = torch.empty(1, dtype=torch.int32).pin_memory()
+            host.copy_(self.status, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream(self.device))
+            self._status_probe = (host, event)
+
     def check_status(self):
         """Read the device status word (synchronises); raise if a kernel reported an error."""
-        bits = int(self.status.item())
         self.status_checked = True
+        self._raise_for(int(self.status.item()))
+
+    def _raise_for(self, bits):
         if bits:
             self.status.zero_()
             if bits & (1 << _lib.B2S_ERR_TIMEOUT):
                 raise RuntimeError("a bounded wait inside a b200sparse kernel ran out "
                                    "(bulk copy did not complete)")
+            if bits & (1 << _lib.B2S_ERR_BOUNDS):
+                raise IndexError("a b200sparse kernel (bounds-checked build) met a column index "
+                                 "or row pointer outside its array")
             raise RuntimeError(f"b200sparse kernels reported error bits {bits:#x}")
 
 

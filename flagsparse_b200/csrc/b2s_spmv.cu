@@ -17,9 +17,8 @@
 // adds those partials to the row in ascending tile order.  No floating-point atomics and only
 // fixed trees: results repeat bit for bit for a given matrix and build.
 //
-// Column-panel layout (b2s_spmv_panels): the same kernel runs over a stack of CSR matrices, one
-// per panel of columns, with panel-local int32 columns; partial results per (panel, row) are
-// added in ascending panel order by panel_combine_kernel.
+// Matrices whose x does not fit L2 are multiplied from a column-panel layout by the kernels of
+// b2s_spmv_stack.cu; the combine kernels at the end of this file add the per-panel partials.
 #include <mutex>
 
 #include "b2s_tile.cuh"
@@ -92,9 +91,7 @@ __global__ void __launch_bounds__(SpmvShape<V>::THREADS, spmv_min_blocks<V, I>()
 spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
                  const V* __restrict__ x, const V* y_in, V* y, V* __restrict__ carry,
                  const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t n_cols,
-                 int64_t nnz, V alpha, V beta, int has_beta, int phase, int32_t* status,
-                 const int64_t* __restrict__ panel_start,
-                 const int32_t* __restrict__ tile_panel, int n_panels, int panel_shift) {
+                 int64_t nnz, V alpha, V beta, int has_beta, int phase, int32_t* status) {
   using S = SpmvShape<V>;
   constexpr int THREADS = S::THREADS, SPT = S::SPT, SLOTS = S::SLOTS, ITEMS = S::ITEMS;
   constexpr int WARPS = THREADS / 32;
@@ -123,25 +120,6 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int lo = a - sb;              // this thread's live elements are lo <= i < hi
   const int hi = a + n_nz - sb;
   const bool live = hi > 0 && lo < SPT;
-
-  // column-panel layout: the matrix is a stack of panels with panel-local columns; the non-zeros
-  // of panel p start at panel_start[p].  Panel of the tile's first non-zero:
-  int p_lo = 0;
-  int straddle = SPT;  // first element of this thread that lies in a later panel (rare)
-  if (panel_start != nullptr && n_nz > 0) {
-    if (tile_panel != nullptr) {
-      p_lo = tile_panel[t];
-    } else {
-      int l = 0, h = n_panels - 1;
-      while (l < h) {
-        const int mid = (l + h + 1) >> 1;
-        if (panel_start[mid] <= tc.j0) l = mid; else h = mid - 1;
-      }
-      p_lo = l;
-    }
-    const int64_t left = panel_start[p_lo + 1] - jt;
-    straddle = left < 0 ? 0 : (left < SPT ? static_cast<int>(left) : SPT);
-  }
 
   // ---- col / val of this thread's slots, and the first row end, all in flight together --------
   I c[SPT];
@@ -172,26 +150,17 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
 
   // ---- gathers of x ---------------------------------------------------------------------------
   V xv[SPT];
-  {
-    const V* xp = x + (static_cast<int64_t>(p_lo) << panel_shift);
 #pragma unroll
-    for (int i = 0; i < SPT; ++i) {
-      xv[i] = vt<V>::zero();
-      if (i >= lo && i < hi) {
-        const V* src = xp + static_cast<int64_t>(c[i]);
-        if (i >= straddle) {  // the tile straddles a panel border
-          int pp = p_lo + 1;
-          while (pp + 1 < n_panels && jt + i >= panel_start[pp + 1]) ++pp;
-          src = x + (static_cast<int64_t>(pp) << panel_shift) + static_cast<int64_t>(c[i]);
-        }
+  for (int i = 0; i < SPT; ++i) {
+    xv[i] = vt<V>::zero();
+    if (i >= lo && i < hi) {
 #ifdef B2S_CHECKED
-        if (src < x || src >= x + n_cols) {  // never dereference a column outside x
-          if (status) atomicOr(status, 1 << B2S_ERR_BOUNDS);
-          continue;
-        }
-#endif
-        xv[i] = ldg_val(src);
+      if (static_cast<uint64_t>(c[i]) >= static_cast<uint64_t>(n_cols)) {
+        if (status) atomicOr(status, 1 << B2S_ERR_BOUNDS);  // never follow a column outside x
+        continue;
       }
+#endif
+      xv[i] = ldg_val(x + static_cast<int64_t>(c[i]));
     }
   }
 
@@ -322,8 +291,7 @@ template <class V, class I, class P>
 int spmv_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* x, const void* y_in, void* y, const void* alpha,
                 const void* beta, const int64_t* tile_row, void* carry, int32_t* status,
-                cudaStream_t stream, const int64_t* panel_start = nullptr, int n_panels = 0,
-                int panel_shift = 0, const int32_t* tile_panel = nullptr) {
+                cudaStream_t stream) {
   using S = SpmvShape<V>;
   const int64_t n_tiles = b2s_tile_count(n_rows, nnz, S::ITEMS);
   if (n_tiles == 0) return B2S_OK;
@@ -336,8 +304,7 @@ int spmv_launch(const void* data, const void* indices, const void* indptr, int64
   spmv_tile_kernel<V, I, P><<<static_cast<unsigned>(n_tiles), S::THREADS, 0, stream>>>(
       static_cast<const V*>(data), static_cast<const I*>(indices), static_cast<const P*>(indptr),
       static_cast<const V*>(x), static_cast<const V*>(y_in), static_cast<V*>(y),
-      static_cast<V*>(carry), tile_row, n_rows, n_cols, nnz, a, b, has_beta, phase, status,
-      panel_start, tile_panel, n_panels, panel_shift);
+      static_cast<V*>(carry), tile_row, n_rows, n_cols, nnz, a, b, has_beta, phase, status);
   if (n_tiles > 1) {
     const int fb = 256;
     spmv_fixup_kernel<V><<<static_cast<unsigned>((n_tiles + fb - 1) / fb), fb, 0, stream>>>(
@@ -426,85 +393,12 @@ __global__ void peer_scatter_kernel(const uint4* __restrict__ src, int64_t n16, 
   }
 }
 
-template <class V, class P>
-int spmv_panels_launch(const void* p_data, const int32_t* p_cols, const void* p_ptr,
-                       int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
-                       const int64_t* panel_start, const void* x, const void* y_in, void* y,
-                       const void* alpha, const void* beta, const int64_t* tile_row, void* carry,
-                       void* ypart, int32_t* status, cudaStream_t stream,
-                       int64_t n_stacked, const int32_t* subpos,
-                       const int32_t* tile_panel, const PeerList* peers = nullptr,
-                       int n_peers = 0, int64_t row_offset = 0) {
-  // 1) the stacked matrix (n_panels * n_rows rows, panel-local int32 columns) times x with
-  //    alpha = 1, beta = 0 -> one partial result per (panel, row)
-  const V one = vt<V>::one(), zero = vt<V>::zero();
-  int st = spmv_launch<V, int32_t, P>(p_data, p_cols, p_ptr, n_stacked, n_cols, nnz, x,
-                                      nullptr, ypart, &one, &zero, tile_row, carry, status,
-                                      stream, panel_start, n_panels, panel_shift, tile_panel);
-  if (st != B2S_OK) return st;
-  if (y == nullptr && peers == nullptr) return launch_status();  // caller combines separately
-  // 2) add the panels of each row and apply alpha / beta
-  const V a = *static_cast<const V*>(alpha);
-  const V b = *static_cast<const V*>(beta);
-  const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
-  if (has_beta && y_in == nullptr) return B2S_ERR_ARG;
-  const int threads = 256;
-  const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
-  if (peers != nullptr)
-    panel_combine_peers_kernel<V><<<grid, threads, 0, stream>>>(
-        static_cast<const V*>(ypart), subpos, n_rows, n_panels, static_cast<const V*>(y_in),
-        *peers, n_peers, row_offset, a, b, has_beta);
-  else if (subpos != nullptr)
-    panel_combine_sparse_kernel<V><<<grid, threads, 0, stream>>>(
-        static_cast<const V*>(ypart), subpos, n_rows, n_panels, static_cast<const V*>(y_in),
-        static_cast<V*>(y), a, b, has_beta);
-  else
-    panel_combine_kernel<V><<<grid, threads, 0, stream>>>(
-        static_cast<const V*>(ypart), n_rows, n_panels, static_cast<const V*>(y_in),
-        static_cast<V*>(y), a, b, has_beta);
-  return launch_status();
-}
-
 }  // namespace b2s
 
 extern "C" int b2s_spmv_tile_items(int val_type, int idx_type) {
   (void)idx_type;
   B2S_DISPATCH_V(val_type, { return b2s::SpmvShape<V>::ITEMS; });
   return 0;
-}
-
-extern "C" int b2s_spmv_panels(int val_type, int ptr_type, const void* p_data_dev,
-                               const int32_t* p_cols_dev, const void* p_ptr_dev, int64_t n_rows,
-                               int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
-                               const int64_t* panel_start_dev, const void* x_dev,
-                               const void* y_in_dev, void* y_dev, const void* alpha,
-                               const void* beta, const int64_t* tile_row_dev, void* carry_dev,
-                               void* ypart_dev, int32_t* status_dev, b2s_stream stream,
-                               int64_t n_stacked, const int32_t* subpos_dev,
-                               const int32_t* tile_panel_dev) {
-  if (n_rows < 0 || n_cols < 0 || nnz < 0 || !alpha || !beta) return B2S_ERR_ARG;
-  if (subpos_dev == nullptr) n_stacked = n_rows * n_panels;
-  if (n_stacked < 0 || n_stacked > n_rows * n_panels) return B2S_ERR_ARG;
-  if (n_panels < 1 || n_panels > 256 || panel_shift < 0 || panel_shift > 40) return B2S_ERR_ARG;
-  if (n_rows == 0) return B2S_OK;
-  if (!p_ptr_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
-    return B2S_ERR_ARG;  // y_dev == NULL: leave the per-panel partials in ypart_dev
-  if (nnz > 0 && (!p_data_dev || !p_cols_dev || !x_dev)) return B2S_ERR_ARG;
-  const size_t vs = b2s::vsize(val_type);
-  if (vs == 0) return B2S_ERR_DTYPE;
-  const uintptr_t m = vs - 1;
-  if ((reinterpret_cast<uintptr_t>(p_data_dev) & m) || (reinterpret_cast<uintptr_t>(x_dev) & m) ||
-      (reinterpret_cast<uintptr_t>(y_dev) & m) || (reinterpret_cast<uintptr_t>(y_in_dev) & m) ||
-      (reinterpret_cast<uintptr_t>(carry_dev) & m) || (reinterpret_cast<uintptr_t>(ypart_dev) & m))
-    return B2S_ERR_ALIGNMENT;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(ptr_type, P, {
-    return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
-                                          n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
-                                          y_dev, alpha, beta, tile_row_dev, carry_dev, ypart_dev,
-                                          status_dev, s, n_stacked, subpos_dev, tile_panel_dev));
-  }));
-  return B2S_ERR_DTYPE;
 }
 
 static int make_peer_list(void* const* peer_ptrs, int n_peers, size_t align,
@@ -519,40 +413,36 @@ static int make_peer_list(void* const* peer_ptrs, int n_peers, size_t align,
   return B2S_OK;
 }
 
-extern "C" int b2s_spmv_panels_peers(int val_type, int ptr_type, const void* p_data_dev,
-                                     const int32_t* p_cols_dev, const void* p_ptr_dev,
-                                     int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels,
-                                     int panel_shift, const int64_t* panel_start_dev,
-                                     const void* x_dev, const void* y_in_dev,
-                                     void* const* peer_y, int n_peers, int64_t row_offset,
-                                     int64_t peer_rows, const void* alpha, const void* beta,
-                                     const int64_t* tile_row_dev, void* carry_dev,
-                                     void* ypart_dev, int32_t* status_dev, b2s_stream stream,
-                                     int64_t n_stacked, const int32_t* subpos_dev,
-                                     const int32_t* tile_panel_dev) {
-  if (n_rows < 0 || n_cols < 0 || nnz < 0 || row_offset < 0 || !alpha || !beta) return B2S_ERR_ARG;
-  if (row_offset + n_rows > peer_rows) return B2S_ERR_ARG;  // block must fit the peers' buffers
-  if (subpos_dev == nullptr) n_stacked = n_rows * n_panels;
-  if (n_stacked < 0 || n_stacked > n_rows * n_panels) return B2S_ERR_ARG;
-  if (n_panels < 1 || n_panels > 256 || panel_shift < 0 || panel_shift > 40) return B2S_ERR_ARG;
+extern "C" int b2s_panel_combine(int val_type, const void* ypart_dev, const int32_t* subpos_dev,
+                                 int64_t n_rows, int n_panels, const void* y_in_dev, void* y_dev,
+                                 const void* alpha, const void* beta, b2s_stream stream) {
+  if (n_rows < 0 || n_panels < 1 || n_panels > 256 || !alpha || !beta) return B2S_ERR_ARG;
   if (n_rows == 0) return B2S_OK;
-  if (!p_ptr_dev || !tile_row_dev || !carry_dev || !ypart_dev || !panel_start_dev)
-    return B2S_ERR_ARG;
-  if (nnz > 0 && (!p_data_dev || !p_cols_dev || !x_dev)) return B2S_ERR_ARG;
+  if (!ypart_dev || !y_dev) return B2S_ERR_ARG;
   const size_t vs = b2s::vsize(val_type);
   if (vs == 0) return B2S_ERR_DTYPE;
-  b2s::PeerList peers;
-  const int pst = make_peer_list(peer_y, n_peers, vs, &peers);
-  if (pst != B2S_OK) return pst;
+  const uintptr_t m = vs - 1;
+  if ((reinterpret_cast<uintptr_t>(ypart_dev) & m) || (reinterpret_cast<uintptr_t>(y_dev) & m) ||
+      (reinterpret_cast<uintptr_t>(y_in_dev) & m))
+    return B2S_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(ptr_type, P, {
-    return (b2s::spmv_panels_launch<V, P>(p_data_dev, p_cols_dev, p_ptr_dev, n_rows, n_cols, nnz,
-                                          n_panels, panel_shift, panel_start_dev, x_dev, y_in_dev,
-                                          nullptr, alpha, beta, tile_row_dev, carry_dev,
-                                          ypart_dev, status_dev, s, n_stacked, subpos_dev,
-                                          tile_panel_dev, &peers, n_peers, row_offset));
-  }));
-  return B2S_ERR_DTYPE;
+  const int threads = 256;
+  const unsigned grid = static_cast<unsigned>((n_rows + threads - 1) / threads);
+  B2S_DISPATCH_V(val_type, {
+    const V a = *static_cast<const V*>(alpha);
+    const V b = *static_cast<const V*>(beta);
+    const int has_beta = b2s::vt<V>::is_zero(b) ? 0 : 1;
+    if (has_beta && y_in_dev == nullptr) return B2S_ERR_ARG;
+    if (subpos_dev != nullptr)
+      (b2s::panel_combine_sparse_kernel<V><<<grid, threads, 0, s>>>(
+          static_cast<const V*>(ypart_dev), subpos_dev, n_rows, n_panels,
+          static_cast<const V*>(y_in_dev), static_cast<V*>(y_dev), a, b, has_beta));
+    else
+      (b2s::panel_combine_kernel<V><<<grid, threads, 0, s>>>(
+          static_cast<const V*>(ypart_dev), n_rows, n_panels, static_cast<const V*>(y_in_dev),
+          static_cast<V*>(y_dev), a, b, has_beta));
+  });
+  return b2s::launch_status();
 }
 
 extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,

@@ -208,8 +208,7 @@ def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
             _lib.ptr(tile_row), _lib.ptr(carry), _lib.ptr(plan.status), window,
             _lib.ptr(table) if window else None, _lib.stream_handle(plan.device))
     _lib.check(st, "b2s_spmm_csr")
-    if not plan.status_checked:
-        plan.check_status()
+    plan.note_launch()
 
 
 def _row_major_ok(t):

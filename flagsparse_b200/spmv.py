@@ -256,33 +256,83 @@ def _scalar(value, dtype):
 
 def _spmv_launch_record(plan: CsrPlan):
     """Everything about a launch that depends only on the matrix, as ready-made ctypes values
-    (built once per plan; keeps the steady-state call short for launch-latency-bound sizes)."""
+    (built once per plan; keeps the steady-state call short for launch-latency-bound sizes).
+    Returns ("csr", fn, head, tile_row pointer, tiles) or ("stack", layout)."""
     rec = plan._spmv_record
     if rec is not None:
         return rec
     lib = _lib.load()
-    items = lib.b2s_spmv_tile_items(plan.vcode, plan.icode)
     lay = plan.panels()
     if lay is None:
+        items = lib.b2s_spmv_tile_items(plan.vcode, plan.icode)
         n_tiles, tile_row = plan.tiles(items)
         head = (plan.vcode, plan.icode, plan.pcode, _lib.ptr(plan.data), _lib.ptr(plan.indices),
                 _lib.ptr(plan.indptr), plan.n_rows, plan.n_cols, plan.nnz)
-        rec = (lib.b2s_spmv_csr, head, _lib.ptr(tile_row), n_tiles, None, _lib.ptr(plan.status),
-               None)
+        rec = ("csr", lib.b2s_spmv_csr, head, _lib.ptr(tile_row), n_tiles)
     else:
-        n_tiles, tile_row, tile_panel = plan.panel_tiles(items)
-        head = (plan.vcode, lay.pcode, _lib.ptr(lay.data), _lib.ptr(lay.cols), _lib.ptr(lay.ptr),
-                plan.n_rows, plan.n_cols, plan.nnz, lay.n_panels, lay.shift,
-                _lib.ptr(lay.panel_start))
-        rec = (lib.b2s_spmv_panels, head, _lib.ptr(tile_row), n_tiles, lay,
-               _lib.ptr(plan.status), _lib.ptr(tile_panel))
+        rec = ("stack", lay)
     plan._spmv_record = rec
     return rec
 
 
+def _launch_stack_partials(plan, lay, x, stream):
+    """Enqueue the wide-panel stack kernel; returns the per-(panel, row) partials."""
+    lib = _lib.load()
+    ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
+    carry = plan.scratch_on("spmv_stack_carry", lay.n_tiles, stream)
+    st = lib.b2s_spmv_stack(
+        plan.vcode, _lib.ptr(lay.vals), _lib.ptr(lay.cols), lay.n_entries, lay.n_stacked,
+        plan.n_cols, lay.n_panels, lay.shift, _lib.ptr(lay.panel_start),
+        _lib.ptr(lay.tile_panel), _lib.ptr(lay.tile_ord), _lib.ptr(x), _lib.ptr(ypart),
+        _lib.ptr(carry), _lib.ptr(plan.status), stream)
+    if st:
+        _lib.check(st, "b2s_spmv_stack")
+    return ypart
+
+
+def _launch_long_rows(plan, lay, x, y, a, stream):
+    """y[long rows] += alpha * (their products), from shared-memory slices of x."""
+    lib = _lib.load()
+    lr = lay.long_rows
+    part = plan.scratch_on("spmv_long_part", lr.n_stacked, stream)
+    carry = plan.scratch_on("spmv_long_carry", lr.n_tiles, stream)
+    st = lib.b2s_spmv_stack_shared(
+        plan.vcode, _lib.ptr(lr.vals), _lib.ptr(lr.cols), lr.n_entries, lr.n_stacked,
+        plan.n_cols, lr.shift, _lib.ptr(lr.units), lr.n_units, _lib.ptr(lr.tile_ord),
+        _lib.ptr(x), _lib.ptr(part), _lib.ptr(carry), _lib.ptr(plan.status), stream)
+    if st:
+        _lib.check(st, "b2s_spmv_stack_shared")
+    st = lib.b2s_spmv_stack_rows_combine(
+        plan.vcode, _lib.ptr(part), _lib.ptr(lr.seg_ptr), _lib.ptr(lr.seg_ids),
+        _lib.ptr(lr.rows), lr.n_long, lr.n_stacked, _lib.ptr(y), a, _lib.ptr(plan.status), stream)
+    if st:
+        _lib.check(st, "b2s_spmv_stack_rows_combine")
+
+
+def _enqueue_spmv(plan, rec, x, y, y_in, a, b, stream):
+    """The kernels of y = alpha * A x + beta * y_in on `stream` (device of the plan current)."""
+    lib = _lib.load()
+    if rec[0] == "csr":
+        _, fn, head, tile_row_p, n_tiles = rec
+        carry = plan.scratch_on("spmv_carry", n_tiles, stream)
+        st = fn(*head, _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b, tile_row_p,
+                _lib.ptr(carry), _lib.ptr(plan.status), stream)
+        if st:
+            _lib.check(st, "b2s_spmv_csr")
+        return
+    lay = rec[1]
+    ypart = _launch_stack_partials(plan, lay, x, stream)
+    st = lib.b2s_panel_combine(plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows,
+                               lay.n_panels, _lib.ptr(y_in), _lib.ptr(y), a, b, stream)
+    if st:
+        _lib.check(st, "b2s_panel_combine")
+    if lay.long_rows is not None:
+        _launch_long_rows(plan, lay, x, y, a, stream)
+
+
 def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
     """Enqueue y = alpha * A x + beta * y_in on the current stream (no synchronisation)."""
-    fn, head, tile_row_p, n_tiles, lay, status_p, tile_panel_p = _spmv_launch_record(plan)
+    rec = _spmv_launch_record(plan)
     dtype = plan.data.dtype
     a = _scalar(alpha, dtype)
     b = _scalar(beta, dtype)
@@ -292,22 +342,12 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
         prev = torch.cuda.current_device()
         torch.cuda.set_device(dev_index)
     try:
-        stream = torch.cuda.current_stream(plan.device).cuda_stream
-        carry = plan.scratch_on("spmv_carry", n_tiles, stream)
-        tail = (_lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b, tile_row_p, _lib.ptr(carry))
-        if lay is None:
-            st = fn(*head, *tail, status_p, stream)
-        else:
-            ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
-            st = fn(*head, *tail, _lib.ptr(ypart), status_p, stream, lay.n_stacked,
-                    _lib.ptr(lay.subpos), tile_panel_p)
+        _enqueue_spmv(plan, rec, x, y, y_in, a, b,
+                      torch.cuda.current_stream(plan.device).cuda_stream)
     finally:
         if switch:
             torch.cuda.set_device(prev)
-    if st:
-        _lib.check(st, "b2s_spmv")
-    if not plan.status_checked:
-        plan.check_status()
+    plan.note_launch()
 
 
 def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row_offset,
@@ -316,7 +356,7 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     [row_offset, row_offset + n_rows) of the y buffer (peer_rows rows) of every rank
     (`peer_array`: ctypes array of the n_peers device pointers, own buffer included).  On the
     column-panel layout the stores are issued by the combine kernel itself
-    (b2s_spmv_panels_peers); otherwise the block is computed into scratch and copied out by
+    (b2s_panel_combine_peers); otherwise the block is computed into scratch and copied out by
     b2s_peer_scatter.  Returns False, having done nothing, when the block cannot go this way
     (on the scratch route its byte size or offset is not a multiple of 16); the caller then
     falls back to a collective.
@@ -327,49 +367,43 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     store_ctas > 0 caps that kernel's grid (CTAs of 256 threads); together with a high-priority
     store_stream a small grid runs beside the next block's tile kernel."""
     plan = prepared.plan()
+    if plan._spmv_record is None:
+        # the combine that stores to the peers adds panels only: keep the long rows in the stack
+        plan.allow_long_rows = False
     lib = _lib.load()
-    fn, head, tile_row_p, n_tiles, lay, status_p, tile_panel_p = _spmv_launch_record(plan)
+    rec = _spmv_launch_record(plan)
     dtype = plan.data.dtype
     itemsize = plan.data.element_size()
     if row_offset < 0 or row_offset + plan.n_rows > peer_rows:
         raise ValueError("row block does not fit the assembled result")
-    if lay is None and ((plan.n_rows * itemsize) % 16 or (row_offset * itemsize) % 16):
+    # the fused combine + store needs all of y in the panel partials
+    fused = rec[0] == "stack" and rec[1].long_rows is None
+    if not fused and ((plan.n_rows * itemsize) % 16 or (row_offset * itemsize) % 16):
         return False
     a, b = _scalar(alpha, dtype), _scalar(beta, dtype)
     with torch.cuda.device(plan.device):
         stream = torch.cuda.current_stream(plan.device).cuda_stream
-        carry = plan.scratch_on("spmv_carry", n_tiles, stream)
-        if lay is not None and store_stream is not None:
-            ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
-            one, zero = _scalar(1.0, dtype), _scalar(0.0, dtype)
-            st = lib.b2s_spmv_panels(
-                *head, _lib.ptr(x), None, None, one, zero, tile_row_p, _lib.ptr(carry),
-                _lib.ptr(ypart), status_p, stream, lay.n_stacked, _lib.ptr(lay.subpos),
-                tile_panel_p)
-            _lib.check(st, "b2s_spmv_panels")
-            done = torch.cuda.Event()
-            done.record(torch.cuda.current_stream(plan.device))
-            store_stream.wait_event(done)
+        if fused:
+            lay = rec[1]
+            ypart = _launch_stack_partials(plan, lay, x, stream)
+            target = stream
+            if store_stream is not None:
+                done = torch.cuda.Event()
+                done.record(torch.cuda.current_stream(plan.device))
+                store_stream.wait_event(done)
+                target = store_stream.cuda_stream
             st = lib.b2s_panel_combine_peers(
                 plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows, lay.n_panels,
                 _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows, a, b,
-                int(store_ctas), store_stream.cuda_stream)
+                int(store_ctas) if store_stream is not None else 0, target)
             _lib.check(st, "b2s_panel_combine_peers")
-        elif lay is not None:
-            ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
-            st = lib.b2s_spmv_panels_peers(
-                *head, _lib.ptr(x), _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows,
-                a, b, tile_row_p, _lib.ptr(carry), _lib.ptr(ypart), status_p, stream,
-                lay.n_stacked, _lib.ptr(lay.subpos), tile_panel_p)
-            _lib.check(st, "b2s_spmv_panels_peers")
         else:
             tmp = plan.scratch_on("spmv_peer_block", plan.n_rows, stream)
-            st = fn(*head, _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(tmp), a, b, tile_row_p,
-                    _lib.ptr(carry), status_p, stream)
-            _lib.check(st, "b2s_spmv_csr")
+            _enqueue_spmv(plan, rec, x, tmp, y_in, a, b, stream)
             st = lib.b2s_peer_scatter(_lib.ptr(tmp), plan.n_rows * itemsize, peer_array, n_peers,
                                       row_offset * itemsize, peer_rows * itemsize, stream)
             _lib.check(st, "b2s_peer_scatter")
+    plan.note_launch()
     return True
 
 

@@ -132,23 +132,14 @@ int b2s_spmv_csr_fixed(int val_type, int idx_type, int ptr_type,
 /* ---- column-panel layout for SpMV -------------------------------------------------------------
  * No counterpart in the reference.  When x is larger than the L2 cache, gathers of x miss and
  * each miss moves a 64-byte DRAM burst for 8 useful bytes.  b2s_panel_build re-lays the matrix
- * out once as a stack of n_panels CSR matrices over the same rows, panel p holding the entries
- * with col >> panel_shift == p (stable, so the order inside a row is kept), columns stored
- * panel-local as int32.  b2s_spmv_panels multiplies the stack (the x slice of the panels in
- * flight stays L2-resident), leaves one partial per (panel, row) in ypart_dev
- * (n_panels * n_rows values) and adds them in ascending panel order with the alpha / beta
- * epilogue.  p_ptr has n_panels * n_rows + 1 entries of p_ptr_type; panel_start_dev has
- * n_panels + 1 int64 entries.
+ * out once as a stack of n_panels (<= 256) CSR matrices over the same rows, panel p holding the
+ * entries with col >> panel_shift == p (stable, so the order inside a row is kept), columns
+ * stored panel-local as int32.  p_ptr has n_panels * n_rows + 1 entries of p_ptr_type;
+ * panel_start_dev has n_panels + 1 int64 entries.
  * b2s_panel_compact drops the empty rows of the stack (a row with few entries is empty in most
  * panels): called with c_ptr_dev == NULL it fills subpos_dev (n_panels * n_rows int32: position
  * of each stacked row among the non-empty ones, or -1) and *count_dev; called again with
- * c_ptr_dev it writes the count + 1 row pointers of the non-empty rows.  b2s_spmv_panels then
- * takes the compacted pointers as p_ptr_dev, n_stacked = count and subpos_dev (or
- * n_stacked = n_panels * n_rows and subpos_dev = NULL for the uncompacted stack); tile_row /
- * carry / ypart are sized for n_stacked rows (b2s_tile_count(n_stacked, nnz, items)).
- * tile_panel_dev (may be NULL): int32 per tile, the panel of the tile's first non-zero, i.e. the
- * largest p with panel_start[p] <= t * items - tile_row[t]; without it every CTA searches
- * panel_start itself.
+ * c_ptr_dev it writes the count + 1 row pointers of the non-empty rows.
  */
 int64_t b2s_panel_compact_bytes(int64_t n_stacked);
 int b2s_panel_compact(const void* p_ptr_dev, int p_ptr_type, int64_t n_stacked,
@@ -171,46 +162,77 @@ int b2s_panel_build_global(int val_type, int idx_type, int ptr_type,
                            int panel_shift, void* p_data_dev, int32_t* p_cols_dev,
                            void* p_ptr_dev, int p_ptr_type, int64_t* panel_start_dev,
                            void* scratch_dev, int64_t scratch_bytes, b2s_stream stream);
-int b2s_spmv_panels(int val_type, int ptr_type,
-                    const void* p_data_dev, const int32_t* p_cols_dev, const void* p_ptr_dev,
-                    int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels, int panel_shift,
-                    const int64_t* panel_start_dev,
-                    const void* x_dev, const void* y_in_dev, void* y_dev,
-                    const void* alpha, const void* beta,
-                    const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
-                    int32_t* status_dev, b2s_stream stream,
-                    int64_t n_stacked, const int32_t* subpos_dev,
-                    const int32_t* tile_panel_dev);
+
+/* ---- SpMV over the end-flag stack ---------------------------------------------------------------
+ * No counterpart in the reference (its kernels walk row pointers, spmv_csr.py:167-192).  Once the
+ * stack of panels holds non-empty rows only, the row pointers are folded into the column words:
+ *   bit 31  the entry is the LAST of its stacked row,
+ *   bit 30  padding entry (adds nothing; its column bits are 0),
+ *   low bits the panel-local column.
+ * s_data_dev / s_cols_dev hold n_entries such entries, n_entries a multiple of the tile size
+ * b2s_spmv_stack_tile_items(val_type) (pad behind the last real entry), both arrays
+ * 32-byte aligned.  tile_ord_dev[t] (n_entries / tile + 1 int64 entries) is the number of end
+ * flags before entry t * tile, i.e. the ordinal of the stacked row active at the start of tile
+ * t.  The kernels write ypart_dev[r] = (sum of the products of stacked row r) for all
+ * n_stacked rows; carry_dev is scratch of n_entries / tile values.  The per-panel partials are
+ * then added per matrix row by b2s_panel_combine (or b2s_panel_combine_peers).
+ *
+ * b2s_spmv_stack: wide panels (n_panels <= 256 of 2^panel_shift columns, the x slice of a panel
+ * sized for L2); panel_start_dev[p] = first entry of panel p (n_panels + 1 entries),
+ * tile_panel_dev[t] = panel of the first entry of tile t; both may be NULL when n_panels == 1.
+ *
+ * b2s_spmv_stack_shared: narrow panels of 2^panel_shift <= b2s_spmv_stack_shared_cols(val_type)
+ * columns for the long rows of a matrix.  Every panel is padded to whole tiles; CTA u copies
+ * the x slice of panel unit_dev[3u] into shared memory (one bulk copy) and multiplies tiles
+ * unit_dev[3u + 1] .. + unit_dev[3u + 2] - 1 of that panel from there, so the gathers of x never
+ * leave the SM.  status_dev: bit B2S_ERR_TIMEOUT if the bulk copy did not arrive.
+ *
+ * b2s_spmv_stack_rows_combine: the stacked rows here are (panel, long row) pairs; seg_ids_dev
+ * [seg_ptr_dev[j] .. seg_ptr_dev[j + 1]) lists the stacked rows of long row j in ascending panel
+ * order and the call adds alpha times their sum (fixed order) to y_dev[rows_dev[j]]; n_part is
+ * the number of stacked rows (the bounds-checked build verifies seg_ids against it).
+ */
+int b2s_spmv_stack_tile_items(int val_type);
+int b2s_spmv_stack_shared_cols(int val_type);
+int b2s_spmv_stack(int val_type, const void* s_data_dev, const uint32_t* s_cols_dev,
+                   int64_t n_entries, int64_t n_stacked, int64_t n_cols, int n_panels,
+                   int panel_shift, const int64_t* panel_start_dev,
+                   const int32_t* tile_panel_dev, const int64_t* tile_ord_dev,
+                   const void* x_dev, void* ypart_dev, void* carry_dev, int32_t* status_dev,
+                   b2s_stream stream);
+int b2s_spmv_stack_shared(int val_type, const void* s_data_dev, const uint32_t* s_cols_dev,
+                          int64_t n_entries, int64_t n_stacked, int64_t n_cols, int panel_shift,
+                          const int32_t* unit_dev, int64_t n_units,
+                          const int64_t* tile_ord_dev, const void* x_dev, void* ypart_dev,
+                          void* carry_dev, int32_t* status_dev, b2s_stream stream);
+int b2s_spmv_stack_rows_combine(int val_type, const void* part_dev, const int64_t* seg_ptr_dev,
+                                const int32_t* seg_ids_dev, const int64_t* rows_dev,
+                                int64_t n_long, int64_t n_part, void* y_dev, const void* alpha,
+                                int32_t* status_dev, b2s_stream stream);
+/* y = alpha * (sum over panels p of ypart[subpos[p * n_rows + r]], ascending p) + beta * y_in,
+ * for every matrix row r (subpos_dev == NULL: ypart holds n_panels * n_rows values, none
+ * dropped).  y_in_dev may be NULL when *beta == 0 and may equal y_dev. */
+int b2s_panel_combine(int val_type, const void* ypart_dev, const int32_t* subpos_dev,
+                      int64_t n_rows, int n_panels, const void* y_in_dev, void* y_dev,
+                      const void* alpha, const void* beta, b2s_stream stream);
 
 /* ---- all-gather fused into the last kernel (several GPUs, no counterpart in the reference) ----
  * In a row-partitioned product every rank owns rows [row_offset, row_offset + n_rows) of the
  * assembled y and every rank wants all of y.  peer_y is a HOST array of n_peers (<= 16) device
  * pointers: the y buffer (peer_rows rows) of each rank, this rank's own included, as addresses
  * that kernels of the current device may write (symmetric / peer-mapped memory).
- * b2s_spmv_panels_peers is b2s_spmv_panels whose combine kernel stores each value into all of
- * them (plain coalesced stores over NVLink) instead of into a local y; b2s_peer_scatter does the
- * same for an already computed block of bytes (16-byte multiples; peer_bytes = size of each
+ * b2s_panel_combine_peers is b2s_panel_combine storing each value into all of them (plain
+ * coalesced stores over NVLink) instead of into a local y; b2s_peer_scatter does the same for
+ * an already computed block of bytes (16-byte multiples; peer_bytes = size of each
  * destination buffer), e.g. the C block of an SpMM.  Blocks that would not fit the destination
  * are refused.  The caller orders the ranks afterwards (any barrier across the ranks after these
  * kernels have finished); neither call waits for a peer.
  */
-int b2s_spmv_panels_peers(int val_type, int ptr_type,
-                          const void* p_data_dev, const int32_t* p_cols_dev, const void* p_ptr_dev,
-                          int64_t n_rows, int64_t n_cols, int64_t nnz, int n_panels,
-                          int panel_shift, const int64_t* panel_start_dev,
-                          const void* x_dev, const void* y_in_dev,
-                          void* const* peer_y, int n_peers, int64_t row_offset, int64_t peer_rows,
-                          const void* alpha, const void* beta,
-                          const int64_t* tile_row_dev, void* carry_dev, void* ypart_dev,
-                          int32_t* status_dev, b2s_stream stream,
-                          int64_t n_stacked, const int32_t* subpos_dev,
-                          const int32_t* tile_panel_dev);
 int b2s_peer_scatter(const void* src_dev, int64_t bytes, void* const* peer_dst, int n_peers,
                      int64_t dst_offset_bytes, int64_t peer_bytes, b2s_stream stream);
-/* The combine + store step alone: b2s_spmv_panels called with y_dev == NULL stops after the
- * carries and leaves the per-panel partials in ypart_dev; this call adds them, applies alpha /
- * beta and stores into the peers.  Split so that it can run on a second stream while the tile
- * kernel of the next row block is already running.  grid_limit > 0 caps the number of CTAs
+/* The combine + store step: adds the per-panel partials b2s_spmv_stack left in ypart_dev,
+ * applies alpha / beta and stores into the peers.  A call of its own so that it can run on a
+ * second stream while the tile kernel of the next row block is already running.  grid_limit > 0 caps the number of CTAs
  * (256 threads each, grid-stride over the rows): on a high-priority stream a few CTAs per SM
  * drain over NVLink beside the other kernel instead of occupying every free slot with stores
  * that wait for the link; 0 = one thread per row. */
