@@ -13,17 +13,26 @@ rows up to 100,000 entries, y = 1.5 * A x + 0.5 * y.  A step is one such product
                 y copied back, copies inside the timed region
   cpu_baseline  the CPU oracle (oracle/, a restatement of the reference's arithmetic) timed on
                 a bounded row slice of the same matrix, all host cores
+  parity        rel-L2 of one fresh product against torch's own CSR product in float64
+                (cuSPARSE), computed once outside every timed region, and against the CPU
+                oracle on the rows of the cpu_baseline sample; a line whose check fails is
+                printed and the run exits non-zero
   extra         GFLOP/s, gathered bytes (x / B counted once per non-zero) and their rate, the
                 SpMM N = 32 product on the same matrix, the measured divergent-gather ceiling
                 of the GPU and the SpMV's fraction of it
   --impl reference   only that CPU measurement, as its own line
+  --workload cfg2mm  the second half of the target as a line of its own: SpMM N = 32 on the
+                same power-law matrix, with its own roofline / cpu_baseline / e2e / parity
 
 With N > 1 (launched by torchrun, one rank per GPU) every rank owns one row block of the same
 size (weak scaling): x is broadcast from rank 0 (NCCL), each rank multiplies its block, and y is
 assembled on every rank -- by default the last kernel of each rank stores its block straight into
 all ranks' symmetric-memory buffers over NVLink (--gather peer), alternatively by an NCCL
 all-gather (--gather nccl); value counts the bytes all ranks processed over the slowest rank's
-time.
+time.  Every rank checks its own block and the block of the next rank of the assembled y against
+torch's CSR product.  The N > 1 line also carries extra.cfg5: ONE 2^26-row float32 / int64 matrix
+row-partitioned by non-zeros over the ranks (RowPartitionedCsr.from_global), SpMV and SpMM
+N = 16, with broadcast / kernel / gather / step times and the same check (--no-cfg5 skips it).
 """
 
 from __future__ import annotations
@@ -45,9 +54,13 @@ if str(ROOT) not in sys.path:
 
 NOMINAL_HBM_GBS = 8000.0
 
-# DRAM bytes (read + written) of one step from ncu (dram__bytes_read.sum + dram__bytes_write.sum
-# over the kernels of a step; profiles/spmv_cfg2_step_launches_dram.md), keyed by (workload, scale)
-NCU_TRAFFIC_BYTES = {("cfg2", 1): 4.50e9}
+# DRAM bytes (read + written) of one step from an ncu capture of the same command
+# (dram__bytes_read.sum + dram__bytes_write.sum over the kernels of a step), keyed by
+# (workload, scale); to be re-captured whenever the kernels of the step change
+NCU_TRAFFIC_BYTES = {("cfg2", 1): 4.87e9}
+
+REL_L2_TOL = {torch.float32: 1e-5, torch.complex64: 1e-5, torch.float64: 1e-12,
+              torch.complex128: 1e-12}
 
 
 def measured_peaks():
@@ -134,7 +147,9 @@ def make_problem(name, device, scale, seed):
     if name == "cfg2":
         return W.cfg2_powerlaw_spmv(device, scale, seed), "spmv"
     if name == "cfg2mm":
-        return W.cfg2_powerlaw_spmv(device, scale, seed, n_dense=32), "spmm"
+        p = W.cfg2_powerlaw_spmv(device, scale, seed, n_dense=32)
+        p.extra["alpha"], p.extra["beta"] = 1.0, 0.0   # C = A B, as the target states it
+        return p, "spmm"
     if name == "cfg3":
         return W.cfg3_banded_spmm(device, scale, seed), "spmm"
     if name == "cfg4":
@@ -162,6 +177,16 @@ WORKLOAD_TEXT = {
 
 DTYPE_TEXT = {torch.float32: "f32", torch.float64: "f64", torch.complex64: "c64",
               torch.complex128: "c128"}
+
+
+def config_dict(args, world, rows, nnz, nbytes_per_gpu):
+    """The `config` object of a line; both arms build it here so that they print the same."""
+    text = WORKLOAD_TEXT[args.workload]
+    if world > 1:
+        text += f"; one such row block per GPU ({world} blocks, weak scaling)"
+    return {"workload": text, "rows": int(rows), "nnz": int(nnz),
+            "l2": "inputs_exceed_l2" if nbytes_per_gpu > 2 * 126e6 else "l2_resident_inputs",
+            "seed": args.seed, "scale": args.scale}
 
 
 def problem_bytes_flops(p, kind):
@@ -228,6 +253,54 @@ def extra_launches(p, kind):
         return 1 if plan.panels() is not None else 0
     row_bytes = int(p.B.shape[1]) * p.B.element_size()
     return 3 if plan.long_row_split(row_bytes) is not None else 0
+
+
+def torch_product(data, indices, indptr, shape, dense, op="non"):
+    """op(A) @ dense by torch's own sparse CSR multiplication in float64 / complex128: the
+    independent product the parity figure is taken against."""
+    wide = torch.complex128 if data.is_complex() else torch.float64
+    vals = data.to(wide)
+    if op == "conj":
+        vals = vals.conj().resolve_conj()
+    A = torch.sparse_csr_tensor(indptr.long(), indices.long(), vals, size=shape)
+    if op != "non":
+        A = A.to_sparse_coo().t().coalesce()
+    return A @ dense.to(wide)
+
+
+def rel_l2(got, want):
+    diff = got.to(want.dtype) - want
+    denom = float(torch.linalg.vector_norm(want))
+    return float(torch.linalg.vector_norm(diff)) / (denom if denom > 0 else 1.0)
+
+
+def parity_check(p, kind):
+    """One fresh product through the public API against torch's CSR product (whole result)."""
+    from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr
+    op = p.extra.get("op", "non")
+    alpha, beta = p.extra.get("alpha", 1.0), p.extra.get("beta", 0.0)
+    dense = p.x if kind == "spmv" else p.B
+    out = p.extra["y0"].clone() if beta != 0.0 else None
+    fn = flagsparse_spmv_csr if kind == "spmv" else flagsparse_spmm_csr
+    got = fn(p.data, p.indices, p.indptr, dense, p.shape, out=out, op=op, alpha=alpha, beta=beta)
+    n = int(dense.shape[1]) if kind == "spmm" else 1
+    err2 = ref2 = 0.0
+    step = max(1, n // 4) if p.nnz > 500_000_000 else n   # bounded memory for the float64 copy
+    for c0 in range(0, n, step):
+        cols = slice(c0, min(n, c0 + step))
+        want = torch_product(p.data, p.indices, p.indptr, p.shape,
+                             dense if kind == "spmv" else dense[:, cols], op)
+        want = alpha * want
+        if beta != 0.0:
+            want = want + beta * p.extra["y0"].to(want.dtype)
+        part = got if kind == "spmv" else got[:, cols]
+        err2 += float(torch.linalg.vector_norm(part.to(want.dtype) - want)) ** 2
+        ref2 += float(torch.linalg.vector_norm(want)) ** 2
+        del want
+    err = (err2 / ref2) ** 0.5 if ref2 > 0 else err2 ** 0.5
+    tol = REL_L2_TOL[p.data.dtype]
+    return {"rel_l2": err, "tol": tol, "ok": bool(err <= tol),
+            "against": "torch.sparse_csr_tensor @ dense in float64 (cuSPARSE), whole result"}
 
 
 def time_device(step, steps, warmup, sampler=None):
@@ -362,13 +435,32 @@ def host_cores():
     return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
 
 
+def oracle_parity(p, kind, expect):
+    """rel-L2 of our product (alpha = 1, beta = 0) against what the CPU oracle computed for the
+    rows of its sample."""
+    import numpy as np
+
+    from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr
+    op = p.extra.get("op", "non")
+    dense = p.x if kind == "spmv" else p.B
+    fn = flagsparse_spmv_csr if kind == "spmv" else flagsparse_spmm_csr
+    got = fn(p.data, p.indices, p.indptr, dense, p.shape, op=op)
+    got = got[: expect.shape[0]].cpu().numpy()
+    wide = np.complex128 if np.iscomplexobj(expect) else np.float64
+    diff = np.linalg.norm((got.astype(wide) - expect.astype(wide)).ravel())
+    denom = np.linalg.norm(expect.astype(wide).ravel())
+    return float(diff / (denom if denom > 0 else 1.0))
+
+
 def cpu_baseline(p, kind, target_seconds=12.0):
     """The oracle port timed on the sample for about target_seconds (best run), plus scipy's
-    single-threaded CSR product on the same sample."""
+    single-threaded CSR product on the same sample, plus the rel-L2 of our result on the
+    sample's rows against the oracle's."""
     import oracle
     threads = oracle.set_threads(host_cores())
     fn, nbytes, text, scipy_fn = cpu_sample(p, kind)
-    fn()  # warm the caches and the thread pool
+    expect = fn()  # warm the caches and the thread pool; also the checker's answer
+    oracle_err = oracle_parity(p, kind, expect)
     reps, t_total, best = 0, 0.0, float("inf")
     while reps < 3 or (t_total < target_seconds and reps < 200):
         t0 = time.perf_counter()
@@ -386,6 +478,7 @@ def cpu_baseline(p, kind, target_seconds=12.0):
     return {
         "value": nbytes / best / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
         "sample": text + f", best of {reps} runs", "scipy_1core_gbs": scipy_gbs,
+        "oracle_rel_l2_on_sample": oracle_err,
     }
 
 
@@ -401,6 +494,12 @@ def run_reference_arm(args, rank, world):
     # all host threads, also where the launcher exported OMP_NUM_THREADS=1 for its workers
     threads = oracle.set_threads(host_cores())
     p, kind = make_problem(args.workload, dev, args.scale, args.seed)
+    job_rows, job_nnz = p.shape[0], p.nnz
+    full_bytes, _ = problem_bytes_flops(p, kind)
+    for r in range(1, world):  # the other ranks' row blocks: only their sizes are needed here
+        q, _ = make_problem(args.workload, dev, args.scale, args.seed + r)
+        job_rows, job_nnz = job_rows + q.shape[0], job_nnz + q.nnz
+        del q
     fn, nbytes, text, _ = cpu_sample(p, kind)
     for _ in range(max(1, args.warmup)):
         fn()
@@ -419,7 +518,7 @@ def run_reference_arm(args, rank, world):
         "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype],
         "data": "synthetic",
-        "config": {"workload": WORKLOAD_TEXT[args.workload], "rows": p.shape[0], "nnz": p.nnz},
+        "config": config_dict(args, world, job_rows, job_nnz, full_bytes),
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -454,6 +553,93 @@ def gather_ceiling(device, spmv_gathers_per_s):
     rate = n / per
     return {"ggathers_per_s": rate / 1e9, "spmv_ggathers_per_s": spmv_gathers_per_s / 1e9,
             "frac": spmv_gathers_per_s / rate, "x_bytes": n_x * 8, "gathers": n}
+
+
+def check_assembled(part, out_full, own, nxt, dense, alpha, beta, staged_rows):
+    """Every rank compares two row blocks of the assembled result with torch's CSR product: its
+    own and the next rank's.  `own` / `nxt` are (data, indices, indptr, y0 or None, rank) of
+    those blocks; staged_rows = rows per stage when the global row order is block-cyclic
+    (sub-block s of rank r at rows (s * world + r) * h), else 0.  Returns the largest rel-L2."""
+    worst = 0.0
+    for data, indices, indptr, y0, r in (own, nxt):
+        n_local = int(indptr.numel()) - 1
+        want = alpha * torch_product(data, indices, indptr, (n_local, part.n_cols), dense)
+        if beta != 0.0:
+            want = want + beta * y0.to(want.dtype)
+        if staged_rows:
+            h = staged_rows
+            got = torch.cat([out_full[(s * part.world + r) * h:(s * part.world + r + 1) * h]
+                             for s in range(n_local // h)])
+        else:
+            off = sum(part.rows_per_rank[:r])
+            got = out_full[off:off + n_local]
+        worst = max(worst, rel_l2(got, want))
+        del want
+    return worst
+
+
+def cfg5_extra(args, rank, world, device, timed):
+    """ONE 2^26-row float32 / int64 matrix (Zipf(2.0) row lengths), row-partitioned by
+    non-zeros over the ranks: SpMV and SpMM N = 16 with x / B broadcast from rank 0 and y / C
+    assembled on every rank.  Every rank draws the same matrix (same seed), keeps its block,
+    and checks its own and the next rank's block of the result against torch's CSR product."""
+    import torch.distributed as dist
+
+    from flagsparse_b200 import workloads as W
+    from flagsparse_b200.distributed import (RowPartitionedCsr, partition_rows_by_nnz,
+                                             slice_rows)
+    out = {}
+    g = W.cfg5_scaling(device, args.cfg5_scale, args.seed)
+    bounds = partition_rows_by_nnz(g.indptr, world)
+    part = RowPartitionedCsr.from_global(g.data, g.indices, g.indptr, g.shape)
+    nxt_rank = (rank + 1) % world
+    own = (part.data, part.indices, part.indptr, None, rank)
+    nd, ni, nptr = slice_rows(g.data, g.indices, g.indptr, bounds[nxt_rank], bounds[nxt_rank + 1])
+    nxt = (nd, ni, nptr, None, nxt_rank)
+    n_rows, n_cols, nnz = g.shape[0], g.shape[1], g.nnz
+    vb, ib = g.data.element_size(), g.indices.element_size()
+    out["rows"], out["nnz"] = n_rows, nnz
+    out["rows_per_rank"] = part.rows_per_rank
+    for kind, dense in (("spmv", g.x), ("spmm", g.B)):
+        n = 1 if kind == "spmv" else int(dense.shape[1])
+        trailing = () if kind == "spmv" else (n,)
+        op = part.spmv if kind == "spmv" else part.spmm
+        local = part.spmv_local if kind == "spmv" else part.spmm_local
+        out_local = torch.empty((part.n_local, *trailing), dtype=g.data.dtype, device=device)
+        out_full = torch.empty((n_rows, *trailing), dtype=g.data.dtype, device=device)
+
+        def step():
+            return op(dense, src=0, out_local=out_local, out=out_full)
+
+        full = step()
+        torch.cuda.synchronize()
+        err = check_assembled(part, full, own, nxt, dense, 1.0, 0.0, 0)
+        errs = torch.tensor([err], dtype=torch.float64, device=device)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        steps = max(3, min(args.steps, 10))
+        per_step = timed(step, steps, 2) / steps
+        phases = {
+            "broadcast_ms": timed(lambda: part.broadcast_dense(dense, 0), 3, 1) / 3 * 1e3,
+            "kernel_ms": timed(lambda: local(dense, out=out_local), 3, 1) / 3 * 1e3,
+            "allgather_ms": timed(lambda: part.gather_rows(out_local, out=out_full), 3, 1)
+            / 3 * 1e3,
+        }
+        if kind == "spmv":
+            nbytes = W.spmv_bytes(n_rows, n_cols, nnz, vb, ib, ib, False)
+        else:
+            nbytes = W.spmm_bytes(n_rows, n_cols, nnz, n, vb, ib, ib, False)
+        # per-GPU algorithmic bytes: the rank's share of the matrix and of y / C, all of x / B
+        per_gpu = (nbytes - n_cols * n * vb) / world + n_cols * n * vb
+        out[kind] = {
+            "ms_per_step": per_step * 1e3, "job_gbs": nbytes / per_step / 1e9,
+            "per_gpu_kernel_gbs": per_gpu / (phases["kernel_ms"] / 1e3) / 1e9,
+            "algorithmic_bytes": nbytes, "phases": phases,
+            "rel_l2_vs_torch_own_and_next_block": float(errs.item()),
+            "parity_ok": bool(float(errs.item()) <= REL_L2_TOL[g.data.dtype]),
+        }
+        del out_local, out_full, full
+        torch.cuda.empty_cache()
+    return out
 
 
 def run_multi_gpu(args, rank, world, local_rank, device):
@@ -540,6 +726,33 @@ def run_multi_gpu(args, rank, world, local_rank, device):
         return float(t.item())
 
     step()  # plans, NCCL communicators
+    torch.cuda.synchronize()
+    # result check, outside every timed region: own block and the next rank's block
+    q, _ = make_problem(args.workload, device, args.scale, args.seed + (rank + 1) % world)
+    y0_of = (lambda pr: pr.extra["y0"]) if beta != 0.0 else (lambda pr: None)
+    if beta != 0.0:
+        out_local.copy_(p.extra["y0"])
+    checked = op(dense, src=0, out_local=out_local, out=out_full, alpha=alpha, beta=beta) \
+        if (staged or gather_mode == "peer") else None
+    if checked is None:
+        bcast()
+        kernel()
+        gather()
+        checked = out_full
+    torch.cuda.synchronize()
+    worst = check_assembled(
+        part, checked, (p.data, p.indices, p.indptr, y0_of(p), rank),
+        (q.data, q.indices, q.indptr, y0_of(q), (rank + 1) % world), dense, alpha, beta,
+        part._stage_rows if staged else 0)
+    del q
+    torch.cuda.empty_cache()
+    errs = torch.tensor([worst], dtype=torch.float64, device=device)
+    dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+    tol = REL_L2_TOL[p.data.dtype]
+    parity = {"rel_l2": float(errs.item()), "tol": tol, "ok": bool(float(errs.item()) <= tol),
+              "against": "torch.sparse_csr_tensor @ dense in float64 (cuSPARSE): every rank "
+                         "checks its own block and the next rank's block of the assembled "
+                         "result"}
     sampler = ClockSampler(local_rank) if rank == 0 else None
     seconds = timed(step, args.steps, args.warmup, sampler)
     per_step = seconds / args.steps
@@ -594,15 +807,16 @@ def run_multi_gpu(args, rank, world, local_rank, device):
             "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype],
             "data": "synthetic",
-            "config": {"workload": WORKLOAD_TEXT[args.workload] + f"; one such row block per GPU "
-                       f"({world} blocks, global matrix {part.n_rows} x {p.shape[1]})",
-                       "rows": part.n_rows, "nnz": int(job_nnz),
-                       "l2": "inputs_exceed_l2" if nbytes > 2 * 126e6 else "l2_resident_inputs",
-                       "seed": args.seed, "scale": args.scale,
-                       "exchange": "NCCL broadcast of x/B from rank 0 + NCCL all-gather of y/C, "
-                                   "both inside the timed step",
-                       "stages": args.stages if staged else 1, "gather": gather_mode,
-                       "store_ctas": part.peer_store_ctas},
+            "config": config_dict(args, world, part.n_rows, int(job_nnz), nbytes),
+            "parity": parity,
+            "exchange": {
+                "broadcast": "NCCL broadcast of x / B from rank 0",
+                "gather": ("stores of each rank's last kernel into every rank's "
+                           "symmetric-memory result buffer over NVLink, then a one-element "
+                           "NCCL all-reduce as the end-of-step fence"
+                           if gather_mode == "peer" else "NCCL all-gather of y / C"),
+                "inside_timed_step": True, "stages": args.stages if staged else 1,
+                "mode": gather_mode, "store_ctas": part.peer_store_ctas},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
                          "peak_kind": peak_kind,
@@ -616,9 +830,23 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                       "phases": phases, "kernel_phase_gbs_all_gpus": kernel_gbs,
                       "algorithmic_bytes_per_step": job_bytes},
         }
+    # the scaling configuration as stated: one 2^26-row matrix partitioned by non-zeros
+    cfg5 = None
+    if not args.no_cfg5:
+        del part, out_local, out_full, p, dense
+        torch.cuda.empty_cache()
+        cfg5 = cfg5_extra(args, rank, world, device, timed)
+    if cfg5 is not None:  # the same figures on every rank (all-reduced)
+        parity["ok"] = bool(parity["ok"] and cfg5["spmv"]["parity_ok"]
+                            and cfg5["spmm"]["parity_ok"])
+    if rank == 0:
+        if cfg5 is not None:
+            line["extra"]["cfg5"] = cfg5
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
 
 
 def main():
@@ -642,6 +870,10 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
                     help="N > 1: how y / C is assembled -- NCCL all-gather, or stores of the last "
                          "kernel into every rank's symmetric-memory buffer")
+    ap.add_argument("--no-cfg5", action="store_true",
+                    help="N > 1: skip the partitioned 2^26-row matrix in extra.cfg5")
+    ap.add_argument("--cfg5-scale", type=int, default=1,
+                    help="divide the rows of the extra.cfg5 matrix (debugging)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the SpMM N=32 side measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
@@ -679,6 +911,9 @@ def main():
     per_step = seconds / args.steps
     gbs = nbytes / per_step / 1e9
 
+    parity = parity_check(p, kind)  # once, outside every timed region
+    torch.cuda.empty_cache()
+
     if args.no_e2e:
         e2e_s, h2d, d2h = float("nan"), 0, 0
     else:
@@ -702,13 +937,19 @@ def main():
         mm_step()
         torch.cuda.synchronize()
         mm_s = time_device(mm_step, max(3, args.steps // 5), 3) / max(3, args.steps // 5)
+        mm_want = torch_product(p.data, p.indices, p.indptr, p.shape, p.extra["B"])
+        mm_err = rel_l2(mm_out, mm_want)
+        del mm_want
         extra["spmm_n32_same_matrix"] = {
+            "rel_l2_vs_torch": mm_err, "parity_ok": bool(mm_err <= REL_L2_TOL[p.data.dtype]),
             "ms_per_step": mm_s * 1e3, "gbs": mm_bytes / mm_s / 1e9,
             "gflops": mm_flops / mm_s / 1e9, "frac_of_measured_peak": mm_bytes / mm_s / 1e9 / peak,
             "algorithmic_bytes_per_step": mm_bytes,
             "gathered_bytes_per_step": gathered_bytes(p, "spmm", mm_bytes),
             "gathered_gbs": gathered_bytes(p, "spmm", mm_bytes) / mm_s / 1e9,
         }
+        if not extra["spmm_n32_same_matrix"]["parity_ok"]:
+            parity["ok"] = False
         p.extra["alpha"], p.extra["beta"] = saved
         del p.extra["B"], mm_out
         torch.cuda.empty_cache()
@@ -747,23 +988,29 @@ def main():
         "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": DTYPE_TEXT[p.data.dtype], "data": "synthetic",
-        "config": {"workload": WORKLOAD_TEXT[args.workload], "rows": p.shape[0], "nnz": p.nnz,
-                   "l2": "inputs_exceed_l2" if nbytes > 2 * 126e6 else "l2_resident_inputs",
-                   "seed": args.seed, "scale": args.scale},
+        "config": config_dict(args, 1, p.shape[0], p.nnz, nbytes),
+        "parity": parity,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
                      "frac": gbs / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.scale)),
                      "peak_kind": peak_kind},
         "e2e": {"value": nbytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3,
-                "steps_in_flight": max(1, args.e2e_depth)},
+                "steps_in_flight": max(1, args.e2e_depth),
+                "note": "throughput with A resident and steps_in_flight steps overlapping their "
+                        "copies; not the latency of one call from host buffers"},
         "gpu_launches": (launches_per_step + extra_launches(p, kind)) * args.steps,
         "clocks": sampler.summary(),
         "extra": extra,
     }
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(p, kind)
+        sample_err = line["cpu_baseline"]["oracle_rel_l2_on_sample"]
+        parity["oracle_rel_l2_on_sample"] = sample_err
+        parity["ok"] = bool(parity["ok"] and sample_err <= parity["tol"])
     print(json.dumps(line), flush=True)
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
 
 
 if __name__ == "__main__":
