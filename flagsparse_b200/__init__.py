@@ -19,6 +19,7 @@ from ._plan import (
     set_long_row_policy,
     set_long_spmv_policy,
     set_panel_policy,
+    set_plan_cache_bytes,
     set_plan_cache_capacity,
     set_window_policy,
 )
@@ -73,6 +74,7 @@ __all__ = [
     "install",
     "clear_plan_cache",
     "set_plan_cache_capacity",
+    "set_plan_cache_bytes",
     "set_panel_policy",
     "set_long_row_policy",
     "set_long_spmv_policy",

@@ -28,7 +28,8 @@ def widened_values(data):
     """float32 copy of a float16 / bfloat16 value array, made once per tensor (and per in-place
     modification of it).  The entry keeps the caller's tensor alive, so its address cannot be
     reused by another tensor while the entry exists."""
-    key = (data.data_ptr(), data.numel(), data.dtype, data._version, str(data.device),
+    from ._plan import tensor_version
+    key = (data.data_ptr(), data.numel(), data.dtype, tensor_version(data), str(data.device),
            tuple(data.stride()))
     hit = _WIDE.get(key)
     if hit is not None:

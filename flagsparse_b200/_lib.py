@@ -65,9 +65,8 @@ SIGNATURES = {
     "b2s_spmv_stack_shared": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                       c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p]),
-    "b2s_spmv_stack_rows_combine": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                            c_int64, c_int64, c_void_p, c_void_p, c_void_p,
-                                            c_void_p]),
+    "b2s_spmv_stack_rows_combine": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                            c_int64, c_void_p, c_void_p, c_void_p]),
     "b2s_panel_combine": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p]),
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,

@@ -56,13 +56,19 @@ LONG_SPMV_POLICY = "auto"
 LONG_SPMV_MIN_PER_PANEL = 4
 LONG_SPMV_MIN_SHARE = 0.1
 LONG_SPMV_TILES_PER_UNIT = 128
+LONG_SPMV_SLICE_COLS = None   # None: the widest slice the kernel holds (64 KB of x)
 
 
-def set_long_spmv_policy(policy="auto", min_per_panel=None, min_share=None, tiles_per_unit=None):
+def set_long_spmv_policy(policy="auto", min_per_panel=None, min_share=None, tiles_per_unit=None,
+                         slice_cols=None):
     """'auto' (default) or 'off': whether SpMV may multiply the long rows of a panel-layout
-    matrix from shared-memory slices of x.  The other arguments override the thresholds."""
+    matrix from shared-memory slices of x.  The other arguments override the thresholds
+    (slice_cols: a narrower slice than the kernel could hold, a power of two; tests use it to
+    get many narrow panels on small matrices)."""
     global LONG_SPMV_POLICY, LONG_SPMV_MIN_PER_PANEL, LONG_SPMV_MIN_SHARE
-    global LONG_SPMV_TILES_PER_UNIT
+    global LONG_SPMV_TILES_PER_UNIT, LONG_SPMV_SLICE_COLS
+    if slice_cols is not None:
+        LONG_SPMV_SLICE_COLS = int(slice_cols) if slice_cols else None
     if policy not in ("auto", "off"):
         raise ValueError("long-row policy must be 'auto' or 'off'")
     LONG_SPMV_POLICY = policy
@@ -375,7 +381,6 @@ class CsrPlan:
         self._scratch = {}                   # (tag, width, stream) -> tensor
         self._transposed = {}                # conj flag -> CsrPlan of the transpose
         self._panels = False                 # False: not decided yet; None: not used
-        self.allow_long_rows = True          # SpMV may take the long rows out (see panels())
         self._long_rows = {}                 # panel shift -> LongRowSplit or None (SpMM)
         self._window = {}                    # tile_items -> widest column span of a tile (SpMM)
         self._spmv_record = None             # prebuilt launch arguments (spmv.py)
@@ -451,16 +456,23 @@ class CsrPlan:
         lay = build_stack_layout(data, indices, indptr, self.n_rows, self.n_cols, n_panels, shift)
         if lay is None:
             return None
+        if long_stack is not None:
+            # the sum of long row j sits behind the stacked rows of the wide panels; the combine
+            # finds it through the position table like the partial of panel 0
+            lay.subpos[long_stack.rows] = (lay.n_stacked + torch.arange(
+                long_stack.n_long, dtype=torch.int64, device=self.device)).to(torch.int32)
         lay.long_rows = long_stack
         self._panels = lay
         return lay
 
     def _long_rows_for_spmv(self):
         """LongRowStack of the rows long enough for the shared-memory kernel, or None."""
-        if LONG_SPMV_POLICY != "auto" or not self.allow_long_rows:
+        if LONG_SPMV_POLICY != "auto":
             return None
         lib = _lib.load()
         width = int(lib.b2s_spmv_stack_shared_cols(self.vcode))
+        if LONG_SPMV_SLICE_COLS:
+            width = max(2, min(width, LONG_SPMV_SLICE_COLS))
         shift = width.bit_length() - 1
         n_panels = ((self.n_cols - 1) >> shift) + 1
         min_len = max(int(LONG_SPMV_MIN_PER_PANEL * n_panels), 2)
@@ -583,6 +595,42 @@ class CsrPlan:
         self._transposed[conj] = plan
         return plan
 
+    def derived_bytes(self):
+        """Device bytes this plan keeps alive beyond the caller's three arrays: tile plans,
+        scratch, the column-panel stack, the long-row layouts, cached transposes."""
+        seen, total = set(), 0
+
+        def add(obj):
+            nonlocal total
+            if torch.is_tensor(obj):
+                key = obj.untyped_storage().data_ptr() if obj.numel() else 0
+                if key and key not in seen:
+                    seen.add(key)
+                    total += obj.untyped_storage().nbytes()
+            elif isinstance(obj, CsrPlan):
+                if id(obj) not in seen:
+                    seen.add(id(obj))
+                    for t in (obj.data, obj.indices, obj.indptr):
+                        add(t)
+                    total += obj.derived_bytes()
+            elif isinstance(obj, (list, tuple)):
+                for o in obj:
+                    add(o)
+            elif isinstance(obj, dict):
+                for o in obj.values():
+                    add(o)
+            elif hasattr(obj, "__dict__") and not callable(obj):
+                add(vars(obj))
+
+        for t in (self.data, self.indices, self.indptr):   # the caller's: not counted
+            if torch.is_tensor(t) and t.numel():
+                seen.add(t.untyped_storage().data_ptr())
+        for name in ("_tiles", "_scratch", "_transposed", "_long_rows", "_window"):
+            add(getattr(self, name))
+        if self._panels not in (False, None):
+            add(self._panels)
+        return total
+
     STATUS_EVERY = 64   # launches between two non-blocking reads of the status word
 
     def note_launch(self):
@@ -630,18 +678,57 @@ class CsrPlan:
 # -------------------------------------------------------------------------------------------------
 _CACHE = OrderedDict()
 _CACHE_CAPACITY = 16
+_CACHE_MAX_BYTES = None   # None: a quarter of the device's memory, decided at the first put
 
 
 def set_plan_cache_capacity(n):
     """Number of matrices whose plans are kept (least recently used is dropped first)."""
     global _CACHE_CAPACITY
     _CACHE_CAPACITY = max(0, int(n))
-    while len(_CACHE) > _CACHE_CAPACITY:
-        _CACHE.popitem(last=False)
+    _trim_cache()
+
+
+def set_plan_cache_bytes(n):
+    """Upper bound, in bytes of device memory, on what the cached plans keep alive beyond the
+    caller's own tensors: re-laid-out copies of the matrix, transposes, scratch (None = a
+    quarter of the device's memory).  Least recently used plans are dropped first."""
+    global _CACHE_MAX_BYTES
+    _CACHE_MAX_BYTES = None if n is None else max(0, int(n))
+    _trim_cache()
 
 
 def clear_plan_cache():
     _CACHE.clear()
+
+
+def tensor_version(t):
+    """torch's in-place modification counter of a tensor; tensors made under
+    torch.inference_mode() have none (and cannot be modified in place outside it): 0."""
+    try:
+        return t._version
+    except RuntimeError:
+        return 0
+
+
+def _trim_cache():
+    while len(_CACHE) > _CACHE_CAPACITY:
+        _CACHE.popitem(last=False)
+    if not _CACHE:
+        return
+    limit = _CACHE_MAX_BYTES
+    if limit is None:
+        any_plan = next(iter(_CACHE.values()))
+        try:
+            limit = torch.cuda.get_device_properties(any_plan.device).total_memory // 4
+        except Exception:  # noqa: BLE001 - no device information: count-bound only
+            return
+    sizes = [(k, v.derived_bytes()) for k, v in _CACHE.items()]
+    total = sum(b for _, b in sizes)
+    for key, nbytes in sizes[:-1]:          # oldest first; the newest plan always stays
+        if total <= limit:
+            break
+        _CACHE.pop(key, None)
+        total -= nbytes
 
 
 def plan_key(kind, data, indices, indptr, shape):
@@ -650,7 +737,7 @@ def plan_key(kind, data, indices, indptr, shape):
         data.data_ptr(), indices.data_ptr(), indptr.data_ptr(),
         data.numel(), indptr.numel(),
         data.dtype, indices.dtype, indptr.dtype,
-        data._version, indices._version, indptr._version,
+        tensor_version(data), tensor_version(indices), tensor_version(indptr),
         data.stride(0) if data.ndim == 1 and data.numel() > 1 else 1,
         indices.stride(0) if indices.ndim == 1 and indices.numel() > 1 else 1,
         indptr.stride(0) if indptr.ndim == 1 and indptr.numel() > 1 else 1,
@@ -671,5 +758,4 @@ def cache_put(key, plan):
         return
     _CACHE[key] = plan
     _CACHE.move_to_end(key)
-    while len(_CACHE) > _CACHE_CAPACITY:
-        _CACHE.popitem(last=False)
+    _trim_cache()

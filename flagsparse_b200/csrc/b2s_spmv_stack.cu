@@ -376,14 +376,13 @@ __global__ void stack_fixup_kernel(V* ypart, const V* __restrict__ carry,
   ypart[r] = ypart[r] + s;
 }
 
-// y[rows[j]] += alpha * (sum of the partials of long row j, in ascending panel order).  One
-// warp per long row: lane l adds partials l, l + 32, ... in order, then a fixed butterfly.
+// out[j] = sum of the partials of long row j, in ascending panel order.  One warp per long row:
+// lane l adds partials l, l + 32, ... in order, then a fixed butterfly.
 template <class V>
 __global__ void stack_rows_combine_kernel(const V* __restrict__ part,
                                           const int64_t* __restrict__ seg_ptr,
-                                          const int32_t* __restrict__ seg_ids,
-                                          const int64_t* __restrict__ rows, int64_t n_long,
-                                          int64_t n_part, int32_t* status, V* y, V alpha) {
+                                          const int32_t* __restrict__ seg_ids, int64_t n_long,
+                                          int64_t n_part, int32_t* status, V* __restrict__ out) {
   const int64_t j = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (j >= n_long) return;
@@ -398,7 +397,7 @@ __global__ void stack_rows_combine_kernel(const V* __restrict__ part,
     s = s + part[seg_ids[k]];
   }
   s = group_sum(s, 32);
-  if (lane == 0) y[rows[j]] = y[rows[j]] + alpha * s;
+  if (lane == 0) out[j] = s;
 }
 
 }  // namespace b2s
@@ -502,16 +501,15 @@ extern "C" int b2s_spmv_stack_shared(int val_type, const void* s_data_dev,
 
 extern "C" int b2s_spmv_stack_rows_combine(int val_type, const void* part_dev,
                                            const int64_t* seg_ptr_dev, const int32_t* seg_ids_dev,
-                                           const int64_t* rows_dev, int64_t n_long,
-                                           int64_t n_part, void* y_dev, const void* alpha,
+                                           int64_t n_long, int64_t n_part, void* out_dev,
                                            int32_t* status_dev, b2s_stream stream) {
-  if (n_long < 0 || !alpha) return B2S_ERR_ARG;
+  if (n_long < 0 || n_part < 0) return B2S_ERR_ARG;
   if (n_long == 0) return B2S_OK;
-  if (!part_dev || !seg_ptr_dev || !seg_ids_dev || !rows_dev || !y_dev) return B2S_ERR_ARG;
+  if (!part_dev || !seg_ptr_dev || !seg_ids_dev || !out_dev) return B2S_ERR_ARG;
   const size_t vs = b2s::vsize(val_type);
   if (vs == 0) return B2S_ERR_DTYPE;
   const uintptr_t m = vs - 1;
-  if ((reinterpret_cast<uintptr_t>(part_dev) & m) || (reinterpret_cast<uintptr_t>(y_dev) & m))
+  if ((reinterpret_cast<uintptr_t>(part_dev) & m) || (reinterpret_cast<uintptr_t>(out_dev) & m))
     return B2S_ERR_ALIGNMENT;
   const int threads = 256;
   const int64_t grid = (n_long * 32 + threads - 1) / threads;
@@ -519,8 +517,8 @@ extern "C" int b2s_spmv_stack_rows_combine(int val_type, const void* part_dev,
   B2S_DISPATCH_V(val_type, {
     (b2s::stack_rows_combine_kernel<V><<<static_cast<unsigned>(grid), threads, 0,
                                          static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const V*>(part_dev), seg_ptr_dev, seg_ids_dev, rows_dev, n_long, n_part,
-        status_dev, static_cast<V*>(y_dev), *static_cast<const V*>(alpha)));
+        static_cast<const V*>(part_dev), seg_ptr_dev, seg_ids_dev, n_long, n_part, status_dev,
+        static_cast<V*>(out_dev)));
     return b2s::launch_status();
   });
   return B2S_ERR_DTYPE;

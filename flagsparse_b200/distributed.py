@@ -133,13 +133,24 @@ class RowPartitionedCsr:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         dev = self.data.device
-        full = symm.empty((self.n_rows, *trailing), dtype=dtype, device=dev)
         group = self.group if self.group is not None else dist.group.WORLD
-        hdl = symm.rendezvous(full, group)
-        offset = int(getattr(hdl, "offset", 0) or 0)
-        ptrs = [int(p) + offset for p in hdl.buffer_ptrs]
-        if len(ptrs) != self.world or ptrs[self.rank] != full.data_ptr():
-            raise RuntimeError("symmetric memory handle does not describe the buffer just made")
+        # every rank issues the same collectives whether or not its own set-up succeeds; the
+        # ranks then agree on the outcome, so that none is left waiting in a barrier
+        failure, full, hdl, ptrs = None, None, None, []
+        try:
+            full = symm.empty((self.n_rows, *trailing), dtype=dtype, device=dev)
+            hdl = symm.rendezvous(full, group)
+            offset = int(getattr(hdl, "offset", 0) or 0)
+            ptrs = [int(p) + offset for p in hdl.buffer_ptrs]
+            if len(ptrs) != self.world or ptrs[self.rank] != full.data_ptr():
+                raise RuntimeError("symmetric memory handle does not describe the buffer "
+                                   "just made")
+        except Exception as exc:  # noqa: BLE001 - reported after the ranks have agreed
+            failure = exc
+        ok = torch.tensor([0 if failure is not None else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            raise RuntimeError(f"peer gather could not be set up on every rank: {failure}")
         row_items = 1
         for t in trailing:
             row_items *= int(t)
@@ -152,6 +163,15 @@ class RowPartitionedCsr:
         }
         dist.barrier(group=self.group)
         return full
+
+    @staticmethod
+    def _into(out, full):
+        """The assembled result in the caller's `out` when one was given and is not already the
+        buffer the kernels stored into."""
+        if out is None or out.data_ptr() == full.data_ptr():
+            return full
+        out.copy_(full)
+        return out
 
     def fence(self):
         """Stream-ordered barrier across the ranks (a one-element all-reduce): when it has
@@ -243,14 +263,16 @@ class RowPartitionedCsr:
 
     def spmv(self, x, src=0, out_local=None, out=None, alpha=1.0, beta=0.0):
         """y = alpha * A x + beta * y0 with x taken from rank `src`; y0 is this rank's block in
-        out_local.  Returns the assembled y on every rank."""
+        out_local.  Returns the assembled y on every rank.  After enable_peer_gather the result
+        is the symmetric-memory buffer that call returned (the next product overwrites it); an
+        `out` that is another tensor receives a copy."""
         self.broadcast_dense(x, src)
         peer = self._peer
         if peer is not None and peer["trailing"] == () and peer["dtype"] == x.dtype \
                 and self.local_spmv is _default_local_spmv:
             done = self._peer_spmv(x, out_local, alpha, beta)
             if done is not None:
-                return done
+                return self._into(out, done)
         if getattr(self, "_stages", None):
             return self._pipelined(self.local_spmv, x, out_local, out, alpha, beta)
         y_local = self.spmv_local(x, out=out_local, alpha=alpha, beta=beta)
@@ -273,7 +295,7 @@ class RowPartitionedCsr:
                         self.n_rows * row_bytes, _lib.stream_handle(C_local.device))
                 _lib.check(st, "b2s_peer_scatter")
                 self.fence()
-                return peer["full"]
+                return self._into(out, peer["full"])
             return self.gather_rows(C_local, out=out)
         if getattr(self, "_stages", None):
             return self._pipelined(self.local_spmm, B, out_local, out, alpha, beta)

@@ -15,6 +15,7 @@ Differences that do not change results beyond rounding:
 
 from __future__ import annotations
 
+import ctypes
 import time
 
 import torch
@@ -44,6 +45,7 @@ from ._plan import (
     cache_put,
     inspect_csr,
     plan_key,
+    tensor_version,
 )
 
 SUPPORTED_SPMV_VALUE_DTYPES = SUPPORTED_VALUE_DTYPES
@@ -154,6 +156,7 @@ class PreparedCsrSpmv:
         self.index_fallback_applied = bool(index_fallback_applied)
         self.index_fallback_reason = index_fallback_reason
         self._plan = _plan
+        self._data_version = tensor_version(data)
 
     @property
     def row_lengths(self):
@@ -163,7 +166,14 @@ class PreparedCsrSpmv:
 
     def plan(self):
         """The CsrPlan of the arrays the kernel reads (built on first use when this object was
-        constructed by hand rather than by prepare_spmv_csr)."""
+        constructed by hand rather than by prepare_spmv_csr).  Like the reference's handle,
+        which keeps the caller's ``data`` tensor itself (spmv_csr.py:55-79), a handle follows
+        in-place changes of the values: the plan, including any re-laid-out copy of the matrix,
+        is rebuilt when torch's modification counter of ``data`` has moved."""
+        version = tensor_version(self.data)
+        if self._plan is not None and version != self._data_version:
+            self._plan = None
+        self._data_version = version
         if self._plan is None:
             self._plan = _checked_spmv_plan(self.data, self.kernel_indices, self.kernel_indptr,
                                             self.shape, self.index_fallback_policy)
@@ -276,9 +286,13 @@ def _spmv_launch_record(plan: CsrPlan):
 
 
 def _launch_stack_partials(plan, lay, x, stream):
-    """Enqueue the wide-panel stack kernel; returns the per-(panel, row) partials."""
+    """Enqueue the kernels that fill the partials the combine adds: the wide-panel stack kernel
+    (one value per (panel, row) with entries) and, when the long rows were taken out, the
+    shared-memory kernel over their narrow panels, whose per-row sums go behind the others."""
     lib = _lib.load()
-    ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked, stream)
+    lr = lay.long_rows
+    n_extra = 0 if lr is None else lr.n_long
+    ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked + n_extra, stream)
     carry = plan.scratch_on("spmv_stack_carry", lay.n_tiles, stream)
     st = lib.b2s_spmv_stack(
         plan.vcode, _lib.ptr(lay.vals), _lib.ptr(lay.cols), lay.n_entries, lay.n_stacked,
@@ -287,26 +301,22 @@ def _launch_stack_partials(plan, lay, x, stream):
         _lib.ptr(carry), _lib.ptr(plan.status), stream)
     if st:
         _lib.check(st, "b2s_spmv_stack")
+    if lr is not None:
+        part = plan.scratch_on("spmv_long_part", lr.n_stacked, stream)
+        carry_l = plan.scratch_on("spmv_long_carry", lr.n_tiles, stream)
+        st = lib.b2s_spmv_stack_shared(
+            plan.vcode, _lib.ptr(lr.vals), _lib.ptr(lr.cols), lr.n_entries, lr.n_stacked,
+            plan.n_cols, lr.shift, _lib.ptr(lr.units), lr.n_units, _lib.ptr(lr.tile_ord),
+            _lib.ptr(x), _lib.ptr(part), _lib.ptr(carry_l), _lib.ptr(plan.status), stream)
+        if st:
+            _lib.check(st, "b2s_spmv_stack_shared")
+        st = lib.b2s_spmv_stack_rows_combine(
+            plan.vcode, _lib.ptr(part), _lib.ptr(lr.seg_ptr), _lib.ptr(lr.seg_ids), lr.n_long,
+            lr.n_stacked, ctypes.c_void_p(ypart.data_ptr() + lay.n_stacked * ypart.element_size()),
+            _lib.ptr(plan.status), stream)
+        if st:
+            _lib.check(st, "b2s_spmv_stack_rows_combine")
     return ypart
-
-
-def _launch_long_rows(plan, lay, x, y, a, stream):
-    """y[long rows] += alpha * (their products), from shared-memory slices of x."""
-    lib = _lib.load()
-    lr = lay.long_rows
-    part = plan.scratch_on("spmv_long_part", lr.n_stacked, stream)
-    carry = plan.scratch_on("spmv_long_carry", lr.n_tiles, stream)
-    st = lib.b2s_spmv_stack_shared(
-        plan.vcode, _lib.ptr(lr.vals), _lib.ptr(lr.cols), lr.n_entries, lr.n_stacked,
-        plan.n_cols, lr.shift, _lib.ptr(lr.units), lr.n_units, _lib.ptr(lr.tile_ord),
-        _lib.ptr(x), _lib.ptr(part), _lib.ptr(carry), _lib.ptr(plan.status), stream)
-    if st:
-        _lib.check(st, "b2s_spmv_stack_shared")
-    st = lib.b2s_spmv_stack_rows_combine(
-        plan.vcode, _lib.ptr(part), _lib.ptr(lr.seg_ptr), _lib.ptr(lr.seg_ids),
-        _lib.ptr(lr.rows), lr.n_long, lr.n_stacked, _lib.ptr(y), a, _lib.ptr(plan.status), stream)
-    if st:
-        _lib.check(st, "b2s_spmv_stack_rows_combine")
 
 
 def _enqueue_spmv(plan, rec, x, y, y_in, a, b, stream):
@@ -326,8 +336,6 @@ def _enqueue_spmv(plan, rec, x, y, y_in, a, b, stream):
                                lay.n_panels, _lib.ptr(y_in), _lib.ptr(y), a, b, stream)
     if st:
         _lib.check(st, "b2s_panel_combine")
-    if lay.long_rows is not None:
-        _launch_long_rows(plan, lay, x, y, a, stream)
 
 
 def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
@@ -367,17 +375,13 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     store_ctas > 0 caps that kernel's grid (CTAs of 256 threads); together with a high-priority
     store_stream a small grid runs beside the next block's tile kernel."""
     plan = prepared.plan()
-    if plan._spmv_record is None:
-        # the combine that stores to the peers adds panels only: keep the long rows in the stack
-        plan.allow_long_rows = False
     lib = _lib.load()
     rec = _spmv_launch_record(plan)
     dtype = plan.data.dtype
     itemsize = plan.data.element_size()
     if row_offset < 0 or row_offset + plan.n_rows > peer_rows:
         raise ValueError("row block does not fit the assembled result")
-    # the fused combine + store needs all of y in the panel partials
-    fused = rec[0] == "stack" and rec[1].long_rows is None
+    fused = rec[0] == "stack"   # the combine kernel itself stores to the peers
     if not fused and ((plan.n_rows * itemsize) % 16 or (row_offset * itemsize) % 16):
         return False
     a, b = _scalar(alpha, dtype), _scalar(beta, dtype)

@@ -189,8 +189,11 @@ int b2s_panel_build_global(int val_type, int idx_type, int ptr_type,
  *
  * b2s_spmv_stack_rows_combine: the stacked rows here are (panel, long row) pairs; seg_ids_dev
  * [seg_ptr_dev[j] .. seg_ptr_dev[j + 1]) lists the stacked rows of long row j in ascending panel
- * order and the call adds alpha times their sum (fixed order) to y_dev[rows_dev[j]]; n_part is
- * the number of stacked rows (the bounds-checked build verifies seg_ids against it).
+ * order and the call writes their sum (fixed order) to out_dev[j].  The host side points the
+ * position table of the wide-panel stack at these sums (one more "stacked row" per long row
+ * behind the n_stacked real ones), so that b2s_panel_combine / b2s_panel_combine_peers add them
+ * like any other partial.  n_part is the number of stacked rows (the bounds-checked build
+ * verifies seg_ids against it).
  */
 int b2s_spmv_stack_tile_items(int val_type);
 int b2s_spmv_stack_shared_cols(int val_type);
@@ -206,9 +209,8 @@ int b2s_spmv_stack_shared(int val_type, const void* s_data_dev, const uint32_t* 
                           const int64_t* tile_ord_dev, const void* x_dev, void* ypart_dev,
                           void* carry_dev, int32_t* status_dev, b2s_stream stream);
 int b2s_spmv_stack_rows_combine(int val_type, const void* part_dev, const int64_t* seg_ptr_dev,
-                                const int32_t* seg_ids_dev, const int64_t* rows_dev,
-                                int64_t n_long, int64_t n_part, void* y_dev, const void* alpha,
-                                int32_t* status_dev, b2s_stream stream);
+                                const int32_t* seg_ids_dev, int64_t n_long, int64_t n_part,
+                                void* out_dev, int32_t* status_dev, b2s_stream stream);
 /* y = alpha * (sum over panels p of ypart[subpos[p * n_rows + r]], ascending p) + beta * y_in,
  * for every matrix row r (subpos_dev == NULL: ypart holds n_panels * n_rows values, none
  * dropped).  y_in_dev may be NULL when *beta == 0 and may equal y_dev. */

@@ -283,6 +283,108 @@ def test_spmv_column_panel_layout_vs_oracle(monkeypatch, dtype, idx_dtype, targe
     clear_plan_cache()
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64], ids=["i32", "i64"])
+@pytest.mark.parametrize("slice_cols", [64, 1024])
+def test_spmv_long_rows_from_shared_memory_slices(monkeypatch, dtype, idx_dtype, slice_cols):
+    """The long rows of a panel-layout matrix are multiplied from shared-memory slices of x
+    (b2s_spmv_stack_shared).  Forced onto a small matrix: narrow panels of 64 / 1024 columns
+    (so 94 / 6 slices), several CTAs per slice, rows that span many tiles, rows that end
+    exactly on tile borders, alpha / beta, bit-identical repeats."""
+    import flagsparse_b200._plan as plan_mod
+    from flagsparse_b200 import clear_plan_cache, flagsparse_spmv_csr
+    monkeypatch.setattr(plan_mod, "PANEL_TRIGGER_BYTES", 0)
+    monkeypatch.setattr(plan_mod, "PANEL_TARGET_BYTES", 2048 * np.dtype(dtype).itemsize)
+    monkeypatch.setattr(plan_mod, "PANEL_MIN_NNZ", 0)
+    monkeypatch.setattr(plan_mod, "LONG_SPMV_SLICE_COLS", slice_cols)
+    monkeypatch.setattr(plan_mod, "LONG_SPMV_MIN_PER_PANEL", 2.0)
+    monkeypatch.setattr(plan_mod, "LONG_SPMV_TILES_PER_UNIT", 2)
+    clear_plan_cache()
+    rng = np.random.default_rng(slice_cols)
+    lengths = np.concatenate([[0, 1, 5000, 0, 33, 256, 512, 1024], rng.integers(0, 12, 3000),
+                              [2500, 0, 9000, 3]])
+    n_rows, n_cols = lengths.size, 6000
+    data, idx, ptr = csr_from_lengths(rng, lengths, n_cols, dtype, sort=False)
+    x = random_values(rng, n_cols, dtype)
+    y0 = random_values(rng, n_rows, dtype)
+    alpha, beta = (1.5, 0.5) if np.dtype(dtype).kind != "c" else (1.5 - 0.25j, 0.5 + 2j)
+    expect = oracle.spmv(data, idx, ptr, x, (n_rows, n_cols), alpha=alpha, beta=beta, y0=y0)
+    args = (dev(data), dev(idx, idx_dtype), dev(ptr, idx_dtype), dev(x), (n_rows, n_cols))
+    out = dev(y0)
+    y = flagsparse_spmv_csr(*args, out=out, alpha=alpha, beta=beta)
+    plan = plan_mod.cache_get(plan_mod.plan_key("spmv", args[0], args[1], args[2], args[4]))
+    lay = plan.panels()
+    assert lay is not None and lay.long_rows is not None
+    assert 3 <= lay.long_rows.n_long <= 8 and lay.long_rows.n_units > 1
+    assert_parity(host(y), expect, dtype)
+    out2 = dev(y0)
+    flagsparse_spmv_csr(*args, out=out2, alpha=alpha, beta=beta)
+    assert torch.equal(out.view(torch.uint8), out2.view(torch.uint8))
+    clear_plan_cache()
+
+
+def test_spmv_and_spmm_accept_inference_mode_tensors():
+    """Tensors made under torch.inference_mode() have no version counter; the plan cache must
+    not trip over that (the reference works there)."""
+    from flagsparse_b200 import clear_plan_cache, flagsparse_spmm_csr, flagsparse_spmv_csr
+    rng = np.random.default_rng(5)
+    lengths = rng.integers(0, 9, 300)
+    data, idx, ptr = csr_from_lengths(rng, lengths, 200, np.float32)
+    x = random_values(rng, 200, np.float32)
+    B = random_values(rng, 200 * 8, np.float32).reshape(200, 8)
+    with torch.inference_mode():
+        d, i, p, xd, Bd = dev(data), dev(idx, torch.int32), dev(ptr, torch.int32), dev(x), dev(B)
+        y = flagsparse_spmv_csr(d, i, p, xd, (300, 200))
+        C = flagsparse_spmm_csr(d, i, p, Bd, (300, 200))
+        y_again = flagsparse_spmv_csr(d, i, p, xd, (300, 200))
+    assert_parity(host(y), oracle.spmv(data, idx, ptr, x, (300, 200)), np.float32)
+    assert_parity(host(C), oracle.spmm(data, idx, ptr, B, (300, 200)), np.float32)
+    assert torch.equal(y, y_again)
+    clear_plan_cache()
+
+
+def test_prepared_handle_follows_in_place_value_updates_on_the_panel_layout(monkeypatch):
+    """A prepared handle keeps the caller's data tensor, as the reference's does
+    (spmv_csr.py:55-79): values changed in place afterwards are the ones multiplied, also when
+    the kernels read a re-laid-out private copy of the matrix."""
+    import flagsparse_b200._plan as plan_mod
+    from flagsparse_b200 import clear_plan_cache, flagsparse_spmv_csr, prepare_spmv_csr
+    monkeypatch.setattr(plan_mod, "PANEL_TRIGGER_BYTES", 0)
+    monkeypatch.setattr(plan_mod, "PANEL_TARGET_BYTES", 512 * 8)
+    monkeypatch.setattr(plan_mod, "PANEL_MIN_NNZ", 0)
+    clear_plan_cache()
+    rng = np.random.default_rng(9)
+    lengths = rng.integers(0, 20, 2000)
+    data, idx, ptr = csr_from_lengths(rng, lengths, 4000, np.float64)
+    x = random_values(rng, 4000, np.float64)
+    d, i, p = dev(data), dev(idx, torch.int64), dev(ptr, torch.int64)
+    prepared = prepare_spmv_csr(d, i, p, (2000, 4000))
+    y1 = flagsparse_spmv_csr(x=dev(x), prepared=prepared)
+    assert prepared.plan().panels() is not None
+    assert_parity(host(y1), oracle.spmv(data, idx, ptr, x, (2000, 4000)), np.float64)
+    d.mul_(-3.0)
+    y2 = flagsparse_spmv_csr(x=dev(x), prepared=prepared)
+    assert_parity(host(y2), oracle.spmv(-3.0 * data, idx, ptr, x, (2000, 4000)), np.float64)
+    clear_plan_cache()
+
+
+def test_plan_cache_is_bounded_by_bytes():
+    import flagsparse_b200._plan as plan_mod
+    from flagsparse_b200 import (clear_plan_cache, flagsparse_spmv_csr, set_plan_cache_bytes)
+    clear_plan_cache()
+    rng = np.random.default_rng(3)
+    try:
+        set_plan_cache_bytes(1)          # nothing but the newest plan fits
+        for k in range(3):
+            data, idx, ptr = csr_from_lengths(rng, rng.integers(1, 9, 500), 300, np.float32)
+            flagsparse_spmv_csr(dev(data), dev(idx, torch.int32), dev(ptr, torch.int32),
+                                dev(random_values(rng, 300, np.float32)), (500, 300))
+            assert len(plan_mod._CACHE) == 1
+    finally:
+        set_plan_cache_bytes(None)
+        clear_plan_cache()
+
+
 def test_spmv_coo_front_door_and_public_transpose():
     """flagsparse_spmv_coo_tocsr (spmv_csr.py:988-1057): unsorted COO with duplicates, the
     prepared form, and csr_to_csc against the oracle's stable transpose."""
