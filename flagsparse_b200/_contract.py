@@ -17,10 +17,13 @@ OP_NAMES = {OP_NON: "non", OP_TRANS: "trans", OP_CONJ_TRANS: "conj"}
 _NAME_TO_OP = {v: k for k, v in OP_NAMES.items()}
 _OP_MESSAGE = "op must be one of: 0=non, 1=trans, 2=conj"
 
-# The value dtypes the kernels compute in.  FlagSparse additionally lists float16 / bfloat16
-# (_common.py:21-29) and computes them in float32; here they are widened once and run through the
-# float32 kernels (_half.py).
+# The value dtypes of FlagSparse (_common.py:21-29).  float16 / bfloat16 are stored as they are
+# (matrix values, dense operand and result) and summed in float32 with one rounding at the end,
+# the arithmetic the reference's launchers do on float32 copies (spmv_csr.py:124-129,
+# spmm_csr.py:2716-2719).
+HALF_VALUE_DTYPES = (torch.float16, torch.bfloat16)
 SUPPORTED_VALUE_DTYPES = (torch.float32, torch.float64, torch.complex64, torch.complex128)
+ALL_VALUE_DTYPES = HALF_VALUE_DTYPES + SUPPORTED_VALUE_DTYPES
 SUPPORTED_INDEX_DTYPES = (torch.int32, torch.int64)
 INDEX_LIMIT_INT32 = 2**31 - 1
 

@@ -19,7 +19,7 @@ LIB_PATH = Path(__file__).resolve().parent / (
     "libb200sparse_checked.so" if CHECKED else "libb200sparse.so")
 
 # dtype codes of include/b200sparse.h
-B2S_F32, B2S_F64, B2S_C64, B2S_C128 = 0, 1, 2, 3
+B2S_F32, B2S_F64, B2S_C64, B2S_C128, B2S_F16, B2S_BF16 = 0, 1, 2, 3, 4, 5
 B2S_I32, B2S_I64 = 0, 1
 B2S_ERR_TIMEOUT = 5
 B2S_ERR_BOUNDS = 9
@@ -29,6 +29,8 @@ VALUE_CODE = {
     torch.float64: B2S_F64,
     torch.complex64: B2S_C64,
     torch.complex128: B2S_C128,
+    torch.float16: B2S_F16,
+    torch.bfloat16: B2S_BF16,
 }
 INDEX_CODE = {torch.int32: B2S_I32, torch.int64: B2S_I64}
 
@@ -72,6 +74,10 @@ SIGNATURES = {
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_int, c_void_p]),
+    "b2s_spmm_csr_colmajor_c": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                        c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p]),
     "b2s_spmm_rows_combine": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                       c_void_p, c_int64, c_void_p, c_void_p]),
     "b2s_dense_transpose": (c_int, [c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
@@ -137,7 +143,7 @@ def stream_handle(device) -> c_void_p:
 
 def scalar_buffer(value, dtype):
     """Host buffer holding one scalar of the value dtype (alpha / beta are host pointers)."""
-    if dtype == torch.float32:
+    if dtype in (torch.float32, torch.float16, torch.bfloat16):   # 16-bit values: float32 sums
         return (ctypes.c_float * 1)(float(value))
     if dtype == torch.float64:
         return (ctypes.c_double * 1)(float(value))

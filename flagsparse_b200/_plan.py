@@ -412,6 +412,14 @@ class CsrPlan:
         return self.scratch_on(tag, n_values, torch.cuda.current_stream(self.device).cuda_stream,
                                dtype)
 
+    def carry_on(self, tag, n_tile_values, stream):
+        """Scratch for the carries of n_tile_values (tiles, or tiles x dense columns): the
+        accumulation dtype, and twice as many for the 16-bit dtypes, whose rows that cross tile
+        borders are finished by the fix-up (include/b200sparse.h, b2s_spmv_csr)."""
+        if self.data.element_size() < 4:
+            return self.scratch_on(tag, 2 * int(n_tile_values), stream, torch.float32)
+        return self.scratch_on(tag, n_tile_values, stream)
+
     def scratch_on(self, tag, n_values, stream, dtype=None):
         key = (tag, int(n_values), stream)
         buf = self._scratch.get(key)
@@ -430,7 +438,7 @@ class CsrPlan:
             return self._panels
         self._panels = None
         vbytes = self.data.element_size()
-        if (PANEL_POLICY != "auto" or self.n_cols * vbytes <= PANEL_TRIGGER_BYTES
+        if (PANEL_POLICY != "auto" or vbytes < 4 or self.n_cols * vbytes <= PANEL_TRIGGER_BYTES
                 or self.nnz < PANEL_MIN_NNZ or self.n_rows == 0):
             return None
         shift = 1
@@ -495,6 +503,8 @@ class CsrPlan:
         matrix, else None (decided and built once per panel width)."""
         shift = long_row_shift(self.n_cols, row_bytes)
         if shift is None or self.nnz < LONG_ROW_MIN_NNZ or self.n_cols > INDEX_LIMIT_INT32:
+            return None
+        if self.data.element_size() < 4:      # 16-bit values: the one-launch product only
             return None
         if shift in self._long_rows:
             return self._long_rows[shift]

@@ -1,5 +1,7 @@
 // Shared device helpers: value types, warp shuffles, mbarrier + bulk-copy (TMA) wrappers.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "../../include/b200sparse.h"
@@ -50,6 +52,44 @@ template <> struct vt<c128> {
   __host__ __device__ static bool is_zero(c128 a) { return a.re == 0.0 && a.im == 0.0; }
   __host__ __device__ static c128 conj(c128 a) { return {a.re, -a.im}; }
 };
+
+// 16-bit storage types: values, x / B and y / C are kept as float16 or bfloat16, every sum is a
+// float32 sum and the result is rounded once.  to_acc widens, from_acc rounds to nearest even.
+using f16 = __half;
+using bf16 = __nv_bfloat16;
+template <class V> __host__ __device__ inline V to_acc(V s) { return s; }
+__device__ inline float to_acc(f16 s) { return __half2float(s); }
+__device__ inline float to_acc(bf16 s) { return __bfloat162float(s); }
+template <class S> struct storage_of {
+  template <class V> __device__ static S from_acc(V v) { return v; }
+};
+template <> struct storage_of<f16> {
+  __device__ static f16 from_acc(float v) { return __float2half_rn(v); }
+};
+template <> struct storage_of<bf16> {
+  __device__ static bf16 from_acc(float v) { return __float2bfloat16_rn(v); }
+};
+__device__ inline f16 ldg_val(const f16* p) { return __ldg(p); }
+__device__ inline bf16 ldg_val(const bf16* p) { return __ldg(p); }
+
+// 2-byte payload for kernels that only move values (transpose, re-layouts): both 16-bit dtypes
+struct raw16 {
+  uint16_t bits;
+};
+template <> struct vt<raw16> {
+  __host__ __device__ static raw16 conj(raw16 a) { return a; }
+};
+// value dtype -> the type that moves its values around (the 16-bit dtypes share one)
+#define B2S_DISPATCH_MOVE(vtype, ...)                           \
+  switch (vtype) {                                              \
+    case B2S_F32: { using V = float; __VA_ARGS__; } break;      \
+    case B2S_F64: { using V = double; __VA_ARGS__; } break;     \
+    case B2S_C64: { using V = b2s::c64; __VA_ARGS__; } break;   \
+    case B2S_C128: { using V = b2s::c128; __VA_ARGS__; } break; \
+    case B2S_F16:                                               \
+    case B2S_BF16: { using V = b2s::raw16; __VA_ARGS__; } break; \
+    default: return B2S_ERR_DTYPE;                              \
+  }
 
 // acc = acc + a * b with the contraction the hardware offers
 __device__ inline void fma_acc(float& acc, float a, float b) { acc = fmaf(a, b, acc); }
@@ -248,8 +288,14 @@ inline size_t vsize(int vtype) {
     case B2S_F64: return 8;
     case B2S_C64: return 8;
     case B2S_C128: return 16;
+    case B2S_F16: return 2;
+    case B2S_BF16: return 2;
   }
   return 0;
+}
+// size of the scalar alpha / beta point at: the accumulation type (float for 16-bit values)
+inline size_t acc_size(int vtype) {
+  return (vtype == B2S_F16 || vtype == B2S_BF16) ? 4 : vsize(vtype);
 }
 inline size_t isize(int itype) { return itype == B2S_I32 ? 4 : (itype == B2S_I64 ? 8 : 0); }
 
@@ -260,6 +306,17 @@ inline size_t isize(int itype) { return itype == B2S_I32 ? 4 : (itype == B2S_I64
     case B2S_C64: { using V = b2s::c64; __VA_ARGS__; } break;    \
     case B2S_C128: { using V = b2s::c128; __VA_ARGS__; } break;  \
     default: return B2S_ERR_DTYPE;                          \
+  }
+// value dtype -> accumulation type V and storage type S (S == V but for the 16-bit dtypes)
+#define B2S_DISPATCH_VS(vtype, ...)                                                   \
+  switch (vtype) {                                                                    \
+    case B2S_F32: { using V = float; using S = float; __VA_ARGS__; } break;           \
+    case B2S_F64: { using V = double; using S = double; __VA_ARGS__; } break;         \
+    case B2S_C64: { using V = b2s::c64; using S = b2s::c64; __VA_ARGS__; } break;     \
+    case B2S_C128: { using V = b2s::c128; using S = b2s::c128; __VA_ARGS__; } break;  \
+    case B2S_F16: { using V = float; using S = b2s::f16; __VA_ARGS__; } break;        \
+    case B2S_BF16: { using V = float; using S = b2s::bf16; __VA_ARGS__; } break;      \
+    default: return B2S_ERR_DTYPE;                                                    \
   }
 #define B2S_DISPATCH_I(itype, NAME, ...)                       \
   switch (itype) {                                             \

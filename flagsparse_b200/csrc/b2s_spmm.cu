@@ -7,6 +7,8 @@
 // combine with a fixed butterfly (inside a warp) or a fixed-order pass over shared memory
 // (whole CTA).  Rows that cross tile borders leave N-wide partials in `carry`; a second kernel
 // adds them in ascending tile order.  No floating-point atomics.
+#include <type_traits>
+
 #include "b2s_tile.cuh"
 
 namespace b2s {
@@ -38,95 +40,140 @@ constexpr int kSpmmWarpRowMax = 512;
 constexpr int kSpmmQueue2Cap = 256;
 constexpr int kSpmmQueue3Cap = 8;
 
-template <class V>
-struct alignas(16) Pack {  // the 16 bytes of a B / C row one lane owns
-  static constexpr int N = sizeof(V) >= 16 ? 1 : 16 / static_cast<int>(sizeof(V));
+// What one lane owns of a B / C row: the values held in 16 bytes of storage (S), kept as
+// accumulation type V (S itself, or float for the 16-bit storage types: 8 values per lane).
+template <class V, class S = V>
+struct alignas(16) Pack {
+  static constexpr int N = sizeof(S) >= 16 ? 1 : 16 / static_cast<int>(sizeof(S));
   V e[N];
 };
 
-template <class V>
-__device__ inline Pack<V> pack_zero() {
-  Pack<V> p;
+template <class V, class S = V>
+__device__ inline Pack<V, S> pack_zero() {
+  Pack<V, S> p;
 #pragma unroll
-  for (int i = 0; i < Pack<V>::N; ++i) p.e[i] = vt<V>::zero();
+  for (int i = 0; i < Pack<V, S>::N; ++i) p.e[i] = vt<V>::zero();
   return p;
+}
+
+// 16 bytes of storage -> the lane's values in accumulation type, and back (rounding once)
+template <class V, class S>
+__device__ inline Pack<V, S> unpack16(const uint4& raw) {
+  Pack<V, S> p;
+  if constexpr (std::is_same<S, V>::value) {
+    *reinterpret_cast<uint4*>(&p) = raw;
+  } else {
+    S s[Pack<V, S>::N];
+    *reinterpret_cast<uint4*>(s) = raw;
+#pragma unroll
+    for (int i = 0; i < Pack<V, S>::N; ++i) p.e[i] = to_acc(s[i]);
+  }
+  return p;
+}
+template <class V, class S>
+__device__ inline uint4 pack16(const Pack<V, S>& p) {
+  uint4 raw;
+  if constexpr (std::is_same<S, V>::value) {
+    raw = *reinterpret_cast<const uint4*>(&p);
+  } else {
+    alignas(16) S s[Pack<V, S>::N];
+#pragma unroll
+    for (int i = 0; i < Pack<V, S>::N; ++i) s[i] = storage_of<S>::from_acc(p.e[i]);
+    raw = *reinterpret_cast<const uint4*>(s);
+  }
+  return raw;
 }
 
 // load the lane's slice of B row `brow` (elements e0 .. e0+N-1 of n_dense)
-template <class V>
-__device__ inline Pack<V> load_pack(const V* __restrict__ brow, int64_t e0, int64_t n_dense,
-                                    bool vec_ok) {
-  Pack<V> p;
-  if (vec_ok && e0 + Pack<V>::N <= n_dense) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(brow + e0));
-    *reinterpret_cast<uint4*>(&p) = raw;
-  } else {
+template <class V, class S>
+__device__ inline Pack<V, S> load_pack(const S* __restrict__ brow, int64_t e0, int64_t n_dense,
+                                       bool vec_ok) {
+  if (vec_ok && e0 + Pack<V, S>::N <= n_dense)
+    return unpack16<V, S>(__ldg(reinterpret_cast<const uint4*>(brow + e0)));
+  Pack<V, S> p;
 #pragma unroll
-    for (int i = 0; i < Pack<V>::N; ++i)
-      p.e[i] = (e0 + i < n_dense) ? ldg_val(brow + e0 + i) : vt<V>::zero();
-  }
+  for (int i = 0; i < Pack<V, S>::N; ++i)
+    p.e[i] = (e0 + i < n_dense) ? to_acc(ldg_val(brow + e0 + i)) : vt<V>::zero();
   return p;
 }
 
-template <class V>
-__device__ inline void fma_pack(Pack<V>& acc, V a, const Pack<V>& b) {
+template <class V, class S>
+__device__ inline void fma_pack(Pack<V, S>& acc, V a, const Pack<V, S>& b) {
 #pragma unroll
-  for (int i = 0; i < Pack<V>::N; ++i) fma_acc(acc.e[i], a, b.e[i]);
+  for (int i = 0; i < Pack<V, S>::N; ++i) fma_acc(acc.e[i], a, b.e[i]);
 }
 
-template <class V>
-__device__ inline Pack<V> add_pack(const Pack<V>& a, const Pack<V>& b) {
-  Pack<V> r;
+template <class V, class S>
+__device__ inline Pack<V, S> add_pack(const Pack<V, S>& a, const Pack<V, S>& b) {
+  Pack<V, S> r;
 #pragma unroll
-  for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = a.e[i] + b.e[i];
+  for (int i = 0; i < Pack<V, S>::N; ++i) r.e[i] = a.e[i] + b.e[i];
   return r;
 }
 
-template <class V>
-__device__ inline Pack<V> shfl_xor_pack(const Pack<V>& a, int m) {
-  Pack<V> r;
+template <class V, class S>
+__device__ inline Pack<V, S> shfl_xor_pack(const Pack<V, S>& a, int m) {
+  Pack<V, S> r;
 #pragma unroll
-  for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = shfl_xor(a.e[i], m);
+  for (int i = 0; i < Pack<V, S>::N; ++i) r.e[i] = shfl_xor(a.e[i], m);
   return r;
 }
 
-// out[e0..] = alpha * acc + beta * in[e0..]
-template <class V>
-__device__ inline void store_pack(V* out, const V* in, int64_t e0, int64_t n_dense,
-                                  const Pack<V>& acc, V alpha, V beta, bool has_beta,
-                                  bool vec_ok) {
+// out[e0..] = alpha * acc + beta * in[e0..], rounded to the storage type; `cs` is the distance
+// between two columns of the row (1: row-major C, one 16-byte store; n_rows: column-major C,
+// one store per value, consecutive rows of a column being neighbours in memory)
+template <class V, class S>
+__device__ inline void store_pack(S* out, const S* in, int64_t e0, int64_t n_dense,
+                                  const Pack<V, S>& acc, V alpha, V beta, bool has_beta,
+                                  bool vec_ok, int64_t cs = 1) {
   if (e0 >= n_dense) return;
-  Pack<V> r;
-  if (vec_ok && e0 + Pack<V>::N <= n_dense) {
-    if (has_beta) {
-      Pack<V> old;
-      *reinterpret_cast<uint4*>(&old) = *reinterpret_cast<const uint4*>(in + e0);
+  constexpr int N = Pack<V, S>::N;
+  Pack<V, S> r;
+  if (cs != 1) {
 #pragma unroll
-      for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = alpha * acc.e[i] + beta * old.e[i];
+    for (int i = 0; i < N; ++i) {
+      if (e0 + i < n_dense) {
+        V v = alpha * acc.e[i];
+        if (has_beta) v = v + beta * to_acc(in[(e0 + i) * cs]);
+        out[(e0 + i) * cs] = storage_of<S>::from_acc(v);
+      }
+    }
+    return;
+  }
+  if (vec_ok && e0 + N <= n_dense) {
+    if (has_beta) {
+      const Pack<V, S> old = unpack16<V, S>(*reinterpret_cast<const uint4*>(in + e0));
+#pragma unroll
+      for (int i = 0; i < N; ++i) r.e[i] = alpha * acc.e[i] + beta * old.e[i];
     } else {
 #pragma unroll
-      for (int i = 0; i < Pack<V>::N; ++i) r.e[i] = alpha * acc.e[i];
+      for (int i = 0; i < N; ++i) r.e[i] = alpha * acc.e[i];
     }
-    *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(&r);
+    *reinterpret_cast<uint4*>(out + e0) = pack16<V, S>(r);
   } else {
 #pragma unroll
-    for (int i = 0; i < Pack<V>::N; ++i) {
-      if (e0 + i < n_dense) out[e0 + i] = axpby(alpha, acc.e[i], has_beta, beta, in + e0 + i);
+    for (int i = 0; i < N; ++i) {
+      if (e0 + i < n_dense) {
+        V v = alpha * acc.e[i];
+        if (has_beta) v = v + beta * to_acc(in[e0 + i]);
+        out[e0 + i] = storage_of<S>::from_acc(v);
+      }
     }
   }
 }
 
-template <class V>
-__device__ inline void store_raw(V* out, int64_t e0, int64_t n_dense, const Pack<V>& acc) {
+// unrounded partial sums (carries) in accumulation type
+template <class V, class S>
+__device__ inline void store_raw(V* out, int64_t e0, int64_t n_dense, const Pack<V, S>& acc) {
 #pragma unroll
-  for (int i = 0; i < Pack<V>::N; ++i)
+  for (int i = 0; i < Pack<V, S>::N; ++i)
     if (e0 + i < n_dense) out[e0 + i] = acc.e[i];
 }
 
-template <int THREADS, int ITEMS, class V, class I>
+template <int THREADS, int ITEMS, class V, class I, class S = V>
 __host__ __device__ constexpr size_t spmm_smem_bytes() {
   return 16 + sizeof(int) * (ITEMS + 4) + sizeof(I) * ITEMS + 16 + sizeof(V) * ITEMS + 16 +
-         sizeof(int) * (kSpmmQueue2Cap + kSpmmQueue3Cap + 4) + 16 * THREADS;
+         sizeof(int) * (kSpmmQueue2Cap + kSpmmQueue3Cap + 4) + sizeof(Pack<V, S>) * THREADS;
 }
 
 // Accumulate A[piece] * B over non-zeros s + first, s + first + step, ... < e of the staged tile.
@@ -145,10 +192,10 @@ __device__ inline uint4 load_b16(const uint4* p) {
     return __ldg(p);
 }
 
-template <class V, class I, bool VEC, bool WIN = false>
-__device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
-                                  const V* __restrict__ sval, int s, int e, int first, int step,
-                                  const V* __restrict__ B, int64_t ldb, int64_t e0,
+template <class V, class I, bool VEC, bool WIN = false, class S = V>
+__device__ inline void accumulate(Pack<V, S>& acc, const I* __restrict__ scol,
+                                  const S* __restrict__ sval, int s, int e, int first, int step,
+                                  const S* __restrict__ B, int64_t ldb, int64_t e0,
                                   int64_t n_dense, const uint4* Bv, int64_t stride16,
                                   uint32_t mask_col = 0) {
   int i = s + first;
@@ -158,7 +205,7 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
       // all of B lies within 2^32 sixteen-byte units: 32-bit row offsets (one multiply, one
       // widening add per gather instead of a 64-bit multiply)
       const uint32_t s32 = static_cast<uint32_t>(-stride16);
-      if constexpr (sizeof(I) == 4 && sizeof(V) == 4) {
+      if constexpr (sizeof(I) == 4 && sizeof(V) == 4 && std::is_same<S, V>::value) {
         // consecutive entries, 4-byte col and val staged with the same 16-byte phase: four
         // columns and four values per 128-bit shared-memory read
         const unsigned phase_c = (static_cast<unsigned>(smem_addr(scol)) >> 2) & 3u;
@@ -174,7 +221,7 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
           for (int a = i - static_cast<int>((static_cast<unsigned>(i) + phase_c) & 3u); a < e;
                a += 4) {
             uint4 c4 = *reinterpret_cast<const uint4*>(scol + a);
-            Pack<V> a4;
+            Pack<V, S> a4;
             *reinterpret_cast<uint4*>(&a4) = *reinterpret_cast<const uint4*>(sval + a);
             const bool k0 = a >= first, k1 = a + 1 >= first && a + 1 < e,
                        k2 = a + 2 >= first && a + 2 < e, k3 = a + 3 < e;
@@ -184,11 +231,11 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
             if (!k1) c4.y = mask_col;
             if (!k2) c4.z = mask_col;
             if (!k3) c4.w = mask_col;
-            Pack<V> b0, b1, b2, b3;
-            *reinterpret_cast<uint4*>(&b0) = load_b16<WIN>(Bv + c4.x * s32);
-            *reinterpret_cast<uint4*>(&b1) = load_b16<WIN>(Bv + c4.y * s32);
-            *reinterpret_cast<uint4*>(&b2) = load_b16<WIN>(Bv + c4.z * s32);
-            *reinterpret_cast<uint4*>(&b3) = load_b16<WIN>(Bv + c4.w * s32);
+            Pack<V, S> b0, b1, b2, b3;
+            b0 = unpack16<V, S>(load_b16<WIN>(Bv + c4.x * s32));
+            b1 = unpack16<V, S>(load_b16<WIN>(Bv + c4.y * s32));
+            b2 = unpack16<V, S>(load_b16<WIN>(Bv + c4.z * s32));
+            b3 = unpack16<V, S>(load_b16<WIN>(Bv + c4.w * s32));
             if (k0) fma_pack(acc, a4.e[0], b0);
             if (k1) fma_pack(acc, a4.e[1], b1);
             if (k2) fma_pack(acc, a4.e[2], b2);
@@ -202,57 +249,57 @@ __device__ inline void accumulate(Pack<V>& acc, const I* __restrict__ scol,
         const uint32_t o1 = static_cast<uint32_t>(scol[i + step]) * s32;
         const uint32_t o2 = static_cast<uint32_t>(scol[i + 2 * step]) * s32;
         const uint32_t o3 = static_cast<uint32_t>(scol[i + 3 * step]) * s32;
-        Pack<V> b0, b1, b2, b3;
-        *reinterpret_cast<uint4*>(&b0) = load_b16<WIN>(Bv + o0);
-        *reinterpret_cast<uint4*>(&b1) = load_b16<WIN>(Bv + o1);
-        *reinterpret_cast<uint4*>(&b2) = load_b16<WIN>(Bv + o2);
-        *reinterpret_cast<uint4*>(&b3) = load_b16<WIN>(Bv + o3);
-        fma_pack(acc, sval[i], b0);
-        fma_pack(acc, sval[i + step], b1);
-        fma_pack(acc, sval[i + 2 * step], b2);
-        fma_pack(acc, sval[i + 3 * step], b3);
+        Pack<V, S> b0, b1, b2, b3;
+        b0 = unpack16<V, S>(load_b16<WIN>(Bv + o0));
+        b1 = unpack16<V, S>(load_b16<WIN>(Bv + o1));
+        b2 = unpack16<V, S>(load_b16<WIN>(Bv + o2));
+        b3 = unpack16<V, S>(load_b16<WIN>(Bv + o3));
+        fma_pack(acc, to_acc(sval[i]), b0);
+        fma_pack(acc, to_acc(sval[i + step]), b1);
+        fma_pack(acc, to_acc(sval[i + 2 * step]), b2);
+        fma_pack(acc, to_acc(sval[i + 3 * step]), b3);
       }
       for (; i < e; i += step) {
-        Pack<V> b;
-        *reinterpret_cast<uint4*>(&b) = load_b16<WIN>(Bv + static_cast<uint32_t>(scol[i]) * s32);
-        fma_pack(acc, sval[i], b);
+        Pack<V, S> b;
+        b = unpack16<V, S>(load_b16<WIN>(Bv + static_cast<uint32_t>(scol[i]) * s32));
+        fma_pack(acc, to_acc(sval[i]), b);
       }
       return;
     }
     for (; i + 3 * step < e; i += 4 * step) {
       const I c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step], c3 = scol[i + 3 * step];
-      Pack<V> b0, b1, b2, b3;
-      *reinterpret_cast<uint4*>(&b0) = __ldg(Bv + static_cast<int64_t>(c0) * stride16);
-      *reinterpret_cast<uint4*>(&b1) = __ldg(Bv + static_cast<int64_t>(c1) * stride16);
-      *reinterpret_cast<uint4*>(&b2) = __ldg(Bv + static_cast<int64_t>(c2) * stride16);
-      *reinterpret_cast<uint4*>(&b3) = __ldg(Bv + static_cast<int64_t>(c3) * stride16);
-      fma_pack(acc, sval[i], b0);
-      fma_pack(acc, sval[i + step], b1);
-      fma_pack(acc, sval[i + 2 * step], b2);
-      fma_pack(acc, sval[i + 3 * step], b3);
+      Pack<V, S> b0, b1, b2, b3;
+      b0 = unpack16<V, S>(__ldg(Bv + static_cast<int64_t>(c0) * stride16));
+      b1 = unpack16<V, S>(__ldg(Bv + static_cast<int64_t>(c1) * stride16));
+      b2 = unpack16<V, S>(__ldg(Bv + static_cast<int64_t>(c2) * stride16));
+      b3 = unpack16<V, S>(__ldg(Bv + static_cast<int64_t>(c3) * stride16));
+      fma_pack(acc, to_acc(sval[i]), b0);
+      fma_pack(acc, to_acc(sval[i + step]), b1);
+      fma_pack(acc, to_acc(sval[i + 2 * step]), b2);
+      fma_pack(acc, to_acc(sval[i + 3 * step]), b3);
     }
     for (; i < e; i += step) {
-      Pack<V> b;
-      *reinterpret_cast<uint4*>(&b) = __ldg(Bv + static_cast<int64_t>(scol[i]) * stride16);
-      fma_pack(acc, sval[i], b);
+      Pack<V, S> b;
+      b = unpack16<V, S>(__ldg(Bv + static_cast<int64_t>(scol[i]) * stride16));
+      fma_pack(acc, to_acc(sval[i]), b);
     }
   } else {
     for (; i + 3 * step < e; i += 4 * step) {
       const int64_t c0 = scol[i], c1 = scol[i + step], c2 = scol[i + 2 * step],
                     c3 = scol[i + 3 * step];
-      const Pack<V> b0 = load_pack(B + c0 * ldb, e0, n_dense, false);
-      const Pack<V> b1 = load_pack(B + c1 * ldb, e0, n_dense, false);
-      const Pack<V> b2 = load_pack(B + c2 * ldb, e0, n_dense, false);
-      const Pack<V> b3 = load_pack(B + c3 * ldb, e0, n_dense, false);
-      fma_pack(acc, sval[i], b0);
-      fma_pack(acc, sval[i + step], b1);
-      fma_pack(acc, sval[i + 2 * step], b2);
-      fma_pack(acc, sval[i + 3 * step], b3);
+      const Pack<V, S> b0 = load_pack<V, S>(B + c0 * ldb, e0, n_dense, false);
+      const Pack<V, S> b1 = load_pack<V, S>(B + c1 * ldb, e0, n_dense, false);
+      const Pack<V, S> b2 = load_pack<V, S>(B + c2 * ldb, e0, n_dense, false);
+      const Pack<V, S> b3 = load_pack<V, S>(B + c3 * ldb, e0, n_dense, false);
+      fma_pack(acc, to_acc(sval[i]), b0);
+      fma_pack(acc, to_acc(sval[i + step]), b1);
+      fma_pack(acc, to_acc(sval[i + 2 * step]), b2);
+      fma_pack(acc, to_acc(sval[i + 3 * step]), b3);
     }
     for (; i < e; i += step) {
       const int64_t c = scol[i];
-      const Pack<V> b = load_pack(B + c * ldb, e0, n_dense, false);
-      fma_pack(acc, sval[i], b);
+      const Pack<V, S> b = load_pack<V, S>(B + c * ldb, e0, n_dense, false);
+      fma_pack(acc, to_acc(sval[i]), b);
     }
   }
 }
@@ -280,11 +327,17 @@ constexpr int spmm_min_blocks() {
 // and the largest column of the tile are copied into shared memory by one bulk copy and every
 // gather of the tile is a shared-memory read; `win_rows_cap` rows fit the buffer behind the
 // other arrays (the host has checked that no tile of the matrix spans more).
-template <class V, class I, class P, int THREADS, int ITEMS, bool VEC, bool WIN = false>
+// ST: storage type of val, B and C (V itself, or a 16-bit float type with V = float: eight
+// columns per lane, float32 sums, one rounding).  With a 16-bit ST the last piece of a row that
+// began in an earlier tile is left unrounded in first_part (one row of n_dense values per tile)
+// and the fix-up rounds the row once.
+template <class V, class I, class P, int THREADS, int ITEMS, bool VEC, bool WIN = false,
+          class ST = V>
 __global__ void __launch_bounds__(THREADS, spmm_min_blocks<V, I, WIN>())
-spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
-                 const V* __restrict__ B, int64_t ldb, int64_t n_dense, const V* C_in, V* C,
-                 int64_t ldc, V* __restrict__ carry, const int64_t* __restrict__ tile_row,
+spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
+                 const ST* __restrict__ B, int64_t ldb, int64_t n_dense, const ST* C_in, ST* C,
+                 int64_t ldc, int64_t cs, V* __restrict__ carry, V* __restrict__ first_part,
+                 const int64_t* __restrict__ tile_row,
                  int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int small_b,
                  int vec_c, int32_t* status, int win_rows_cap = 0,
                  const int32_t* __restrict__ tile_win = nullptr) {
@@ -297,7 +350,7 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   int* queue2 = reinterpret_cast<int*>(val_buf + sizeof(V) * ITEMS + 16);
   int* queue3 = queue2 + kSpmmQueue2Cap;
   int* qcount = queue3 + kSpmmQueue3Cap;
-  Pack<V>* part = reinterpret_cast<Pack<V>*>(qcount + 4);  // THREADS slots of 16 bytes
+  Pack<V, ST>* part = reinterpret_cast<Pack<V, ST>*>(qcount + 4);  // one slot per thread
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -311,9 +364,9 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   const int n_end = static_cast<int>(tc.r1 - tc.r0);
 
   const I* gcol = col + tc.j0;
-  const V* gval = val + tc.j0;
+  const ST* gval = val + tc.j0;
   const Staged<I> sc = stage_layout<I>(col_buf, gcol, n_nz);
-  const Staged<V> sv = stage_layout<V>(val_buf, gval, n_nz);
+  const Staged<ST> sv = stage_layout<ST>(val_buf, gval, n_nz);
   const uint32_t tx = stage_bytes(sc) + stage_bytes(sv);
   if (tid == 0) {
     qcount[0] = 0;
@@ -325,7 +378,7 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   int win_lo = 0, win_rows = 0;
   uint32_t win_bytes = 0;
   constexpr size_t win_off =
-      (spmm_smem_bytes<THREADS, ITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
+      (spmm_smem_bytes<THREADS, ITEMS, V, I, ST>() + 15) & ~static_cast<size_t>(15);
   if constexpr (WIN) {
     win_lo = tile_win[2 * t];
     win_rows = tile_win[2 * t + 1];
@@ -337,8 +390,8 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     // view whose last row has nothing behind it)
     if (win_rows > 0)
       win_bytes = static_cast<uint32_t>(win_rows - 1) *
-                      static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(V))) +
-                  static_cast<uint32_t>(n_dense * static_cast<int64_t>(sizeof(V)));
+                      static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(ST))) +
+                  static_cast<uint32_t>(n_dense * static_cast<int64_t>(sizeof(ST)));
   }
   __syncthreads();
   if (tid == 0 && (tx || win_bytes)) {
@@ -367,21 +420,28 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   __syncthreads();
 
   const I* scol = sc.s;
-  const V* sval = sv.s;
+  const ST* sval = sv.s;
   const bool open_row = tc.r1 < n_rows;
   const int n_seg = n_end + 1;
   const int64_t e0 =
-      (static_cast<int64_t>(blockIdx.y) * G + (tid & (G - 1))) * Pack<V>::N;  // lane's columns
+      (static_cast<int64_t>(blockIdx.y) * G + (tid & (G - 1))) * Pack<V, ST>::N;  // lane's columns
   const bool vc = VEC || vec_c != 0;
   const uint4* Bv = reinterpret_cast<const uint4*>(B + (VEC && e0 < n_dense ? e0 : 0));
-  int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(V)) / 16 : 0;
+  int64_t stride16 = VEC ? ldb * static_cast<int64_t>(sizeof(ST)) / 16 : 0;
   if (VEC && small_b) stride16 = -stride16;  // flag for 32-bit row offsets (see accumulate)
   V* carry_row = carry + t * n_dense;
+  // 16-bit storage: the tile's first row, when it began in an earlier tile, is finished (and
+  // rounded once) by the fix-up; its piece here goes to first_part instead of C
+  V* first_row = nullptr;
+  if constexpr (!std::is_same<ST, V>::value) {
+    if (tc.r0 < n_rows && static_cast<int64_t>(ptr[tc.r0]) < tc.j0)
+      first_row = first_part + t * n_dense;
+  }
   uint32_t mask_col = 0;
   if constexpr (WIN) {
-    const uint32_t pitch = static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(V)));
+    const uint32_t pitch = static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(ST)));
     // base such that base + col * (pitch / 16) sixteen-byte units is the lane's slice of row col
-    const uintptr_t lane_bytes = static_cast<uintptr_t>(e0 < n_dense ? e0 : 0) * sizeof(V);
+    const uintptr_t lane_bytes = static_cast<uintptr_t>(e0 < n_dense ? e0 : 0) * sizeof(ST);
     const uintptr_t base = reinterpret_cast<uintptr_t>(smem + win_off) + lane_bytes -
                            static_cast<uintptr_t>(win_lo) * pitch;
     Bv = reinterpret_cast<const uint4*>(base);
@@ -413,9 +473,9 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
         e = row_end[k];
       }
       const int len = e - s;
-      Pack<V> acc = pack_zero<V>();
+      Pack<V, ST> acc = pack_zero<V, ST>();
       if (len <= p1max) {
-        accumulate<V, I, VEC, WIN>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, Bv,
+        accumulate<V, I, VEC, WIN, ST>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, Bv,
                                    stride16, mask_col);
       } else if ((tid % team) == 0) {
         if (len <= kSpmmWarpRowMax) {
@@ -430,7 +490,10 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
       if (live && grp_in_team == 0 && len <= p1max) {
         if (k < n_end) {
           const int64_t r = tc.r0 + k;
-          store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc);
+          if (k == 0 && first_row != nullptr)
+            store_raw(first_row, e0, n_dense, acc);
+          else
+            store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc, cs);
         } else if (open_row) {
           store_raw(carry_row, e0, n_dense, acc);
         }
@@ -445,14 +508,17 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     const int k = queue2[q];
     const int s = k ? row_end[k - 1] : 0;
     const int e = row_end[k];
-    Pack<V> acc = pack_zero<V>();
-    accumulate<V, I, VEC, WIN>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0,
+    Pack<V, ST> acc = pack_zero<V, ST>();
+    accumulate<V, I, VEC, WIN, ST>(acc, scol, sval, s, e, lane / G, groups_per_warp, B, ldb, e0,
                                n_dense, Bv, stride16, mask_col);
     for (int m = 16; m >= G; m >>= 1) acc = add_pack(acc, shfl_xor_pack(acc, m));
     if (lane < G) {
       if (k < n_end) {
         const int64_t r = tc.r0 + k;
-        store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc);
+        if (k == 0 && first_row != nullptr)
+          store_raw(first_row, e0, n_dense, acc);
+        else
+          store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc, cs);
       } else if (open_row) {
         store_raw(carry_row, e0, n_dense, acc);
       }
@@ -466,17 +532,20 @@ spmm_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     const int k = queue3[q];
     const int s = k ? row_end[k - 1] : 0;
     const int e = row_end[k];
-    Pack<V> acc = pack_zero<V>();
-    accumulate<V, I, VEC, WIN>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, Bv,
+    Pack<V, ST> acc = pack_zero<V, ST>();
+    accumulate<V, I, VEC, WIN, ST>(acc, scol, sval, s, e, tid / G, n_grp, B, ldb, e0, n_dense, Bv,
                                stride16, mask_col);
     part[tid] = acc;
     __syncthreads();
     if (tid < G) {
-      Pack<V> tot = part[tid];
+      Pack<V, ST> tot = part[tid];
       for (int g = 1; g < n_grp; ++g) tot = add_pack(tot, part[g * G + tid]);
       if (k < n_end) {
         const int64_t r = tc.r0 + k;
-        store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, tot, alpha, beta, has_beta, vc);
+        if (k == 0 && first_row != nullptr)
+          store_raw(first_row, e0, n_dense, tot);
+        else
+          store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, tot, alpha, beta, has_beta, vc, cs);
       } else if (open_row) {
         store_raw(carry_row, e0, n_dense, tot);
       }
@@ -509,9 +578,10 @@ template <class V, class I, class P, int THREADS, int ITEMS, bool VEC>
 __global__ void __launch_bounds__(THREADS)
 spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
                   const P* __restrict__ ptr, const V* __restrict__ B, int64_t ldb,
-                  int64_t n_dense, const V* C_in, V* C, int64_t ldc, V* __restrict__ carry,
-                  const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t nnz, V alpha,
-                  V beta, int has_beta_i, int G, int CH, int vec_c, int32_t* status) {
+                  int64_t n_dense, const V* C_in, V* C, int64_t ldc, int64_t cs,
+                  V* __restrict__ carry, const int64_t* __restrict__ tile_row, int64_t n_rows,
+                  int64_t nnz, V alpha, V beta, int has_beta_i, int G, int CH, int vec_c,
+                  int32_t* status) {
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
   int* row_end = reinterpret_cast<int*>(smem + 16);
@@ -579,13 +649,13 @@ spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
       else
         b = pack_zero<V>();
     } else {
-      b = load_pack(B + static_cast<int64_t>(c) * ldb, e0, n_dense, false);
+      b = load_pack<V, V>(B + static_cast<int64_t>(c) * ldb, e0, n_dense, false);
     }
     return b;
   };
   auto store_row = [&](int k, const Pack<V>& acc) {
     const int64_t r = tc.r0 + k;
-    store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc);
+    store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, acc, alpha, beta, has_beta, vc, cs);
   };
 
   // rows without entries in this tile: alpha * 0 + beta * C_in, all teams in parallel
@@ -683,7 +753,7 @@ spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
 }
 
 template <class V>
-__global__ void spmm_fixup_kernel(V* C, int64_t ldc, int64_t n_dense,
+__global__ void spmm_fixup_kernel(V* C, int64_t ldc, int64_t cs, int64_t n_dense,
                                   const V* __restrict__ carry,
                                   const int64_t* __restrict__ tile_row, int64_t n_tiles,
                                   V alpha) {
@@ -697,15 +767,44 @@ __global__ void spmm_fixup_kernel(V* C, int64_t ldc, int64_t n_dense,
   while (u0 >= 1 && tile_row[u0] == r) --u0;
   V s = carry[u0 * n_dense + n];
   for (int64_t u = u0 + 1; u < t; ++u) s = s + carry[u * n_dense + n];
-  C[r * ldc + n] = C[r * ldc + n] + alpha * s;
+  C[r * ldc + n * cs] = C[r * ldc + n * cs] + alpha * s;
 }
 
-template <class V, class I, class P>
+// 16-bit storage: the pieces of the row (carries of the earlier tiles, then the piece the tile
+// it ends in left in first_part) are added in float32 and the row is rounded once.
+template <class V, class S, class P>
+__global__ void spmm_fixup_narrow_kernel(S* C, const S* C_in, int64_t ldc, int64_t cs,
+                                         int64_t n_dense,
+                                         const V* __restrict__ carry,
+                                         const V* __restrict__ first_part,
+                                         const int64_t* __restrict__ tile_row,
+                                         const P* __restrict__ ptr, int64_t n_tiles, int items,
+                                         int64_t total, V alpha, V beta, int has_beta) {
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t t = idx / n_dense;
+  const int64_t n = idx - t * n_dense;
+  if (t < 1 || t >= n_tiles) return;
+  const int64_t r = tile_row[t];
+  if (tile_row[t + 1] <= r) return;
+  int64_t d0 = t * static_cast<int64_t>(items);
+  if (d0 > total) d0 = total;
+  if (static_cast<int64_t>(ptr[r]) >= d0 - r) return;  // row r starts in tile t: written there
+  int64_t u0 = t - 1;
+  while (u0 >= 1 && tile_row[u0] == r) --u0;
+  V s = carry[u0 * n_dense + n];
+  for (int64_t u = u0 + 1; u < t; ++u) s = s + carry[u * n_dense + n];
+  s = s + first_part[t * n_dense + n];
+  V out = alpha * s;
+  if (has_beta) out = out + beta * to_acc(C_in[r * ldc + n * cs]);
+  C[r * ldc + n * cs] = storage_of<S>::from_acc(out);
+}
+
+template <class V, class I, class P, class S = V>
 int spmm_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
                 void* C, int64_t ldc, const void* alpha, const void* beta,
                 const int64_t* tile_row, void* carry, int32_t* status, cudaStream_t stream,
-                int64_t window_rows = 0, const int32_t* tile_win = nullptr) {
+                int64_t window_rows = 0, const int32_t* tile_win = nullptr, int64_t cs = 1) {
   using Cfg = SpmmCfg<V, I>;
   constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
   const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
@@ -715,21 +814,24 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   const V b = *static_cast<const V*>(beta);
   const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
   if (has_beta && C_in == nullptr) return B2S_ERR_ARG;
-  constexpr int PN = Pack<V>::N;
+  constexpr int PN = Pack<V, S>::N;
+  constexpr bool kNarrow = !std::is_same<S, V>::value;
+  V* first_part = static_cast<V*>(carry) + n_tiles * n_dense;  // 16-bit dtypes only
   // lanes per B row: enough 16-byte slices to cover N, at most a warp
   const int64_t slices = (n_dense + PN - 1) / PN;
   int G = 1;
   while (G < slices && G < 32) G <<= 1;
   const int64_t col_tiles = (slices + G - 1) / G;
   if (col_tiles > 65535) return B2S_ERR_RANGE;
-  const int vec_b = (reinterpret_cast<uintptr_t>(B) % 16 == 0) && ((ldb * sizeof(V)) % 16 == 0);
-  const int vec_c = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * sizeof(V)) % 16 == 0) &&
+  const int vec_b = (reinterpret_cast<uintptr_t>(B) % 16 == 0) && ((ldb * sizeof(S)) % 16 == 0);
+  const int vec_c = cs == 1 && (reinterpret_cast<uintptr_t>(C) % 16 == 0) &&
+                    ((ldc * sizeof(S)) % 16 == 0) &&
                     (!has_beta || reinterpret_cast<uintptr_t>(C_in) % 16 == 0);
   dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(col_tiles));
   // fast path: every pack is whole and 16-byte aligned in B, C and C_in
   const bool vec = vec_b && vec_c && (n_dense % PN == 0);
   // B spans fewer than 2^32 sixteen-byte units (64 GB): row offsets fit 32 bits
-  const int small_b = (static_cast<double>(n_cols) * static_cast<double>(ldb) * sizeof(V) / 16.0) < 4.0e9;
+  const int small_b = (static_cast<double>(n_cols) * static_cast<double>(ldb) * sizeof(S) / 16.0) < 4.0e9;
   // Two tile kernels.  Narrow rows of B (G <= 4 lanes, e.g. N = 16 float32): the chunk kernel,
   // where every team has 8 gathers in flight whatever the row lengths (measured on the 2^26-row
   // power-law matrix, N = 16: 30 ms against 40 ms).  Wider rows: the team-per-row kernel, whose
@@ -738,9 +840,35 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   // With 4-byte column indices the team-per-row kernel (12 CTAs per SM) is the faster one for
   // narrow rows too: the two pieces of the long-row split of that matrix, N = 16, take
   // 18.7 + 4.8 ms against 21.1 + 9.8 ms with the chunk kernel.
-  const bool chunked =
-      B2S_SPMM_CHUNKED == 1 || (B2S_SPMM_CHUNKED == 2 && G <= 4 && sizeof(I) == 8);
-  if (chunked) {
+  const bool chunked = !kNarrow && (B2S_SPMM_CHUNKED == 1 ||
+                                    (B2S_SPMM_CHUNKED == 2 && G <= 4 && sizeof(I) == 8));
+  if constexpr (kNarrow) {
+    // 16-bit storage: the team-per-row kernel only (no chunk kernel, no shared-memory window)
+    constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I, S>();
+    auto launch = [&](auto kern) {
+      ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem);
+      kern<<<grid, THREADS, smem, stream>>>(
+          static_cast<const S*>(data), static_cast<const I*>(indices),
+          static_cast<const P*>(indptr), static_cast<const S*>(B), ldb, n_dense,
+          static_cast<const S*>(C_in), static_cast<S*>(C), ldc, cs, static_cast<V*>(carry),
+          first_part, tile_row, n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0,
+          nullptr);
+    };
+    if (vec)
+      launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true, false, S>);
+    else
+      launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, false, false, S>);
+    if (n_tiles > 1) {
+      const int fb = 256;
+      const int64_t work = n_tiles * n_dense;
+      spmm_fixup_narrow_kernel<V, S, P><<<static_cast<unsigned>((work + fb - 1) / fb), fb, 0,
+                                          stream>>>(
+          static_cast<S*>(C), static_cast<const S*>(C_in), ldc, cs, n_dense,
+          static_cast<const V*>(carry), first_part, tile_row, static_cast<const P*>(indptr),
+          n_tiles, ITEMS, n_rows + nnz, a, b, has_beta);
+    }
+    return launch_status();
+  } else if (chunked) {
     // shorter chunks for very narrow rows: all teams busy
     const int CH = G > 4 ? B2S_SPMM_CHUNK_WIDE : (G == 4 ? 16 : 4 * G);
     const size_t smem = spmm_chunk_smem_base<ITEMS, V, I>() +
@@ -752,8 +880,8 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
       kern<<<grid, THREADS, smem, stream>>>(
           static_cast<const V*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
-          static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-          n_rows, nnz, a, b, has_beta, G, CH, vec_c, status);
+          static_cast<const V*>(C_in), static_cast<V*>(C), ldc, cs, static_cast<V*>(carry),
+          tile_row, n_rows, nnz, a, b, has_beta, G, CH, vec_c, status);
     };
     if (vec)
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, true>);
@@ -770,9 +898,9 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
     kern<<<grid, THREADS, smem, stream>>>(
         static_cast<const V*>(data), static_cast<const I*>(indices),
         static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
-        static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-        n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, static_cast<int>(window_rows),
-        tile_win);
+        static_cast<const V*>(C_in), static_cast<V*>(C), ldc, cs, static_cast<V*>(carry),
+        first_part, tile_row, n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status,
+        static_cast<int>(window_rows), tile_win);
   } else {
     constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
     auto launch = [&](auto kern) {
@@ -780,8 +908,9 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
       kern<<<grid, THREADS, smem, stream>>>(
           static_cast<const V*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
-          static_cast<const V*>(C_in), static_cast<V*>(C), ldc, static_cast<V*>(carry), tile_row,
-          n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0, nullptr);
+          static_cast<const V*>(C_in), static_cast<V*>(C), ldc, cs, static_cast<V*>(carry),
+          first_part, tile_row, n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0,
+          nullptr);
     };
     if (vec)
       launch(spmm_tile_kernel<V, I, P, THREADS, ITEMS, true>);
@@ -792,7 +921,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
     const int fb = 256;
     const int64_t work = n_tiles * n_dense;
     spmm_fixup_kernel<V><<<static_cast<unsigned>((work + fb - 1) / fb), fb, 0, stream>>>(
-        static_cast<V*>(C), ldc, n_dense, static_cast<const V*>(carry), tile_row, n_tiles, a);
+        static_cast<V*>(C), ldc, cs, n_dense, static_cast<const V*>(carry), tile_row, n_tiles, a);
   }
   return launch_status();
 }
@@ -881,7 +1010,7 @@ static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* da
                         int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
                         const void* alpha, const void* beta, const int64_t* tile_row_dev,
                         void* carry_dev, int32_t* status_dev, b2s_stream stream,
-                        int64_t window_rows, const int32_t* tile_win_dev);
+                        int64_t window_rows, const int32_t* tile_win_dev, int64_t c_col_stride);
 
 extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void* data_dev,
                             const void* indices_dev, const void* indptr_dev, int64_t n_rows,
@@ -891,7 +1020,7 @@ extern "C" int b2s_spmm_csr(int val_type, int idx_type, int ptr_type, const void
                             void* carry_dev, int32_t* status_dev, b2s_stream stream) {
   return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
                       n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, alpha, beta,
-                      tile_row_dev, carry_dev, status_dev, stream, 0, nullptr);
+                      tile_row_dev, carry_dev, status_dev, stream, 0, nullptr, 1);
 }
 
 extern "C" int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
@@ -907,7 +1036,22 @@ extern "C" int b2s_spmm_csr_windowed(int val_type, int idx_type, int ptr_type,
   if (window_rows > 0 && !tile_win_dev) return B2S_ERR_ARG;
   return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
                       n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, alpha, beta,
-                      tile_row_dev, carry_dev, status_dev, stream, window_rows, tile_win_dev);
+                      tile_row_dev, carry_dev, status_dev, stream, window_rows, tile_win_dev, 1);
+}
+
+extern "C" int b2s_spmm_csr_colmajor_c(int val_type, int idx_type, int ptr_type,
+                                       const void* data_dev, const void* indices_dev,
+                                       const void* indptr_dev, int64_t n_rows, int64_t n_cols,
+                                       int64_t nnz, const void* B_dev, int64_t ldb,
+                                       int64_t n_dense, const void* C_in_dev, void* C_dev,
+                                       int64_t ldc_col, const void* alpha, const void* beta,
+                                       const int64_t* tile_row_dev, void* carry_dev,
+                                       int32_t* status_dev, b2s_stream stream) {
+  if (ldc_col < n_rows) return B2S_ERR_ARG;
+  // element (r, n) of C at r + n * ldc_col: row stride 1, column stride ldc_col
+  return spmm_csr_any(val_type, idx_type, ptr_type, data_dev, indices_dev, indptr_dev, n_rows,
+                      n_cols, nnz, B_dev, ldb, n_dense, C_in_dev, C_dev, 1, alpha, beta,
+                      tile_row_dev, carry_dev, status_dev, stream, 0, nullptr, ldc_col);
 }
 
 static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* data_dev,
@@ -916,10 +1060,10 @@ static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* da
                         int64_t n_dense, const void* C_in_dev, void* C_dev, int64_t ldc,
                         const void* alpha, const void* beta, const int64_t* tile_row_dev,
                         void* carry_dev, int32_t* status_dev, b2s_stream stream,
-                        int64_t window_rows, const int32_t* tile_win_dev) {
+                        int64_t window_rows, const int32_t* tile_win_dev, int64_t c_col_stride) {
   if (n_rows < 0 || n_cols < 0 || nnz < 0 || n_dense < 0 || !alpha || !beta) return B2S_ERR_ARG;
   if (n_rows == 0 || n_dense == 0) return B2S_OK;
-  if (ldb < n_dense || ldc < n_dense) return B2S_ERR_ARG;
+  if (ldb < n_dense || (c_col_stride == 1 && ldc < n_dense)) return B2S_ERR_ARG;
   if (!indptr_dev || !C_dev || !tile_row_dev || !carry_dev) return B2S_ERR_ARG;
   if (nnz > 0 && (!data_dev || !indices_dev || !B_dev)) return B2S_ERR_ARG;
   const size_t vs = b2s::vsize(val_type);
@@ -927,13 +1071,14 @@ static int spmm_csr_any(int val_type, int idx_type, int ptr_type, const void* da
   const uintptr_t m = vs - 1;
   if ((reinterpret_cast<uintptr_t>(data_dev) & m) || (reinterpret_cast<uintptr_t>(B_dev) & m) ||
       (reinterpret_cast<uintptr_t>(C_dev) & m) || (reinterpret_cast<uintptr_t>(C_in_dev) & m) ||
-      (reinterpret_cast<uintptr_t>(carry_dev) & m))
+      (reinterpret_cast<uintptr_t>(carry_dev) & (b2s::acc_size(val_type) - 1)))
     return B2S_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
-    return (b2s::spmm_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, B_dev, ldb,
+  B2S_DISPATCH_VS(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
+    return (b2s::spmm_launch<V, I, P, S>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, B_dev, ldb,
                                       n_dense, C_in_dev, C_dev, ldc, alpha, beta, tile_row_dev,
-                                      carry_dev, status_dev, s, window_rows, tile_win_dev));
+                                      carry_dev, status_dev, s, window_rows, tile_win_dev,
+                                      c_col_stride));
   })));
   return B2S_ERR_DTYPE;
 }

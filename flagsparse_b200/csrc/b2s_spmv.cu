@@ -20,6 +20,7 @@
 // Matrices whose x does not fit L2 are multiplied from a column-panel layout by the kernels of
 // b2s_spmv_stack.cu; the combine kernels at the end of this file add the per-panel partials.
 #include <mutex>
+#include <type_traits>
 
 #include "b2s_tile.cuh"
 
@@ -86,14 +87,20 @@ __device__ inline void load_run(const T* p, T (&out)[N], int lo, int hi, uint64_
   memcpy(out, w, BYTES);
 }
 
-template <class V, class I, class P>
+// S: storage type of val, x and y (V itself, or a 16-bit float type with V = float).  With a
+// 16-bit S the last piece of a row that began in an earlier tile is not written to y but left,
+// unrounded, in first_part[t]; the fix-up adds it to the carries and rounds the row once.
+template <class V, class I, class P, class S = V>
 __global__ void __launch_bounds__(SpmvShape<V>::THREADS, spmv_min_blocks<V, I>())
-spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
-                 const V* __restrict__ x, const V* y_in, V* y, V* __restrict__ carry,
-                 const int64_t* __restrict__ tile_row, int64_t n_rows, int64_t n_cols,
-                 int64_t nnz, V alpha, V beta, int has_beta, int phase, int32_t* status) {
-  using S = SpmvShape<V>;
-  constexpr int THREADS = S::THREADS, SPT = S::SPT, SLOTS = S::SLOTS, ITEMS = S::ITEMS;
+spmv_tile_kernel(const S* __restrict__ val, const I* __restrict__ col, const P* __restrict__ ptr,
+                 const S* __restrict__ x, const S* y_in, S* y, V* __restrict__ carry,
+                 V* __restrict__ first_part, const int64_t* __restrict__ tile_row,
+                 int64_t n_rows, int64_t n_cols, int64_t nnz, V alpha, V beta, int has_beta,
+                 int phase, int32_t* status) {
+  constexpr bool kNarrow = !std::is_same<S, V>::value;
+  using Shape = SpmvShape<V>;
+  constexpr int THREADS = Shape::THREADS, SPT = Shape::SPT, SLOTS = Shape::SLOTS;
+  constexpr int ITEMS = Shape::ITEMS;
   constexpr int WARPS = THREADS / 32;
   __shared__ uint32_t head[SLOTS / 32];
   __shared__ __align__(16) unsigned char seg_raw[sizeof(V) * SLOTS];
@@ -124,24 +131,29 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
   // ---- col / val of this thread's slots, and the first row end, all in flight together --------
   I c[SPT];
   V v[SPT];
+  {
+    S vs[SPT];  // as stored
 #pragma unroll
-  for (int i = 0; i < SPT; ++i) {
-    c[i] = 0;
-    v[i] = vt<V>::zero();
-  }
-  if (live) {
-    if (phase >= 0) {
-      const uint64_t once = policy_evict_first();
-      load_run(col + jt, c, lo, hi, once);
-      load_run(val + jt, v, lo, hi, once);
-    } else {
-#pragma unroll
-      for (int i = 0; i < SPT; ++i)
-        if (i >= lo && i < hi) {
-          c[i] = col[jt + i];
-          v[i] = val[jt + i];
-        }
+    for (int i = 0; i < SPT; ++i) {
+      c[i] = 0;
+      vs[i] = storage_of<S>::from_acc(vt<V>::zero());
     }
+    if (live) {
+      if (phase >= 0) {
+        const uint64_t once = policy_evict_first();
+        load_run(col + jt, c, lo, hi, once);
+        load_run(val + jt, vs, lo, hi, once);
+      } else {
+#pragma unroll
+        for (int i = 0; i < SPT; ++i)
+          if (i >= lo && i < hi) {
+            c[i] = col[jt + i];
+            vs[i] = val[jt + i];
+          }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) v[i] = to_acc(vs[i]);
   }
   int64_t e_first = 0;
   if (tid < n_end) e_first = static_cast<int64_t>(ptr[tc.r0 + 1 + tid]);
@@ -160,7 +172,7 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
         continue;
       }
 #endif
-      xv[i] = ldg_val(x + static_cast<int64_t>(c[i]));
+      xv[i] = to_acc(ldg_val(x + static_cast<int64_t>(c[i])));
     }
   }
 
@@ -244,9 +256,13 @@ spmv_tile_kernel(const V* __restrict__ val, const I* __restrict__ col, const P* 
     if (e < a || e > a + n_nz) continue;
 #endif
     const V sum = e > s ? seg_at[e] : vt<V>::zero();
+    if (kNarrow && k == 0 && s64 < a) {  // began in an earlier tile: rounded by the fix-up
+      first_part[t] = sum;
+      continue;
+    }
     V r = alpha * sum;
-    if (has_beta) r = r + beta * y_in[tc.r0 + k];
-    y[tc.r0 + k] = r;
+    if (has_beta) r = r + beta * to_acc(y_in[tc.r0 + k]);
+    y[tc.r0 + k] = storage_of<S>::from_acc(r);
   }
   if (tid == 0 && tc.r1 < n_rows) {  // the row still open at the end of the tile
     const int64_t s64 = static_cast<int64_t>(ptr[tc.r1]) - jb;
@@ -273,42 +289,77 @@ __global__ void spmv_fixup_kernel(V* y, const V* __restrict__ carry,
   y[r] = y[r] + alpha * s;
 }
 
+// The same for 16-bit storage: the row's pieces (carries of the earlier tiles, then the piece
+// the tile it ends in has left in first_part) are added in float32 and the row is rounded once.
+template <class V, class S, class P>
+__global__ void spmv_fixup_narrow_kernel(S* y, const S* y_in, const V* __restrict__ carry,
+                                         const V* __restrict__ first_part,
+                                         const int64_t* __restrict__ tile_row,
+                                         const P* __restrict__ ptr, int64_t n_tiles, int items,
+                                         int64_t total, V alpha, V beta, int has_beta) {
+  const int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (t < 1 || t >= n_tiles) return;
+  const int64_t r = tile_row[t];
+  if (tile_row[t + 1] <= r) return;  // row r does not end in tile t
+  int64_t d0 = t * static_cast<int64_t>(items);
+  if (d0 > total) d0 = total;
+  if (static_cast<int64_t>(ptr[r]) >= d0 - r) return;  // row r starts in tile t: written there
+  int64_t u0 = t - 1;
+  while (u0 >= 1 && tile_row[u0] == r) --u0;
+  V s = carry[u0];
+  for (int64_t u = u0 + 1; u < t; ++u) s = s + carry[u];
+  s = s + first_part[t];
+  V out = alpha * s;
+  if (has_beta) out = out + beta * to_acc(y_in[r]);
+  y[r] = storage_of<S>::from_acc(out);
+}
+
 // Element offset of the two arrays from a common vector boundary, or -1 when they have
 // none (then the kernel reads element by element).  Slices taken at the same element offset of
 // two aligned allocations, as a row block of a larger matrix is, do have one.
-template <class V, class I>
+template <class V, class I, class S>
 int spmv_vector_phase(const void* data, const void* indices) {
   constexpr int SPT = SpmvShape<V>::SPT;
   const uintptr_t d = reinterpret_cast<uintptr_t>(data), c = reinterpret_cast<uintptr_t>(indices);
-  if (d % sizeof(V) || c % sizeof(I)) return -1;
-  constexpr uintptr_t vb = run_chunk_bytes<V, SPT>(), cb = run_chunk_bytes<I, SPT>();
+  if (d % sizeof(S) || c % sizeof(I)) return -1;
+  constexpr uintptr_t vb = run_chunk_bytes<S, SPT>(), cb = run_chunk_bytes<I, SPT>();
   for (int o = 0; o < SPT; ++o)
-    if ((d - o * sizeof(V)) % vb == 0 && (c - o * sizeof(I)) % cb == 0) return o;
+    if ((d - o * sizeof(S)) % vb == 0 && (c - o * sizeof(I)) % cb == 0) return o;
   return -1;
 }
 
-template <class V, class I, class P>
+template <class V, class I, class P, class S = V>
 int spmv_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* x, const void* y_in, void* y, const void* alpha,
                 const void* beta, const int64_t* tile_row, void* carry, int32_t* status,
                 cudaStream_t stream) {
-  using S = SpmvShape<V>;
-  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, S::ITEMS);
+  using Shape = SpmvShape<V>;
+  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, Shape::ITEMS);
   if (n_tiles == 0) return B2S_OK;
   if (n_tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
   const V a = *static_cast<const V*>(alpha);
   const V b = *static_cast<const V*>(beta);
   const int has_beta = vt<V>::is_zero(b) ? 0 : 1;
   if (has_beta && y_in == nullptr) return B2S_ERR_ARG;
-  const int phase = nnz > 0 ? spmv_vector_phase<V, I>(data, indices) : 0;
-  spmv_tile_kernel<V, I, P><<<static_cast<unsigned>(n_tiles), S::THREADS, 0, stream>>>(
-      static_cast<const V*>(data), static_cast<const I*>(indices), static_cast<const P*>(indptr),
-      static_cast<const V*>(x), static_cast<const V*>(y_in), static_cast<V*>(y),
-      static_cast<V*>(carry), tile_row, n_rows, n_cols, nnz, a, b, has_beta, phase, status);
+  const int phase = nnz > 0 ? spmv_vector_phase<V, I, S>(data, indices) : 0;
+  V* first_part = static_cast<V*>(carry) + n_tiles;  // used by the 16-bit dtypes only
+  spmv_tile_kernel<V, I, P, S><<<static_cast<unsigned>(n_tiles), Shape::THREADS, 0, stream>>>(
+      static_cast<const S*>(data), static_cast<const I*>(indices), static_cast<const P*>(indptr),
+      static_cast<const S*>(x), static_cast<const S*>(y_in), static_cast<S*>(y),
+      static_cast<V*>(carry), first_part, tile_row, n_rows, n_cols, nnz, a, b, has_beta, phase,
+      status);
   if (n_tiles > 1) {
     const int fb = 256;
-    spmv_fixup_kernel<V><<<static_cast<unsigned>((n_tiles + fb - 1) / fb), fb, 0, stream>>>(
-        static_cast<V*>(y), static_cast<const V*>(carry), tile_row, n_tiles, a);
+    const unsigned grid = static_cast<unsigned>((n_tiles + fb - 1) / fb);
+    if constexpr (std::is_same<S, V>::value)
+      spmv_fixup_kernel<V><<<grid, fb, 0, stream>>>(static_cast<V*>(y),
+                                                    static_cast<const V*>(carry), tile_row,
+                                                    n_tiles, a);
+    else
+      spmv_fixup_narrow_kernel<V, S, P><<<grid, fb, 0, stream>>>(
+          static_cast<S*>(y), static_cast<const S*>(y_in), static_cast<const V*>(carry),
+          first_part, tile_row, static_cast<const P*>(indptr), n_tiles, Shape::ITEMS,
+          n_rows + nnz, a, b, has_beta);
   }
   return launch_status();
 }
@@ -397,7 +448,10 @@ __global__ void peer_scatter_kernel(const uint4* __restrict__ src, int64_t n16, 
 
 extern "C" int b2s_spmv_tile_items(int val_type, int idx_type) {
   (void)idx_type;
-  B2S_DISPATCH_V(val_type, { return b2s::SpmvShape<V>::ITEMS; });
+  B2S_DISPATCH_VS(val_type, {
+    (void)sizeof(S);
+    return b2s::SpmvShape<V>::ITEMS;
+  });
   return 0;
 }
 
@@ -514,11 +568,11 @@ extern "C" int b2s_spmv_csr(int val_type, int idx_type, int ptr_type, const void
   const uintptr_t m = vs - 1;
   if ((reinterpret_cast<uintptr_t>(data_dev) & m) || (reinterpret_cast<uintptr_t>(x_dev) & m) ||
       (reinterpret_cast<uintptr_t>(y_dev) & m) || (reinterpret_cast<uintptr_t>(y_in_dev) & m) ||
-      (reinterpret_cast<uintptr_t>(carry_dev) & m))
+      (reinterpret_cast<uintptr_t>(carry_dev) & (b2s::acc_size(val_type) - 1)))
     return B2S_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
-    return (b2s::spmv_launch<V, I, P>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, x_dev,
+  B2S_DISPATCH_VS(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
+    return (b2s::spmv_launch<V, I, P, S>(data_dev, indices_dev, indptr_dev, n_rows, n_cols, nnz, x_dev,
                                       y_in_dev, y_dev, alpha, beta, tile_row_dev, carry_dev,
                                       status_dev, s));
   })));

@@ -433,7 +433,7 @@ static int panel_build_any(int val_type, int idx_type, int ptr_type, const void*
     return B2S_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool wide = b2s::wide_needed(n_cols, nnz);
-  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P,
+  B2S_DISPATCH_MOVE(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P,
       B2S_DISPATCH_I(p_ptr_type, PP, {
     if (wide)
       return (b2s::panel_build_run<V, I, P, PP, uint64_t>(
@@ -496,7 +496,7 @@ extern "C" int b2s_csr2csc(int val_type, int idx_type, int ptr_type, const void*
   if (!data_dev || !indices_dev || !t_data_dev || !t_indices_dev || !scratch_dev)
     return B2S_ERR_ARG;
   const bool wide = b2s::wide_needed(n_cols, nnz);
-  B2S_DISPATCH_V(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
+  B2S_DISPATCH_MOVE(val_type, B2S_DISPATCH_I(idx_type, I, B2S_DISPATCH_I(ptr_type, P, {
     if (wide)
       return (b2s::csr2csc_run<V, I, P, uint64_t>(data_dev, indices_dev, indptr_dev, n_rows,
                                                   n_cols, nnz, conj, t_data_dev, t_indices_dev,
@@ -559,11 +559,14 @@ extern "C" int b2s_dense_transpose(int elem_bytes, const void* src_dev, int64_t 
   if (rows < 0 || cols < 0 || ld_src < cols || ld_dst < rows) return B2S_ERR_ARG;
   if (rows == 0 || cols == 0) return B2S_OK;
   if (!src_dev || !dst_dev) return B2S_ERR_ARG;
-  if (elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16) return B2S_ERR_DTYPE;
+  if (elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16)
+    return B2S_ERR_DTYPE;
   const uintptr_t both =
       reinterpret_cast<uintptr_t>(src_dev) | reinterpret_cast<uintptr_t>(dst_dev);
   if (both % static_cast<uintptr_t>(elem_bytes)) return B2S_ERR_ALIGNMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (elem_bytes == 2)
+    return b2s::dense_transpose_launch<uint16_t>(src_dev, rows, cols, ld_src, dst_dev, ld_dst, s);
   if (elem_bytes == 4)
     return b2s::dense_transpose_launch<uint32_t>(src_dev, rows, cols, ld_src, dst_dev, ld_dst, s);
   if (elem_bytes == 8)

@@ -16,8 +16,9 @@ import time
 
 import torch
 
-from . import _half, _lib
+from . import _lib
 from ._contract import (
+    ALL_VALUE_DTYPES,
     INDEX_LIMIT_INT32,
     OP_CONJ_TRANS,
     SUPPORTED_INDEX_DTYPES,
@@ -112,7 +113,7 @@ def _checked_spmm_plan(data, indices, indptr, shape):
         raise ValueError("data, indices, and indptr must be CUDA tensors")
     if not all(t.device == data.device for t in (indices, indptr)):
         raise ValueError("data, indices, and indptr must be on the same CUDA device")
-    if data.dtype not in SUPPORTED_SPMM_VALUE_DTYPES:
+    if data.dtype not in ALL_VALUE_DTYPES:
         raise TypeError(
             "data dtype must be one of: float16, bfloat16, float32, float64, complex64, "
             "complex128")
@@ -180,13 +181,41 @@ def _launch_spmm(plan: CsrPlan, B, C, C_in, alpha, beta):
     _lib.check(st, "b2s_spmm_rows_combine")
 
 
+def _launch_spmm_colmajor_c(plan: CsrPlan, B, C):
+    """Enqueue C = A B with C column-major (strides (1, ldc_col)): the kernel stores column-major
+    itself (b2s_spmm_csr_colmajor_c).  Returns False, having done nothing, when the matrix runs
+    with its long rows split off (that route combines row-major partials); the caller then
+    takes the row-major product and transposes it."""
+    n_dense = int(B.shape[1])
+    if plan.long_row_split(n_dense * B.element_size()) is not None:
+        return False
+    lib = _lib.load()
+    items = lib.b2s_spmm_tile_items(plan.vcode, plan.icode)
+    n_tiles, tile_row = plan.tiles(items)
+    carry = plan.carry_on("spmm_carry", n_tiles * n_dense,
+                          torch.cuda.current_stream(plan.device).cuda_stream)
+    dtype = plan.data.dtype
+    a, b = _lib.scalar_buffer(1.0, dtype), _lib.scalar_buffer(0.0, dtype)
+    with torch.cuda.device(plan.device):
+        st = lib.b2s_spmm_csr_colmajor_c(
+            plan.vcode, plan.icode, plan.pcode,
+            _lib.ptr(plan.data), _lib.ptr(plan.indices), _lib.ptr(plan.indptr),
+            plan.n_rows, plan.n_cols, plan.nnz, _lib.ptr(B), int(B.stride(0)), n_dense,
+            None, _lib.ptr(C), int(C.stride(1)), a, b, _lib.ptr(tile_row), _lib.ptr(carry),
+            _lib.ptr(plan.status), _lib.stream_handle(plan.device))
+    _lib.check(st, "b2s_spmm_csr_colmajor_c")
+    plan.note_launch()
+    return True
+
+
 def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
     """One b2s_spmm_csr launch for the matrix of `plan` as it is."""
     lib = _lib.load()
     n_dense = int(B.shape[1])
     items = lib.b2s_spmm_tile_items(plan.vcode, plan.icode)
     n_tiles, tile_row = plan.tiles(items)
-    carry = plan.scratch("spmm_carry", n_tiles * n_dense)
+    carry = plan.carry_on("spmm_carry", n_tiles * n_dense,
+                          torch.cuda.current_stream(plan.device).cuda_stream)
     dtype = plan.data.dtype
     a = _lib.scalar_buffer(alpha, dtype)
     b = _lib.scalar_buffer(beta, dtype)
@@ -237,15 +266,6 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
     if max_segments is not None and max_segments <= 0:
         raise ValueError("max_segments must be positive when provided")
 
-    # float16 / bfloat16: B and out are the caller's 16-bit tensors, the product is float32
-    half = data.dtype if _half.is_half(data) else None
-    half_out = None
-    if half is not None:
-        data = _half.widened_values(data)
-        if torch.is_tensor(B):
-            if B.dtype != half:
-                raise TypeError("B dtype must match data dtype")
-            B = B.to(torch.float32)
     plan = _checked_spmm_plan(data, indices, indptr, shape)
     if B.ndim != 2:
         raise ValueError("B must be a 2D dense tensor")
@@ -266,10 +286,6 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
     alpha = check_scalar(alpha, dtype, "alpha")
     beta = check_scalar(beta, dtype, "beta")
 
-    if half is not None and torch.is_tensor(out):
-        if out.shape != (eff_rows, n_dense) or out.dtype != half:
-            raise ValueError("out shape/dtype must match result")
-        half_out, out = out, (out.to(torch.float32) if beta != 0 else None)
     if out is not None:
         if not out.is_cuda:
             raise ValueError("out must be a CUDA tensor")
@@ -323,8 +339,6 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
         out.copy_(C)
     if out is not None:
         C = out
-    if half is not None:
-        C = _half.narrow_result(C, half, half_out)
     if do_timing:
         torch.cuda.synchronize()
         t2 = time.perf_counter()

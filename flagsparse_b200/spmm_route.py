@@ -20,9 +20,11 @@ from __future__ import annotations
 
 import torch
 
-from . import _half, _lib
+from . import _lib
+from ._contract import HALF_VALUE_DTYPES
 from ._contract import OP_CONJ_TRANS, is_complex, normalize_op, op_name, op_transposes
-from .spmm import SUPPORTED_SPMM_VALUE_DTYPES, _checked_spmm_plan, _launch_spmm, _row_major_ok
+from .spmm import (SUPPORTED_SPMM_VALUE_DTYPES, _checked_spmm_plan, _launch_spmm,
+                   _launch_spmm_colmajor_c, _row_major_ok)
 
 
 class SpmmCsrAlgorithmUnavailable(RuntimeError):
@@ -32,7 +34,7 @@ class SpmmCsrAlgorithmUnavailable(RuntimeError):
 # name -> (display name, value dtypes the reference registers the route for)
 _REAL = (torch.float32, torch.float64)
 SPMM_CSR_ALGORITHMS = {
-    "csr_base": ("Base", _half.HALF_VALUE_DTYPES + SUPPORTED_SPMM_VALUE_DTYPES),
+    "csr_base": ("Base", HALF_VALUE_DTYPES + SUPPORTED_SPMM_VALUE_DTYPES),
     "alpha_alg1_tle_opt": ("TLEOpt", _REAL),
     "alpha_alg1_tle_opt2": ("TLEOpt2", _REAL),
     "spmm_csr_alg1": ("Alg1", _REAL),
@@ -150,8 +152,6 @@ def prepare_spmm_csr_route(data, indices, indptr, shape, *, op="non", alg="auto"
     return the handle for ``flagsparse_spmm_csr_run``."""
     name = op_name(normalize_op(op))
     value_dtype = data.dtype if torch.is_tensor(data) else None
-    if _half.is_half(data):
-        data = _half.widened_values(data)
     plan = _checked_spmm_plan(data, indices, indptr, shape)
     resolved = _normalize_spmm_csr_alg(alg)
     if resolved != "auto":
@@ -198,8 +198,6 @@ def flagsparse_spmm_csr_run(prepared, B, *, alg=None, op=None, dense_layout="aut
         raise ValueError("B must be on the same CUDA device as sparse matrix data")
     if B.dtype != value_dtype:
         raise TypeError("B dtype must match sparse matrix dtype")
-    if value_dtype != dtype:
-        B = B.to(dtype)  # float16 / bfloat16 operand, float32 product
 
     want_ms = bool(return_time or return_meta)
     if want_ms:
@@ -255,18 +253,17 @@ def flagsparse_spmm_csr_run(prepared, B, *, alg=None, op=None, dense_layout="aut
                     _transpose_dense(B, n_dense, n_inner, int(B.stride(1)), B_run, n_dense)
             else:
                 B_run = B.contiguous()
-            C_row = torch.empty((n_rows, n_dense), dtype=dtype, device=device)
-            _launch_spmm(plan, B_run, C_row, None, 1.0, 0.0)
-            with torch.cuda.device(device):
-                _transpose_dense(C_row, n_rows, n_dense, n_dense, C, int(C.stride(1)))
+            if not _launch_spmm_colmajor_c(plan, B_run, C):
+                C_row = torch.empty((n_rows, n_dense), dtype=dtype, device=device)
+                _launch_spmm(plan, B_run, C_row, None, 1.0, 0.0)
+                with torch.cuda.device(device):
+                    _transpose_dense(C_row, n_rows, n_dense, n_dense, C, int(C.stride(1)))
     compute_ms = None
     if timing:
         c1.record()
         torch.cuda.synchronize()
         compute_ms = c0.elapsed_time(c1)
 
-    if value_dtype != dtype:
-        C = C.to(value_dtype)  # keeps the strides of a column-major C
     gpu_ms = None
     process_cpu_ms = 0.0
     if want_ms:

@@ -20,8 +20,9 @@ import time
 
 import torch
 
-from . import _half, _lib
+from . import _half, _lib  # noqa: F401 - _half documents the 16-bit dtypes
 from ._contract import (
+    ALL_VALUE_DTYPES,
     INDEX_LIMIT_INT32,
     OP_CONJ_TRANS,
     OP_NON,
@@ -88,7 +89,7 @@ def _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy="auto
         raise ValueError("data, indices, indptr must be CUDA tensors")
     if not all(t.device == data.device for t in (indices, indptr)):
         raise ValueError("data, indices, indptr must be on the same CUDA device")
-    if data.dtype not in SUPPORTED_SPMV_VALUE_DTYPES:
+    if data.dtype not in ALL_VALUE_DTYPES:
         raise TypeError(_spmv_dtype_error_message())
     if indices.dtype not in SUPPORTED_INDEX_DTYPES:
         raise TypeError("indices dtype must be torch.int32 or torch.int64")
@@ -194,8 +195,6 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
     if op is not None and bool(transpose) and op_code == OP_NON:
         raise ValueError("transpose=True conflicts with op=non")
     value_dtype = data.dtype if torch.is_tensor(data) else None
-    if _half.is_half(data):
-        data = _half.widened_values(data)
     base_plan = _checked_spmv_plan(data, indices, indptr, shape, index_fallback_policy)
     memo_key = (op_code, block_nnz, max_segments, index_fallback_policy)
     memo = base_plan._prepared.get(memo_key)
@@ -324,7 +323,7 @@ def _enqueue_spmv(plan, rec, x, y, y_in, a, b, stream):
     lib = _lib.load()
     if rec[0] == "csr":
         _, fn, head, tile_row_p, n_tiles = rec
-        carry = plan.scratch_on("spmv_carry", n_tiles, stream)
+        carry = plan.carry_on("spmv_carry", n_tiles, stream)
         st = fn(*head, _lib.ptr(x), _lib.ptr(y_in), _lib.ptr(y), a, b, tile_row_p,
                 _lib.ptr(carry), _lib.ptr(plan.status), stream)
         if st:
@@ -531,19 +530,6 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
     dtype = prepared.data.dtype
     alpha = check_scalar(alpha, dtype, "alpha")
     beta = check_scalar(beta, dtype, "beta")
-    half = getattr(prepared, "value_dtype", dtype)
-    half = half if half in _half.HALF_VALUE_DTYPES else None
-    half_out = None
-    if half is not None:
-        # float16 / bfloat16: x and out are the caller's 16-bit tensors, the product is float32
-        if torch.is_tensor(x):
-            if x.dtype != half:
-                raise TypeError("x dtype must match sparse matrix dtype")
-            x = x.to(torch.float32)
-        if torch.is_tensor(out):
-            if out.shape != (prepared.n_rows,) or out.dtype != half:
-                raise ValueError("out shape/dtype must match result")
-            half_out, out = out, (out.to(torch.float32) if beta != 0 else None)
     x = _validate_spmv_x(x, prepared)
     if out is not None:
         if not torch.is_tensor(out) or not out.is_cuda:
@@ -565,8 +551,6 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
         t1 = time.perf_counter()
     y = _run_spmv_prepared_with_fallback(prepared, x, use_opt=use_opt, out=out, alpha=alpha,
                                          beta=beta)
-    if half is not None:
-        y = _half.narrow_result(y, half, half_out)
     if do_timing:
         torch.cuda.synchronize()
         t2 = time.perf_counter()

@@ -41,8 +41,14 @@ typedef enum {
                              access was skipped                                       */
 } b2s_status;
 
-/* value dtypes (order follows FlagSparse's SUPPORTED_VALUE_DTYPES, _common.py:21-29) */
-typedef enum { B2S_F32 = 0, B2S_F64 = 1, B2S_C64 = 2, B2S_C128 = 3 } b2s_vtype;
+/* value dtypes (FlagSparse's SUPPORTED_VALUE_DTYPES, _common.py:21-29).  B2S_F16 / B2S_BF16:
+ * the matrix values AND the dense operand AND the result are 16-bit arrays; every sum is a
+ * float32 sum and the result is rounded once, the arithmetic FlagSparse's launchers do for these
+ * dtypes (spmv_csr.py:124-129, spmm_csr.py:2716-2719) without its float32 copies; alpha / beta
+ * then point at float32 scalars.  Accepted by b2s_spmv_csr, b2s_spmm_csr and b2s_csr2csc. */
+typedef enum {
+  B2S_F32 = 0, B2S_F64 = 1, B2S_C64 = 2, B2S_C128 = 3, B2S_F16 = 4, B2S_BF16 = 5
+} b2s_vtype;
 /* index dtypes (SUPPORTED_INDEX_DTYPES, _common.py:30) */
 typedef enum { B2S_I32 = 0, B2S_I64 = 1 } b2s_itype;
 
@@ -92,7 +98,10 @@ int b2s_spmm_tile_items(int val_type, int idx_type);
  * _spmv_csr_complex_kernel (:196-227) and the bucketed kernels (:234-351) with their launchers
  * (:412-461, :679-723).  One launch of the tile kernel plus one launch of the carry fix-up.
  *   y_in_dev  may be NULL when *beta == 0, and may equal y_dev;
- *   carry_dev scratch of T values (T = b2s_tile_count(..., b2s_spmv_tile_items(...)));
+ *   carry_dev scratch of T values (T = b2s_tile_count(..., b2s_spmv_tile_items(...))); for the
+ *             16-bit dtypes 2 T float32 values (the second half holds the last piece of every
+ *             row that crosses a tile border, so that such a row is rounded once, after all
+ *             of its pieces have been added in float32);
  *   status_dev one int32 the kernels OR error bits into (B2S_ERR_TIMEOUT); may be NULL.
  * The result is bit-identical from run to run: no floating-point atomics, fixed reduction trees.
  */
@@ -245,7 +254,7 @@ int b2s_panel_combine_peers(int val_type, const void* ypart_dev, const int32_t* 
                             int grid_limit, b2s_stream stream);
 
 /* ---- dense transpose ---------------------------------------------------------------------------
- * dst[c * ld_dst + r] = src[r * ld_src + c] for a rows x cols matrix of 4-, 8- or 16-byte
+ * dst[c * ld_dst + r] = src[r * ld_src + c] for a rows x cols matrix of 2-, 4-, 8- or 16-byte
  * elements.  Serves dense_layout="col" of the prepared SpMM route (_run_spmm_csr_base_route,
  * spmm_csr.py:713-788, with _materialize_dense_layout :617-627): a column-major B is turned
  * into the row-major operand the SpMM kernel gathers whole rows from, and the row-major result
@@ -259,7 +268,8 @@ int b2s_dense_transpose(int elem_bytes, const void* src_dev, int64_t rows, int64
  * C (n_rows x n_dense, leading dimension ldc) row-major.  Replaces _spmm_csr_real_kernel
  * (spmm_csr.py:135-176), _spmm_csr_complex_kernel (:181-237) and _triton_spmm_csr_impl
  * (:2684-2789).  carry_dev: scratch of T * n_dense values with
- * T = b2s_tile_count(..., b2s_spmm_tile_items(...)).
+ * T = b2s_tile_count(..., b2s_spmm_tile_items(...)); for B2S_F16 / B2S_BF16 2 * T * n_dense
+ * float32 values (see b2s_spmv_csr) -- with those dtypes a lane owns eight columns of a row.
  */
 int b2s_spmm_csr(int val_type, int idx_type, int ptr_type,
                  const void* data_dev, const void* indices_dev, const void* indptr_dev,
@@ -269,6 +279,21 @@ int b2s_spmm_csr(int val_type, int idx_type, int ptr_type,
                  const void* alpha, const void* beta,
                  const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
                  b2s_stream stream);
+
+/* The same product with C (and C_in) column-major: element (r, n) at r + n * ldc_col
+ * (ldc_col >= n_rows).  Serves dense_layout="col" of the prepared route
+ * (_run_spmm_csr_base_route, spmm_csr.py:713-788, which hands its kernel the strides of C): the
+ * kernel stores each value of a row by itself (the 16-byte store of the row-major case does
+ * not apply), rows handled by neighbouring lane groups being neighbours in memory.  B is read
+ * row-major as always. */
+int b2s_spmm_csr_colmajor_c(int val_type, int idx_type, int ptr_type,
+                            const void* data_dev, const void* indices_dev,
+                            const void* indptr_dev, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                            const void* B_dev, int64_t ldb, int64_t n_dense,
+                            const void* C_in_dev, void* C_dev, int64_t ldc_col,
+                            const void* alpha, const void* beta,
+                            const int64_t* tile_row_dev, void* carry_dev, int32_t* status_dev,
+                            b2s_stream stream);
 
 /* Banded / local matrices (no counterpart in the reference).  When the columns of every tile of
  * tile_items merge items lie within a narrow span, the rows of B a tile needs are one contiguous

@@ -1,8 +1,9 @@
 """float16 / bfloat16 values (FlagSparse lists both, _common.py:21-29, and computes them in
-float32: spmv_csr.py:124-129, spmm_csr.py:2716-2719).  The result must be the float32 product of
-the widened operands rounded once to the 16-bit dtype: bit-identical to rounding this package's
-own float32 result, and within the reference's tolerance for the dtype
-(tests/pytest/accuracy_utils.py:24-26: 1e-3 for float16, 0.016 for bfloat16) of the oracle."""
+float32: spmv_csr.py:124-129, spmm_csr.py:2716-2719).  The kernels read the 16-bit arrays
+themselves; the result must be the float32 product of the widened operands rounded once to the
+16-bit dtype: bit-identical to rounding this package's own float32 result, and within the
+reference's tolerance for the dtype (tests/pytest/accuracy_utils.py:24-26: 1e-3 for float16,
+0.016 for bfloat16) of the oracle."""
 
 import numpy as np
 import pytest
@@ -44,7 +45,7 @@ def test_spmv_half_values(dtype, op):
     _close(y, oracle.spmv(host(d.float()), idx, ptr, host(x.float()), shape, op=op), dtype)
     # prepared handle, out and beta
     h = prepare_spmv_csr(d, i, p, shape, op=op)
-    assert h.value_dtype == dtype and h.data.dtype == torch.float32
+    assert h.value_dtype == dtype and h.data.dtype == dtype      # kept as stored: no float32 copy
     assert torch.equal(flagsparse_spmv_csr(x=x, prepared=h), y)
     y0 = dev(random_values(rng, y.numel(), np.float32)).to(dtype)
     out = y0.clone()

@@ -34,24 +34,14 @@ def test_long_row_panel_width_and_policy():
     assert _plan.LONG_ROW_MIN == saved[1] and _plan.LONG_ROW_POLICY == saved[0]
 
 
-def test_widened_half_values_are_made_once_per_tensor_state():
-    from flagsparse_b200 import _half
-    _half.clear_widened()
-    d = torch.arange(8, dtype=torch.float32).to(torch.bfloat16)
-    w1 = _half.widened_values(d)
-    assert w1.dtype == torch.float32 and torch.equal(w1, d.float())
-    assert _half.widened_values(d) is w1                 # same tensor, same version: cached
-    d.mul_(2)                                            # in-place change bumps the version
-    w2 = _half.widened_values(d)
-    assert w2 is not w1 and torch.equal(w2, d.float())
+def test_half_dtypes_have_value_codes_and_float32_scalars():
+    """float16 / bfloat16 are value dtypes of their own at the C ABI (no widened copies): their
+    codes, and alpha / beta passed as float32."""
+    import ctypes
+
+    from flagsparse_b200 import _half, _lib
+    assert _lib.VALUE_CODE[torch.float16] == 4 and _lib.VALUE_CODE[torch.bfloat16] == 5
     h = torch.ones(8, dtype=torch.float16)
-    assert _half.widened_values(h).dtype == torch.float32
-    assert _half.is_half(h) and not _half.is_half(w2) and not _half.is_half(None)
-    for k in range(20):                                  # bounded: old entries fall out
-        _half.widened_values(torch.full((4,), float(k), dtype=torch.float16))
-    assert len(_half._WIDE) <= _half._WIDE_CAPACITY
-    out = torch.zeros(8, dtype=torch.float16)
-    r = torch.arange(8, dtype=torch.float32)
-    assert _half.narrow_result(r, torch.float16, out) is out and torch.equal(out.float(), r)
-    assert _half.narrow_result(r, torch.bfloat16, None).dtype == torch.bfloat16
-    _half.clear_widened()
+    assert _half.is_half(h) and not _half.is_half(h.float()) and not _half.is_half(None)
+    buf = _lib.scalar_buffer(0.5, torch.bfloat16)
+    assert isinstance(buf, ctypes.Array) and ctypes.sizeof(buf) == 4 and buf[0] == 0.5
