@@ -158,7 +158,7 @@ def test_dense_transpose_entry_point():
     from flagsparse_b200 import _lib as L
     lib = L.load()
     stream = L.stream_handle(torch.device("cuda", 0))
-    for dtype in (torch.float32, torch.float64, torch.complex128):
+    for dtype in (torch.float16, torch.float32, torch.float64, torch.complex128):
         for rows, cols in ((1, 1), (31, 33), (64, 32), (100, 7), (5, 1000)):
             src = torch.randn(rows, cols + 2, dtype=torch.float64, device="cuda").to(dtype)
             dst = torch.zeros(cols, rows + 3, dtype=dtype, device="cuda")
@@ -169,7 +169,7 @@ def test_dense_transpose_entry_point():
             assert torch.equal(dst[:, :rows], src[:, :cols].t())
             assert float(dst[:, rows:].abs().sum()) == 0.0
     a = torch.zeros(8, 8, device="cuda")
-    assert lib.b2s_dense_transpose(2, L.ptr(a), 8, 8, 8, L.ptr(a), 8, stream) == 1
+    assert lib.b2s_dense_transpose(3, L.ptr(a), 8, 8, 8, L.ptr(a), 8, stream) == 1
     assert lib.b2s_dense_transpose(4, L.ptr(a), 8, 8, 7, L.ptr(a), 8, stream) == 2
     assert lib.b2s_dense_transpose(4, None, 8, 8, 8, L.ptr(a), 8, stream) == 2
     assert lib.b2s_dense_transpose(4, L.ptr(a), 0, 8, 8, L.ptr(a), 8, stream) == 0
