@@ -90,8 +90,15 @@ _PATCHED_NAMES = ("flagsparse_spmv_csr", "flagsparse_spmm_csr", "prepare_spmv_cs
                   "PreparedCsrSpmmRoute")
 
 
-def install(flagsparse_module=None):
+def install(flagsparse_module=None, replace_modules=False):
     """Rebind FlagSparse's CSR SpMV / SpMM entry points to this package.
+
+    replace_modules=True additionally registers this package's ``spmv`` / ``spmm`` modules as
+    ``flagsparse.sparse_operations.spmv_csr`` / ``.spmm_csr`` (in ``sys.modules`` and as
+    attributes of the subpackage), so that code which reaches into those modules by name --
+    FlagSparse's own accuracy tests patch ``_triton_spmv_csr_impl_prepared`` and
+    ``_run_spmv_prepared`` there (tests/pytest/test_spmv_csr_accuracy.py:152-234) -- acts on
+    this implementation.
 
     FlagSparse resolves its public names lazily from ``flagsparse.sparse_operations``
     (src/flagsparse/__init__.py:247-254) and imports them eagerly into that subpackage
@@ -118,6 +125,16 @@ def install(flagsparse_module=None):
             if name in vars(mod) or mod is flagsparse_module:
                 replaced[(mod.__name__, name)] = vars(mod).get(name)
                 setattr(mod, name, getattr(here, name))
+    if replace_modules:
+        ops_name = f"{flagsparse_module.__name__}.sparse_operations"
+        ops = sys.modules.get(ops_name)
+        for sub, ours in (("spmv_csr", "spmv"), ("spmm_csr", "spmm")):
+            mine = importlib.import_module(f"{__name__}.{ours}")
+            replaced[("sys.modules", f"{ops_name}.{sub}")] = sys.modules.get(f"{ops_name}.{sub}")
+            sys.modules[f"{ops_name}.{sub}"] = mine
+            if ops is not None:
+                replaced[(ops_name, sub)] = vars(ops).get(sub)
+                setattr(ops, sub, mine)
     return replaced
 
 
@@ -126,6 +143,12 @@ def uninstall(replaced):
     import sys
 
     for (mod_name, name), old in replaced.items():
+        if mod_name == "sys.modules":
+            if old is None:
+                sys.modules.pop(name, None)
+            else:
+                sys.modules[name] = old
+            continue
         mod = sys.modules.get(mod_name)
         if mod is None:
             continue

@@ -475,7 +475,10 @@ def _triton_spmv_csr_impl_prepared(prepared, x, **kw):
 
 def _run_spmv_prepared(prepared, x, use_opt=False, opt_buckets=None, out=None, alpha=1.0,
                        beta=0.0):
-    # looked up by name at call time so that patching the module attribute takes effect
+    # looked up by name at call time so that patching the module attribute takes effect; the
+    # reference's two-argument call shape is kept when nothing beyond it is asked for
+    if out is None and alpha == 1.0 and beta == 0.0:
+        return _triton_spmv_csr_impl_prepared(prepared, x)
     return _triton_spmv_csr_impl_prepared(prepared, x, out=out, alpha=alpha, beta=beta)
 
 
@@ -483,16 +486,18 @@ def _run_spmv_prepared_with_fallback(prepared, x, use_opt=False, opt_buckets=Non
                                      alpha=1.0, beta=0.0):
     """Run; if the launch raises and the matrix has int64 indices and the policy is 'auto',
     run once more on int32 copies of the index arrays (spmv_csr.py:790-810)."""
+    extra = {} if (out is None and alpha == 1.0 and beta == 0.0) else dict(
+        out=out, alpha=alpha, beta=beta)
     try:
-        return _run_spmv_prepared(prepared, x, use_opt=use_opt, opt_buckets=opt_buckets, out=out,
-                                  alpha=alpha, beta=beta)
+        if opt_buckets is None and not extra:
+            return _run_spmv_prepared(prepared, x, use_opt=use_opt)
+        return _run_spmv_prepared(prepared, x, use_opt=use_opt, opt_buckets=opt_buckets, **extra)
     except Exception as exc:
         if (prepared.index_fallback_policy != "auto"
                 or not _spmv_uses_int64_indices(prepared)):
             raise
         fallback = _spmv_prepared_with_int32_indices(prepared, exc)
-        return _run_spmv_prepared(fallback, x, use_opt=use_opt, opt_buckets=None, out=out,
-                                  alpha=alpha, beta=beta)
+        return _run_spmv_prepared(fallback, x, use_opt=use_opt, opt_buckets=None, **extra)
 
 
 def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None, block_nnz=256,

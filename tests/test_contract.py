@@ -124,14 +124,16 @@ def test_install_rebinds_a_flagsparse_like_package():
 
 
 def test_install_into_the_real_flagsparse_package_when_its_source_is_at_hand():
-    """Only where a FlagSparse checkout is reachable (FLAGSPARSE_SRC or the usual location):
+    """Only where FlagSparse is reachable (FLAGSPARSE_SRC, or the package installed under
+    baseline/_ref):
     install() rebinds the public names on the package and its submodules; uninstall() puts the
     Triton implementations back."""
     import importlib
     import os
     import sys
 
-    src = os.environ.get("FLAGSPARSE_SRC", "/root/reference/src")
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.environ.get("FLAGSPARSE_SRC", os.path.join(here, "baseline", "_ref"))
     if not os.path.isdir(os.path.join(src, "flagsparse")):
         pytest.skip("no FlagSparse source tree here")
     sys.path.insert(0, src)
