@@ -304,6 +304,62 @@ __device__ inline void accumulate(Pack<V, S>& acc, const I* __restrict__ scol,
   }
 }
 
+// ---- float32 / int32 window path ---------------------------------------------------------------
+// The staged columns and values of the tile and its window of B rows are all in shared memory;
+// everything is addressed with 32-bit shared addresses (one multiply-add per gather, no generic
+// loads).  A row piece [i, e) is walked in aligned quads of the staging buffers: one masked
+// quad at the head, unmasked quads in the middle, one masked quad at the tail, so that the mask
+// arithmetic is paid twice per row instead of once per quad.  Same order of additions as
+// accumulate().
+__device__ inline uint4 lds_u4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(a));
+  return v;
+}
+
+template <bool MASKED>
+__device__ inline void window_quad(Pack<float>& acc, uint32_t col32, uint32_t val32, int a,
+                                   int first, int e, uint32_t win32, uint32_t pitch,
+                                   uint32_t mask_col) {
+  uint4 c4 = lds_u4(col32 + 4u * static_cast<uint32_t>(a));
+  const uint4 v4 = lds_u4(val32 + 4u * static_cast<uint32_t>(a));
+  bool k0 = true, k1 = true, k2 = true, k3 = true;
+  if constexpr (MASKED) {
+    k0 = a >= first;
+    k1 = a + 1 >= first && a + 1 < e;
+    k2 = a + 2 >= first && a + 2 < e;
+    k3 = a + 3 < e;
+    // masked entries read the first row of the window and are not added
+    if (!k0) c4.x = mask_col;
+    if (!k1) c4.y = mask_col;
+    if (!k2) c4.z = mask_col;
+    if (!k3) c4.w = mask_col;
+  }
+  const Pack<float> b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
+  const Pack<float> b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
+  const Pack<float> b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
+  const Pack<float> b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
+  if (k0) fma_pack(acc, __uint_as_float(v4.x), b0);
+  if (k1) fma_pack(acc, __uint_as_float(v4.y), b1);
+  if (k2) fma_pack(acc, __uint_as_float(v4.z), b2);
+  if (k3) fma_pack(acc, __uint_as_float(v4.w), b3);
+}
+
+// col32 / val32: shared addresses of the staged columns / values (same 16-byte phase);
+// win32 + col * pitch: shared address of the lane's 16 bytes of B row `col`
+__device__ inline void accumulate_window_quads(Pack<float>& acc, uint32_t col32, uint32_t val32,
+                                               int i, int e, uint32_t win32, uint32_t pitch,
+                                               uint32_t mask_col) {
+  if (i >= e) return;
+  int a = i - static_cast<int>((static_cast<unsigned>(i) + ((col32 >> 2) & 3u)) & 3u);
+  window_quad<true>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
+  for (a += 4; a + 4 <= e; a += 4)
+    window_quad<false>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
+  if (a < e) window_quad<true>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
+}
+
 // CTAs per SM the register allocation of the tile kernel aims at.  With 4-byte column indices and
 // values of up to 8 bytes, 12 CTAs (40 registers, a few bytes of spills) measured faster than
 // the 10 the compiler settles on by itself: banded float32 N = 32 1.27 -> 1.15 ms, transposed
@@ -456,6 +512,19 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
     const int mean = (n_nz + n_seg - 1) / n_seg;
     while (S * B2S_SPMM_GROUP_NNZ < mean && S < groups_per_warp) S <<= 1;
   }
+  // float32 / int32 window, one group per row piece: the quad walk on shared addresses
+  bool quads = false;
+  uint32_t col32 = 0, val32 = 0, win32 = 0, pitch32 = 0;
+  if constexpr (WIN && sizeof(I) == 4 && std::is_same<V, float>::value &&
+                std::is_same<ST, float>::value) {
+    col32 = smem_addr(scol);
+    val32 = smem_addr(sval);
+    pitch32 = static_cast<uint32_t>(ldb * static_cast<int64_t>(sizeof(ST)));
+    win32 = smem_addr(smem + win_off) +
+            static_cast<uint32_t>((e0 < n_dense ? e0 : 0) * sizeof(ST)) -
+            static_cast<uint32_t>(win_lo) * pitch32;
+    quads = S == 1 && (((col32 ^ val32) >> 2) & 3u) == 0;
+  }
   const int team = S * G;  // lanes per row piece
   const int p1max = (S == groups_per_warp) ? kSpmmWarpRowMax : 64 * S;
 
@@ -475,8 +544,18 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
       const int len = e - s;
       Pack<V, ST> acc = pack_zero<V, ST>();
       if (len <= p1max) {
-        accumulate<V, I, VEC, WIN, ST>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0, n_dense, Bv,
-                                   stride16, mask_col);
+        bool done = false;
+        if constexpr (WIN && sizeof(I) == 4 && std::is_same<V, float>::value &&
+                      std::is_same<ST, float>::value) {
+          if (quads) {
+            if (e0 < n_dense)
+              accumulate_window_quads(acc, col32, val32, s, e, win32, pitch32, mask_col);
+            done = true;
+          }
+        }
+        if (!done)
+          accumulate<V, I, VEC, WIN, ST>(acc, scol, sval, s, e, grp_in_team, S, B, ldb, e0,
+                                         n_dense, Bv, stride16, mask_col);
       } else if ((tid % team) == 0) {
         if (len <= kSpmmWarpRowMax) {
           const int q = atomicAdd(&qcount[0], 1);
