@@ -45,6 +45,9 @@ SIGNATURES = {
     "b2s_tile_plan": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "b2s_spmv_tile_items": (c_int, [c_int, c_int]),
     "b2s_spmm_tile_items": (c_int, [c_int, c_int]),
+    "b2s_spmm_window_tile_items": (c_int, [c_int, c_int]),
+    "b2s_spmm_window_usable": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                       c_int64, c_int64, c_int64]),
     "b2s_spmv_csr": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                              c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p]),

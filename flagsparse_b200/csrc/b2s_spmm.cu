@@ -22,6 +22,18 @@ namespace b2s {
 #ifndef B2S_SPMM_CHUNK_WIDE
 #define B2S_SPMM_CHUNK_WIDE 16  // chunk length of the chunk kernel when B rows take more than 4 lanes
 #endif
+#ifndef B2S_SPMM_WIN_PRED
+#define B2S_SPMM_WIN_PRED 1
+#endif
+#ifndef B2S_SPMM_WIN_DUAL
+#define B2S_SPMM_WIN_DUAL 0
+#endif
+#ifndef B2S_SPMM_WIN_MINBLOCKS
+#define B2S_SPMM_WIN_MINBLOCKS 6  // CTAs per SM the float32 / int32 windowed kernel is compiled for
+#endif
+#ifndef B2S_SPMM_WIN_ITEMS
+#define B2S_SPMM_WIN_ITEMS 1536  // merge items per tile of that kernel
+#endif
 #ifndef B2S_SPMM_THREADS
 #define B2S_SPMM_THREADS 128
 #endif
@@ -337,15 +349,55 @@ __device__ inline void window_quad(Pack<float>& acc, uint32_t col32, uint32_t va
     if (!k2) c4.z = mask_col;
     if (!k3) c4.w = mask_col;
   }
-  const Pack<float> b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
-  const Pack<float> b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
-  const Pack<float> b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
-  const Pack<float> b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
+  Pack<float> b0, b1, b2, b3;
+#if B2S_SPMM_WIN_PRED
+  if constexpr (MASKED) {
+    // a masked entry is not loaded at all: its lanes add no wavefront to the shared-memory pipe
+    b0 = b1 = b2 = b3 = pack_zero<float, float>();
+    if (k0) b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
+    if (k1) b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
+    if (k2) b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
+    if (k3) b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
+  } else
+#endif
+  {
+    b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
+    b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
+    b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
+    b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
+  }
   if (k0) fma_pack(acc, __uint_as_float(v4.x), b0);
   if (k1) fma_pack(acc, __uint_as_float(v4.y), b1);
   if (k2) fma_pack(acc, __uint_as_float(v4.z), b2);
   if (k3) fma_pack(acc, __uint_as_float(v4.w), b3);
 }
+
+#if B2S_SPMM_WIN_DUAL
+// two unmasked quads: eight gathers in flight before the first multiply
+__device__ inline void window_quad2(Pack<float>& acc, uint32_t col32, uint32_t val32, int a,
+                                    uint32_t win32, uint32_t pitch) {
+  const uint4 c4 = lds_u4(col32 + 4u * static_cast<uint32_t>(a));
+  const uint4 d4 = lds_u4(col32 + 4u * static_cast<uint32_t>(a) + 16u);
+  const uint4 v4 = lds_u4(val32 + 4u * static_cast<uint32_t>(a));
+  const uint4 w4 = lds_u4(val32 + 4u * static_cast<uint32_t>(a) + 16u);
+  const Pack<float> b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
+  const Pack<float> b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
+  const Pack<float> b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
+  const Pack<float> b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
+  const Pack<float> b4 = unpack16<float, float>(lds_u4(win32 + d4.x * pitch));
+  const Pack<float> b5 = unpack16<float, float>(lds_u4(win32 + d4.y * pitch));
+  const Pack<float> b6 = unpack16<float, float>(lds_u4(win32 + d4.z * pitch));
+  const Pack<float> b7 = unpack16<float, float>(lds_u4(win32 + d4.w * pitch));
+  fma_pack(acc, __uint_as_float(v4.x), b0);
+  fma_pack(acc, __uint_as_float(v4.y), b1);
+  fma_pack(acc, __uint_as_float(v4.z), b2);
+  fma_pack(acc, __uint_as_float(v4.w), b3);
+  fma_pack(acc, __uint_as_float(w4.x), b4);
+  fma_pack(acc, __uint_as_float(w4.y), b5);
+  fma_pack(acc, __uint_as_float(w4.z), b6);
+  fma_pack(acc, __uint_as_float(w4.w), b7);
+}
+#endif
 
 // col32 / val32: shared addresses of the staged columns / values (same 16-byte phase);
 // win32 + col * pitch: shared address of the lane's 16 bytes of B row `col`
@@ -355,7 +407,11 @@ __device__ inline void accumulate_window_quads(Pack<float>& acc, uint32_t col32,
   if (i >= e) return;
   int a = i - static_cast<int>((static_cast<unsigned>(i) + ((col32 >> 2) & 3u)) & 3u);
   window_quad<true>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
-  for (a += 4; a + 4 <= e; a += 4)
+  a += 4;
+#if B2S_SPMM_WIN_DUAL
+  for (; a + 8 <= e; a += 8) window_quad2(acc, col32, val32, a, win32, pitch);
+#endif
+  for (; a + 4 <= e; a += 4)
     window_quad<false>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
   if (a < e) window_quad<true>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
 }
@@ -373,7 +429,8 @@ constexpr int spmm_min_blocks() {
 #ifdef B2S_SPMM_MINBLOCKS
   return B2S_SPMM_MINBLOCKS;
 #else
-  return WIN ? 1 : ((sizeof(I) == 4 && sizeof(V) <= 8) ? 12 : 1);
+  if (WIN) return (sizeof(I) == 4 && sizeof(V) == 4) ? B2S_SPMM_WIN_MINBLOCKS : 1;
+  return (sizeof(I) == 4 && sizeof(V) <= 8) ? 12 : 1;
 #endif
 }
 
@@ -644,7 +701,7 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
 // of the preceding chunks in ascending order.  Work per team is uniform (CH entries), sums have
 // a fixed order, nothing is atomic.
 // ---------------------------------------------------------------------------------------------
-constexpr int kSpmmMaxChunks = 256;
+constexpr int kSpmmMaxChunks = B2S_SPMM_ITEMS / 4;
 static_assert(B2S_SPMM_ITEMS <= 4 * kSpmmMaxChunks, "the shortest chunk has 4 entries");
 
 template <int ITEMS, class V, class I>
@@ -878,6 +935,34 @@ __global__ void spmm_fixup_narrow_kernel(S* C, const S* C_in, int64_t ldc, int64
   C[r * ldc + n * cs] = storage_of<S>::from_acc(out);
 }
 
+// Tile length of the windowed kernel.  float32 values with int32 columns (the quad walk) run
+// 1536-item tiles, 6 CTAs per SM: on the banded benchmark matrix 0.79 ms against 1.03 ms with
+// 1024-item tiles at 5 CTAs (more rows per tile for the 16 teams, a smaller share of halo rows
+// in the window).
+template <class V, class I>
+constexpr int spmm_window_items() {
+  return (std::is_same<V, float>::value && sizeof(I) == 4) ? B2S_SPMM_WIN_ITEMS
+                                                             : SpmmCfg<V, I>::ITEMS;
+}
+
+// Whether the windowed kernel can run this product: whole, 16-byte aligned packs in B, C and
+// C_in, one dense-column tile, 32-bit row offsets into B, the window within its buffer.
+template <class V>
+bool spmm_window_usable(const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
+                        const void* C, int64_t ldc, int64_t n_cols, int64_t window_rows) {
+  constexpr int PN = Pack<V>::N;
+  if (window_rows <= 0 || n_dense <= 0 || n_dense % PN != 0) return false;
+  if ((n_dense + PN - 1) / PN > 32) return false;
+  const bool aligned = reinterpret_cast<uintptr_t>(B) % 16 == 0 && (ldb * sizeof(V)) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(C) % 16 == 0 && (ldc * sizeof(V)) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(C_in) % 16 == 0;
+  if (!aligned) return false;
+  if (static_cast<double>(n_cols) * static_cast<double>(ldb) * sizeof(V) / 16.0 >= 4.0e9)
+    return false;
+  return static_cast<uint64_t>(window_rows) * static_cast<uint64_t>(ldb) * sizeof(V) <=
+         kSpmmWindowMaxBytes;
+}
+
 template <class V, class I, class P, class S = V>
 int spmm_launch(const void* data, const void* indices, const void* indptr, int64_t n_rows,
                 int64_t n_cols, int64_t nnz, const void* B, int64_t ldb, int64_t n_dense, const void* C_in,
@@ -886,7 +971,15 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
                 int64_t window_rows = 0, const int32_t* tile_win = nullptr, int64_t cs = 1) {
   using Cfg = SpmmCfg<V, I>;
   constexpr int THREADS = Cfg::THREADS, ITEMS = Cfg::ITEMS;
-  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, ITEMS);
+  constexpr int WITEMS = spmm_window_items<V, I>();
+  // with a window the caller's tile plan, window table and carries are those of WITEMS-item tiles
+  const bool windowed = window_rows > 0;
+  if (windowed) {
+    if (!std::is_same<S, V>::value || tile_win == nullptr || cs != 1 ||
+        !spmm_window_usable<V>(B, ldb, n_dense, C_in, C, ldc, n_cols, window_rows))
+      return B2S_ERR_ARG;
+  }
+  const int64_t n_tiles = b2s_tile_count(n_rows, nnz, windowed ? WITEMS : ITEMS);
   if (n_tiles == 0 || n_dense == 0) return B2S_OK;
   if (n_tiles > 0x7fffffffLL) return B2S_ERR_RANGE;
   const V a = *static_cast<const V*>(alpha);
@@ -919,7 +1012,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
   // With 4-byte column indices the team-per-row kernel (12 CTAs per SM) is the faster one for
   // narrow rows too: the two pieces of the long-row split of that matrix, N = 16, take
   // 18.7 + 4.8 ms against 21.1 + 9.8 ms with the chunk kernel.
-  const bool chunked = !kNarrow && (B2S_SPMM_CHUNKED == 1 ||
+  const bool chunked = !kNarrow && !windowed && (B2S_SPMM_CHUNKED == 1 ||
                                     (B2S_SPMM_CHUNKED == 2 && G <= 4 && sizeof(I) == 8));
   if constexpr (kNarrow) {
     // 16-bit storage: the team-per-row kernel only (no chunk kernel, no shared-memory window)
@@ -966,13 +1059,12 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, true>);
     else
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, false>);
-  } else if (window_rows > 0 && tile_win != nullptr && vec && small_b && col_tiles == 1 &&
-             static_cast<uint64_t>(window_rows) * static_cast<uint64_t>(ldb) * sizeof(V) <=
-                 kSpmmWindowMaxBytes) {
+  } else if (windowed) {
     // the B rows of every tile fit a shared-memory window: gather from there
-    constexpr size_t base = (spmm_smem_bytes<THREADS, ITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
+    constexpr size_t base =
+        (spmm_smem_bytes<THREADS, WITEMS, V, I>() + 15) & ~static_cast<size_t>(15);
     const size_t smem = base + static_cast<size_t>(window_rows) * static_cast<size_t>(ldb) * sizeof(V);
-    auto kern = spmm_tile_kernel<V, I, P, THREADS, ITEMS, true, true>;
+    auto kern = spmm_tile_kernel<V, I, P, THREADS, WITEMS, true, true>;
     ensure_dyn_smem(reinterpret_cast<const void*>(kern), base + kSpmmWindowMaxBytes);
     kern<<<grid, THREADS, smem, stream>>>(
         static_cast<const V*>(data), static_cast<const I*>(indices),
@@ -1011,6 +1103,23 @@ extern "C" int b2s_spmm_tile_items(int val_type, int idx_type) {
   (void)val_type;
   (void)idx_type;
   return b2s::SpmmCfg<float, int32_t>::ITEMS;
+}
+
+extern "C" int b2s_spmm_window_tile_items(int val_type, int idx_type) {
+  return (val_type == B2S_F32 && idx_type == B2S_I32) ? b2s::spmm_window_items<float, int32_t>()
+                                                      : b2s::SpmmCfg<float, int32_t>::ITEMS;
+}
+
+extern "C" int b2s_spmm_window_usable(int val_type, const void* B_dev, int64_t ldb,
+                                      int64_t n_dense, const void* C_in_dev, const void* C_dev,
+                                      int64_t ldc, int64_t n_cols, int64_t window_rows) {
+  switch (val_type) {
+    case B2S_F32: return b2s::spmm_window_usable<float>(B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, n_cols, window_rows);
+    case B2S_F64: return b2s::spmm_window_usable<double>(B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, n_cols, window_rows);
+    case B2S_C64: return b2s::spmm_window_usable<b2s::c64>(B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, n_cols, window_rows);
+    case B2S_C128: return b2s::spmm_window_usable<b2s::c128>(B_dev, ldb, n_dense, C_in_dev, C_dev, ldc, n_cols, window_rows);
+    default: return 0;
+  }
 }
 
 namespace b2s {

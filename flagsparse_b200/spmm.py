@@ -212,21 +212,26 @@ def _launch_spmm_plain(plan: CsrPlan, B, C, C_in, alpha, beta):
     """One b2s_spmm_csr launch for the matrix of `plan` as it is."""
     lib = _lib.load()
     n_dense = int(B.shape[1])
+    dtype = plan.data.dtype
+    # banded / local matrices: when the B rows of every tile fit a shared-memory window the
+    # kernel copies them there once per tile and gathers from shared memory; that kernel has its
+    # own tile length, so the window is settled before the tile plan is picked
+    window, table = 0, None
     items = lib.b2s_spmm_tile_items(plan.vcode, plan.icode)
+    pitch = int(B.stride(0)) * B.element_size()
+    if (_plan_mod.WINDOW_POLICY == "auto" and 0 < pitch <= _plan_mod.WINDOW_MAX_BYTES
+            and dtype in SUPPORTED_VALUE_DTYPES):
+        w_items = lib.b2s_spmm_window_tile_items(plan.vcode, plan.icode)
+        rows, w_table = plan.window(w_items)
+        if w_table is not None and rows > 0 and lib.b2s_spmm_window_usable(
+                plan.vcode, _lib.ptr(B), int(B.stride(0)), n_dense, _lib.ptr(C_in), _lib.ptr(C),
+                int(C.stride(0)), plan.n_cols, rows):
+            window, table, items = rows, w_table, w_items
     n_tiles, tile_row = plan.tiles(items)
     carry = plan.carry_on("spmm_carry", n_tiles * n_dense,
                           torch.cuda.current_stream(plan.device).cuda_stream)
-    dtype = plan.data.dtype
     a = _lib.scalar_buffer(alpha, dtype)
     b = _lib.scalar_buffer(beta, dtype)
-    # banded / local matrices: when the B rows of every tile fit a shared-memory window the
-    # kernel copies them there once per tile and gathers from shared memory
-    window, table = 0, None
-    pitch = int(B.stride(0)) * B.element_size()
-    if _plan_mod.WINDOW_POLICY == "auto" and 0 < pitch <= _plan_mod.WINDOW_MAX_BYTES:
-        rows, table = plan.window(items)
-        if table is not None and 0 < rows * pitch <= _plan_mod.WINDOW_MAX_BYTES:
-            window = rows
     with torch.cuda.device(plan.device):
         st = lib.b2s_spmm_csr_windowed(
             plan.vcode, plan.icode, plan.pcode,

@@ -301,9 +301,19 @@ int b2s_spmm_csr_colmajor_c(int val_type, int idx_type, int ptr_type,
  * and gathers from there instead of from L1 / L2.  b2s_spmm_window_stat writes to *widest_dev
  * the widest column span (largest - smallest column + 1) over the tiles of the matrix and, when
  * tile_win_dev is not NULL, to tile_win_dev[2t], [2t + 1] the first column and the span of
- * tile t (b2s_tile_count tiles); the caller passes both on (window_rows = 0: no window).  The window is used when it fits
- * (window_rows * ldb * value size <= 32 KB), B and C are 16-byte aligned with whole 16-byte
- * packs per row, and N fits one dense-column tile; otherwise the call is b2s_spmm_csr. */
+ * tile t (b2s_tile_count tiles).
+ * b2s_spmm_csr_windowed with window_rows > 0 runs the windowed kernel; its tiles are
+ * b2s_spmm_window_tile_items(...) merge items long (1536 for B2S_F32 with B2S_I32, else the
+ * length b2s_spmm_tile_items gives), and tile_row_dev, tile_win_dev and the T * n_dense carries
+ * must describe tiles of that length.  The kernel needs the window to fit (window_rows * ldb *
+ * value size <= 32 KB), B, C and C_in 16-byte aligned with whole 16-byte packs per row, N within
+ * one dense-column tile and B below 64 GB: b2s_spmm_window_usable answers 1 when all of that
+ * holds (ask before building the plan); when it does not, the call returns B2S_ERR_ARG.
+ * window_rows = 0: the call is b2s_spmm_csr. */
+int b2s_spmm_window_tile_items(int val_type, int idx_type);
+int b2s_spmm_window_usable(int val_type, const void* B_dev, int64_t ldb, int64_t n_dense,
+                           const void* C_in_dev, const void* C_dev, int64_t ldc, int64_t n_cols,
+                           int64_t window_rows);
 int b2s_spmm_window_stat(int idx_type, const void* indices_dev, int64_t n_rows, int64_t nnz,
                          const int64_t* tile_row_dev, int tile_items, int64_t* widest_dev,
                          int32_t* tile_win_dev, b2s_stream stream);

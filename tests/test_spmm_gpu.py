@@ -307,8 +307,11 @@ def test_long_row_split_is_not_taken_for_small_or_uniform_matrices():
 @pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64], ids=["i32", "i64"])
 def test_spmm_banded_matrix_uses_the_shared_memory_window(dtype, n_dense, idx_dtype):
     """A banded matrix (unsorted columns inside the band, empty rows, one dense row piece) whose
-    tiles span few columns: B rows come from the shared-memory window.  Same additions in the
-    same order as the plain kernel, so the two results are equal bit for bit."""
+    tiles span few columns: B rows come from the shared-memory window.  Where the windowed kernel
+    cuts the same tiles as the plain one it does the same additions in the same order and the
+    two results are equal bit for bit; float32 with int32 columns runs longer tiles, so rows that
+    cross a tile border are split elsewhere and the results agree to the parity tolerance."""
+    from flagsparse_b200 import _lib as _lib_mod
     from flagsparse_b200 import _plan, clear_plan_cache, flagsparse_spmm_csr, set_window_policy
     rng = np.random.default_rng(300 + n_dense)
     n, band = 3000, 10
@@ -334,9 +337,13 @@ def test_spmm_banded_matrix_uses_the_shared_memory_window(dtype, n_dense, idx_dt
         out = dev(C0)
         flagsparse_spmm_csr(d, i, p, dev(B), (n, n), out=out, alpha=0.5, beta=-1.5)
         plan = _plan.cache_get(_plan.plan_key("spmm", d, i, p, (n, n)))
-        span = plan.window_rows(1024)
+        lib = _lib_mod.load()
+        w_items = lib.b2s_spmm_window_tile_items(plan.vcode, plan.icode)
+        same_tiles = w_items == lib.b2s_spmm_tile_items(plan.vcode, plan.icode)
+        assert same_tiles == (not (dtype == np.float32 and plan.indices.dtype == torch.int32))
+        span = plan.window_rows(w_items)
         assert 0 < span < 200
-        if n_dense * data.itemsize <= 256:   # wider B rows do not fit and take the plain kernel
+        if n_dense * data.itemsize <= 128:   # wider B rows may not fit and take the plain kernel
             assert span * n_dense * data.itemsize <= _plan.WINDOW_MAX_BYTES
         expect = oracle.spmm(data, cols, ptr, B, (n, n), alpha=0.5, beta=-1.5, C0=C0)
         assert_parity(host(out), expect, dtype)
@@ -350,7 +357,10 @@ def test_spmm_banded_matrix_uses_the_shared_memory_window(dtype, n_dense, idx_dt
         set_window_policy("off")
         clear_plan_cache()
         plain = flagsparse_spmm_csr(d, i, p, dev(B), (n, n))
-        assert torch.equal(C.view(torch.uint8), plain.view(torch.uint8))
+        if same_tiles:
+            assert torch.equal(C.view(torch.uint8), plain.view(torch.uint8))
+        else:
+            assert_parity(host(C), host(plain), dtype)
     finally:
         set_window_policy("auto")
         clear_plan_cache()
