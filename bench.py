@@ -19,7 +19,9 @@ rows up to 100,000 entries, y = 1.5 * A x + 0.5 * y.  A step is one such product
                 printed and the run exits non-zero
   extra         GFLOP/s, gathered bytes (x / B counted once per non-zero) and their rate, the
                 SpMM N = 32 product on the same matrix, the measured divergent-gather ceiling
-                of the GPU and the SpMV's fraction of it
+                of the GPU and the SpMV's fraction of it, and (when the unmodified FlagSparse
+                package is installed under baseline/_ref) its Triton kernels timed on the same
+                GPU and tensors beside this package (reference_triton_same_gpu)
   --impl reference   only that CPU measurement, as its own line
   --workload cfg2mm  the second half of the target as a line of its own: SpMM N = 32 on the
                 same power-law matrix, with its own roofline / cpu_baseline / e2e / parity
@@ -239,9 +241,10 @@ def make_step(p, kind):
 
 
 def extra_launches(p, kind):
-    """Kernels per step beyond the tile kernel and the carry fix-up: 1 when the SpMV runs on the
-    column-panel layout (panel combine), 3 when the SpMM splits the long rows off (a second tile
-    kernel and fix-up for the panel stack, and the combine)."""
+    """Kernels per step beyond the two make_step counts.  SpMV on the column-panel stack: the
+    stack kernel, its fix-up and the combine (1 more), and with long rows split off the
+    shared-memory kernel, its fix-up and the long-row combine (4 more).  SpMM with the long rows
+    split off: a second tile kernel and fix-up for the panel stack, and the combine (3 more)."""
     from flagsparse_b200 import _plan
     key = _plan.plan_key(kind, p.data, p.indices, p.indptr, p.shape)
     plan = _plan.cache_get(key)
@@ -250,7 +253,10 @@ def extra_launches(p, kind):
     if p.extra.get("op", "non") != "non":
         plan = plan.transposed(conj=p.extra.get("op") == "conj")
     if kind == "spmv":
-        return 1 if plan.panels() is not None else 0
+        lay = plan.panels()
+        if lay is None:
+            return 0
+        return 4 if lay.long_rows is not None else 1
     row_bytes = int(p.B.shape[1]) * p.B.element_size()
     return 3 if plan.long_row_split(row_bytes) is not None else 0
 
@@ -524,6 +530,65 @@ def run_reference_arm(args, rank, world):
                 "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def reference_triton(p, kind, repeats=5):
+    """The unmodified FlagSparse package (its Triton kernels, its public functions) on this GPU
+    and on the same device tensors, beside this package on those tensors.  Context only -- the
+    reference arm of this benchmark is the CPU path.  Runs when the package is installed under
+    baseline/_ref (baseline/install_reference.py), else returns None.
+
+    The reference's SpMV kernel walks ceil(longest row / 256) segments for every row of the
+    matrix it is given (spmv_csr.py:183), so power-law matrices are timed on their first 2^18
+    rows; SpMM on more than 2 * 10^8 non-zeros on the first 2^20 rows.  Both sides get the same
+    slice, alpha = 1, beta = 0 (the reference has no alpha / beta)."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "flagsparse").is_dir():
+        return None
+    sys.path.insert(0, str(ref_dir))
+    try:
+        import flagsparse as ref
+        from flagsparse_b200 import flagsparse_spmm_csr, flagsparse_spmv_csr
+        op = p.extra.get("op", "non")
+        rows_cap = p.shape[0]
+        if kind == "spmv" and p.shape[0] > (1 << 18) and op == "non":
+            rows_cap = 1 << 18
+        elif kind == "spmm" and p.nnz > 200_000_000 and op == "non":
+            rows_cap = 1 << 20
+        j1 = int(p.indptr[rows_cap])
+        data, indices = p.data[:j1], p.indices[:j1]
+        indptr = p.indptr[:rows_cap + 1].clone()
+        shape = (rows_cap, p.shape[1])
+        if kind == "spmv":
+            theirs = lambda: ref.flagsparse_spmv_csr(data, indices, indptr, p.x, shape, op=op)  # noqa: E731
+            ours = lambda: flagsparse_spmv_csr(data, indices, indptr, p.x, shape, op=op)  # noqa: E731
+        else:
+            theirs = lambda: ref.flagsparse_spmm_csr(data, indices, indptr, p.B, shape, op=op)  # noqa: E731
+            ours = lambda: flagsparse_spmm_csr(data, indices, indptr, p.B, shape, op=op)  # noqa: E731
+
+        def timed(fn):
+            for _ in range(2):
+                got = fn()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(repeats):
+                fn()
+            t1.record()
+            torch.cuda.synchronize()
+            return t0.elapsed_time(t1) / repeats, got
+
+        ref_ms, ref_out = timed(theirs)
+        our_ms, our_out = timed(ours)
+        return {"reference_ms": ref_ms, "ours_ms": our_ms, "rows": rows_cap, "nnz": j1,
+                "rel_l2_ours_vs_reference": rel_l2(our_out, ref_out.to(
+                    torch.complex128 if ref_out.is_complex() else torch.float64)),
+                "timing": f"CUDA events over {repeats} calls of the public function after 2 "
+                          "warm-up calls, plans / prepared state cached on both sides"}
+    except Exception as exc:  # reported, never fatal for the bench line
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+    finally:
+        sys.path.remove(str(ref_dir))
 
 
 def gather_ceiling(device, spmv_gathers_per_s):
@@ -956,6 +1021,12 @@ def main():
 
     if kind == "spmv" and not args.no_extra:
         extra["gather_ceiling"] = gather_ceiling(device, p.nnz / per_step)
+
+    if not args.no_extra:
+        side = reference_triton(p, kind)
+        if side is not None:
+            extra["reference_triton_same_gpu"] = side
+        torch.cuda.empty_cache()
 
     if nbytes < 1e9:
         # small problems are bound by launch latency: the same products replayed from a CUDA

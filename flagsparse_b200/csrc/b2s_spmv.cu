@@ -406,30 +406,54 @@ struct PeerList {
   void* p[16];
 };
 
+// A thread finishes the 16 / sizeof(V) consecutive rows that make up 16 bytes of y and stores
+// them to every peer with one 16-byte store (vec_ok: the peers' buffers are 16-byte aligned and
+// row_offset is a multiple of that row count); ragged ends and unaligned blocks store by value.
 template <class V>
 __global__ void panel_combine_peers_kernel(const V* __restrict__ ypart,
                                            const int32_t* __restrict__ subpos, int64_t n_rows,
                                            int n_panels, const V* y_in, PeerList peers,
                                            int n_peers, int64_t row_offset, V alpha, V beta,
-                                           int has_beta) {
-  // grid-stride: with one thread per row the loop runs once; a small grid (grid_limit of the
-  // entry point) keeps the kernel to a few CTAs per SM so that it can drain over NVLink beside
-  // the tile kernel of the next row block instead of filling the GPU with stalled stores
+                                           int has_beta, int vec_ok) {
+  constexpr int RP = sizeof(V) >= 16 ? 1 : 16 / static_cast<int>(sizeof(V));
+  // grid-stride: with one thread per row group the loop runs once; a small grid (grid_limit of
+  // the entry point) keeps the kernel to a few CTAs per SM so that it can drain over NVLink
+  // beside the tile kernel of the next row block instead of filling the GPU with stalled stores
+  const int64_t n_groups = (n_rows + RP - 1) / RP;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < n_rows;
-       r += stride) {
-    V s = vt<V>::zero();
-    for (int p = 0; p < n_panels; ++p) {
-      if (subpos != nullptr) {
-        const int32_t c = subpos[p * n_rows + r];
-        if (c >= 0) s = s + ypart[c];
-      } else {
-        s = s + ypart[p * n_rows + r];
+  for (int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; g < n_groups;
+       g += stride) {
+    const int64_t r0 = g * RP;
+    alignas(16) V out[RP];
+#pragma unroll
+    for (int j = 0; j < RP; ++j) {
+      const int64_t r = r0 + j;
+      V s = vt<V>::zero();
+      if (r < n_rows) {
+        for (int p = 0; p < n_panels; ++p) {
+          if (subpos != nullptr) {
+            const int32_t c = subpos[p * n_rows + r];
+            if (c >= 0) s = s + ypart[c];
+          } else {
+            s = s + ypart[p * n_rows + r];
+          }
+        }
+        s = alpha * s;
+        if (has_beta) s = s + beta * y_in[r];
       }
+      out[j] = s;
     }
-    V out = alpha * s;
-    if (has_beta) out = out + beta * y_in[r];
-    for (int q = 0; q < n_peers; ++q) static_cast<V*>(peers.p[q])[row_offset + r] = out;
+    if (vec_ok && r0 + RP <= n_rows) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(out);
+      for (int q = 0; q < n_peers; ++q)
+        *reinterpret_cast<uint4*>(static_cast<V*>(peers.p[q]) + row_offset + r0) = raw;
+    } else {
+#pragma unroll
+      for (int j = 0; j < RP; ++j)
+        if (r0 + j < n_rows)
+          for (int q = 0; q < n_peers; ++q)
+            static_cast<V*>(peers.p[q])[row_offset + r0 + j] = out[j];
+    }
   }
 }
 
@@ -517,7 +541,12 @@ extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
   if (pst != B2S_OK) return pst;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = 256;
-  int64_t want = (n_rows + threads - 1) / threads;
+  const int64_t rows_per_thread = vs >= 16 ? 1 : 16 / static_cast<int64_t>(vs);
+  int vec_ok = row_offset % rows_per_thread == 0;
+  for (int q = 0; q < n_peers; ++q)
+    if (reinterpret_cast<uintptr_t>(peer_y[q]) % 16) vec_ok = 0;
+  const int64_t n_groups = (n_rows + rows_per_thread - 1) / rows_per_thread;
+  int64_t want = (n_groups + threads - 1) / threads;
   if (grid_limit > 0 && want > grid_limit) want = grid_limit;
   const unsigned grid = static_cast<unsigned>(want);
   B2S_DISPATCH_V(val_type, {
@@ -527,7 +556,7 @@ extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
     if (has_beta && y_in_dev == nullptr) return B2S_ERR_ARG;
     (b2s::panel_combine_peers_kernel<V><<<grid, threads, 0, s>>>(
         static_cast<const V*>(ypart_dev), subpos_dev, n_rows, n_panels,
-        static_cast<const V*>(y_in_dev), peers, n_peers, row_offset, a, b, has_beta));
+        static_cast<const V*>(y_in_dev), peers, n_peers, row_offset, a, b, has_beta, vec_ok));
   });
   return b2s::launch_status();
 }

@@ -233,3 +233,52 @@ def test_csr2csc_with_more_than_2_31_columns_uses_the_64_bit_sort():
     assert bool((t_ptr[1:200_000] >= t_ptr[:199_999]).all())
     del ws, t_ptr
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64, torch.complex128],
+                         ids=lambda d: str(d).replace("torch.", ""))
+@pytest.mark.parametrize("n_rows,row_offset", [(1001, 0), (1000, 4), (777, 3), (5, 1)])
+def test_panel_combine_peers_stores_the_same_values_as_panel_combine(dtype, n_rows, row_offset):
+    """b2s_panel_combine_peers with two buffers of this GPU standing for the peers: every buffer
+    receives, at row_offset, exactly what b2s_panel_combine writes (16-byte stores where the
+    block is aligned, by value otherwise and at the ragged end), and nothing outside the block."""
+    lib, L = _lib()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(n_rows + row_offset)
+    n_panels = 3
+    real = torch.float64 if dtype in (torch.float64, torch.complex128) else torch.float32
+    def rand(n):
+        if dtype.is_complex:
+            return torch.complex(torch.randn(n, dtype=real, device="cuda", generator=g),
+                                 torch.randn(n, dtype=real, device="cuda", generator=g))
+        return torch.randn(n, dtype=dtype, device="cuda", generator=g)
+    n_part = 2 * n_rows
+    ypart = rand(n_part)
+    subpos = torch.randint(-1, n_part, (n_panels * n_rows,), dtype=torch.int32, device="cuda",
+                           generator=g)
+    y_in = rand(n_rows)
+    vcode = L.VALUE_CODE[dtype]
+    a, b = L.scalar_buffer(0.75, dtype), L.scalar_buffer(-0.5, dtype)
+    stream = L.stream_handle(ypart.device)
+    want = torch.empty(n_rows, dtype=dtype, device="cuda")
+    assert lib.b2s_panel_combine(vcode, L.ptr(ypart), L.ptr(subpos), n_rows, n_panels,
+                                 L.ptr(y_in), L.ptr(want), a, b, stream) == 0
+    peer_rows = row_offset + n_rows + 7
+    bufs = [torch.full((peer_rows,), 9.0, dtype=dtype, device="cuda") for _ in range(2)]
+    arr = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in bufs])
+    for grid_limit in (0, 2):
+        for t in bufs:
+            t.fill_(9.0)
+        assert lib.b2s_panel_combine_peers(vcode, L.ptr(ypart), L.ptr(subpos), n_rows, n_panels,
+                                           L.ptr(y_in), arr, 2, row_offset, peer_rows, a, b,
+                                           grid_limit, stream) == 0
+        torch.cuda.synchronize()
+        for t in bufs:
+            assert torch.equal(t[row_offset:row_offset + n_rows].view(torch.uint8),
+                               want.view(torch.uint8))
+            assert bool((t[:row_offset] == 9.0).all()) and bool(
+                (t[row_offset + n_rows:] == 9.0).all())
+    # a block that does not fit the peers' buffers is refused
+    assert lib.b2s_panel_combine_peers(vcode, L.ptr(ypart), L.ptr(subpos), n_rows, n_panels,
+                                       L.ptr(y_in), arr, 2, 8, n_rows + 7, a, b, 0, stream) == \
+        2   # B2S_ERR_ARG
