@@ -743,6 +743,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
         args.stages = 1 if world < 4 else 2
     if args.store_ctas >= 0:
         part.peer_store_ctas = args.store_ctas
+    part.pipeline_broadcast = not args.no_pipelined_broadcast
     staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
     gather_mode = args.gather
@@ -859,10 +860,14 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     panels = (kind == "spmv" and plan_mod.PANEL_POLICY == "auto"
               and dense.numel() * dense.element_size() > plan_mod.PANEL_TRIGGER_BYTES
               and p.nnz // n_stage >= plan_mod.PANEL_MIN_NNZ)
-    per_stage = 3 if (panels or gather_mode == "peer") else 2
-    if kind == "spmm":
-        per_stage = 2 + extra_launches(p, kind) + (1 if gather_mode == "peer" else 0)
+    # (the count follows the plan of the whole block, which the phase timing above has built)
+    per_stage = 2 + extra_launches(p, kind)
+    if gather_mode == "peer" and not panels:
+        per_stage += 1
     launches_per_rank_step = n_stage * per_stage
+    pipelined_bcast = bool(gather_mode == "peer" and panels and part.pipeline_broadcast)
+    if pipelined_bcast:   # the wide-panel kernel of the first stage runs as one launch per panel
+        launches_per_rank_step += (((p.shape[1] - 1) >> plan_mod.panel_shift(p.data.dtype)) + 1) - 1
     if rank == 0:
         gbs = job_bytes / per_step / 1e9
         kernel_gbs = job_bytes / (phases["kernel_ms"] / 1e3) / 1e9
@@ -875,7 +880,10 @@ def run_multi_gpu(args, rank, world, local_rank, device):
             "config": config_dict(args, world, part.n_rows, int(job_nnz), nbytes),
             "parity": parity,
             "exchange": {
-                "broadcast": "NCCL broadcast of x / B from rank 0",
+                "broadcast": ("NCCL broadcast of x from rank 0, one asynchronous broadcast per "
+                              "column panel; the kernel of a panel starts when its slice has "
+                              "landed" if pipelined_bcast else
+                              "NCCL broadcast of x / B from rank 0"),
                 "gather": ("stores of each rank's last kernel into every rank's "
                            "symmetric-memory result buffer over NVLink, then a one-element "
                            "NCCL all-reduce as the end-of-step fence"
@@ -935,6 +943,8 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
                     help="N > 1: how y / C is assembled -- NCCL all-gather, or stores of the last "
                          "kernel into every rank's symmetric-memory buffer")
+    ap.add_argument("--no-pipelined-broadcast", action="store_true",
+                    help="N > 1: broadcast x in one piece before the first kernel")
     ap.add_argument("--no-cfg5", action="store_true",
                     help="N > 1: skip the partitioned 2^26-row matrix in extra.cfg5")
     ap.add_argument("--cfg5-scale", type=int, default=1,

@@ -67,6 +67,9 @@ SIGNATURES = {
     "b2s_spmv_stack": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p]),
+    "b2s_spmv_stack_tiles": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                     c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b2s_spmv_stack_shared": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                       c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p]),

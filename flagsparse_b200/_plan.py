@@ -80,6 +80,16 @@ def set_long_spmv_policy(policy="auto", min_per_panel=None, min_share=None, tile
         LONG_SPMV_TILES_PER_UNIT = max(1, int(tiles_per_unit))
 
 
+def panel_shift(value_dtype):
+    """log2 of the column-panel width the panel layout uses for this value type (a function of
+    the value size alone, so every rank of a partitioned matrix arrives at the same one)."""
+    vbytes = torch.empty(0, dtype=value_dtype).element_size()
+    shift = 1
+    while (2 << shift) * vbytes <= PANEL_TARGET_BYTES:
+        shift += 1
+    return shift
+
+
 def set_panel_policy(policy):
     """'auto' (default) or 'off': whether SpMV may keep a column-panel copy of large matrices."""
     global PANEL_POLICY
@@ -207,8 +217,21 @@ class StackLayout:
         self.tile_ord, self.tile_panel, self.panel_start = tile_ord, tile_panel, panel_start
         self.n_panels, self.shift = int(n_panels), int(shift)
         self.subpos = subpos                # int32[n_panels * n_rows]
+        self.tile = int(tile)
         self.n_tiles = self.n_entries // int(tile)
         self.long_rows = None               # LongRowStack when the long rows were taken out
+        self._tile_bounds = None
+
+    def panel_tile_bounds(self):
+        """Host list b of n_panels tile indices: the tiles that need no x beyond panel p are
+        tiles [0, b[p]) (a tile that straddles two panels counts for the later one); b[-1] is
+        the number of tiles.  One read-back, kept."""
+        if self._tile_bounds is None:
+            b = torch.div(self.panel_start[1:], self.tile, rounding_mode="floor").tolist()
+            b = [min(int(v), self.n_tiles) for v in b]
+            b[-1] = self.n_tiles
+            self._tile_bounds = b
+        return self._tile_bounds
 
 
 class LongRowStack:
@@ -441,9 +464,7 @@ class CsrPlan:
         if (PANEL_POLICY != "auto" or vbytes < 4 or self.n_cols * vbytes <= PANEL_TRIGGER_BYTES
                 or self.nnz < PANEL_MIN_NNZ or self.n_rows == 0):
             return None
-        shift = 1
-        while (2 << shift) * vbytes <= PANEL_TARGET_BYTES:
-            shift += 1
+        shift = panel_shift(self.data.dtype)
         n_panels = ((self.n_cols - 1) >> shift) + 1
         if n_panels < 2 or n_panels > 256 or shift > 29:
             return None

@@ -22,12 +22,6 @@ namespace b2s {
 #ifndef B2S_SPMM_CHUNK_WIDE
 #define B2S_SPMM_CHUNK_WIDE 16  // chunk length of the chunk kernel when B rows take more than 4 lanes
 #endif
-#ifndef B2S_SPMM_WIN_PRED
-#define B2S_SPMM_WIN_PRED 1
-#endif
-#ifndef B2S_SPMM_WIN_DUAL
-#define B2S_SPMM_WIN_DUAL 0
-#endif
 #ifndef B2S_SPMM_WIN_MINBLOCKS
 #define B2S_SPMM_WIN_MINBLOCKS 6  // CTAs per SM the float32 / int32 windowed kernel is compiled for
 #endif
@@ -350,7 +344,6 @@ __device__ inline void window_quad(Pack<float>& acc, uint32_t col32, uint32_t va
     if (!k3) c4.w = mask_col;
   }
   Pack<float> b0, b1, b2, b3;
-#if B2S_SPMM_WIN_PRED
   if constexpr (MASKED) {
     // a masked entry is not loaded at all: its lanes add no wavefront to the shared-memory pipe
     b0 = b1 = b2 = b3 = pack_zero<float, float>();
@@ -358,9 +351,7 @@ __device__ inline void window_quad(Pack<float>& acc, uint32_t col32, uint32_t va
     if (k1) b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
     if (k2) b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
     if (k3) b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
-  } else
-#endif
-  {
+  } else {
     b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
     b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
     b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
@@ -372,33 +363,6 @@ __device__ inline void window_quad(Pack<float>& acc, uint32_t col32, uint32_t va
   if (k3) fma_pack(acc, __uint_as_float(v4.w), b3);
 }
 
-#if B2S_SPMM_WIN_DUAL
-// two unmasked quads: eight gathers in flight before the first multiply
-__device__ inline void window_quad2(Pack<float>& acc, uint32_t col32, uint32_t val32, int a,
-                                    uint32_t win32, uint32_t pitch) {
-  const uint4 c4 = lds_u4(col32 + 4u * static_cast<uint32_t>(a));
-  const uint4 d4 = lds_u4(col32 + 4u * static_cast<uint32_t>(a) + 16u);
-  const uint4 v4 = lds_u4(val32 + 4u * static_cast<uint32_t>(a));
-  const uint4 w4 = lds_u4(val32 + 4u * static_cast<uint32_t>(a) + 16u);
-  const Pack<float> b0 = unpack16<float, float>(lds_u4(win32 + c4.x * pitch));
-  const Pack<float> b1 = unpack16<float, float>(lds_u4(win32 + c4.y * pitch));
-  const Pack<float> b2 = unpack16<float, float>(lds_u4(win32 + c4.z * pitch));
-  const Pack<float> b3 = unpack16<float, float>(lds_u4(win32 + c4.w * pitch));
-  const Pack<float> b4 = unpack16<float, float>(lds_u4(win32 + d4.x * pitch));
-  const Pack<float> b5 = unpack16<float, float>(lds_u4(win32 + d4.y * pitch));
-  const Pack<float> b6 = unpack16<float, float>(lds_u4(win32 + d4.z * pitch));
-  const Pack<float> b7 = unpack16<float, float>(lds_u4(win32 + d4.w * pitch));
-  fma_pack(acc, __uint_as_float(v4.x), b0);
-  fma_pack(acc, __uint_as_float(v4.y), b1);
-  fma_pack(acc, __uint_as_float(v4.z), b2);
-  fma_pack(acc, __uint_as_float(v4.w), b3);
-  fma_pack(acc, __uint_as_float(w4.x), b4);
-  fma_pack(acc, __uint_as_float(w4.y), b5);
-  fma_pack(acc, __uint_as_float(w4.z), b6);
-  fma_pack(acc, __uint_as_float(w4.w), b7);
-}
-#endif
-
 // col32 / val32: shared addresses of the staged columns / values (same 16-byte phase);
 // win32 + col * pitch: shared address of the lane's 16 bytes of B row `col`
 __device__ inline void accumulate_window_quads(Pack<float>& acc, uint32_t col32, uint32_t val32,
@@ -408,9 +372,6 @@ __device__ inline void accumulate_window_quads(Pack<float>& acc, uint32_t col32,
   int a = i - static_cast<int>((static_cast<unsigned>(i) + ((col32 >> 2) & 3u)) & 3u);
   window_quad<true>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
   a += 4;
-#if B2S_SPMM_WIN_DUAL
-  for (; a + 8 <= e; a += 8) window_quad2(acc, col32, val32, a, win32, pitch);
-#endif
   for (; a + 4 <= e; a += 4)
     window_quad<false>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
   if (a < e) window_quad<true>(acc, col32, val32, a, i, e, win32, pitch, mask_col);
@@ -422,8 +383,9 @@ __device__ inline void accumulate_window_quads(Pack<float>& acc, uint32_t col32,
 // Poisson matrix N = 64 0.95 -> 0.81 ms, both pieces of the long-row split of the power-law
 // matrix 3-6 % (same box).  With 8-byte indices the same limit made the one-launch product of
 // that matrix slower (13.6 -> 15.4 ms), so those instantiations stay unconstrained.
-// The windowed variant holds a window of B rows per CTA (about 7 CTAs fit an SM), so it is not
-// squeezed into 40 registers.
+// The windowed variants hold a window of B rows per CTA and are not squeezed into 40 registers:
+// the float32 / int32 one is compiled for the 6 CTAs its 37 KB of shared memory allow (80
+// registers), the others keep the compiler's choice.
 template <class V, class I, bool WIN = false>
 constexpr int spmm_min_blocks() {
 #ifdef B2S_SPMM_MINBLOCKS

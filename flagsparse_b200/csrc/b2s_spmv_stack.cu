@@ -254,10 +254,12 @@ spmv_stack_kernel(const V* __restrict__ val, const uint32_t* __restrict__ col,
                   V* __restrict__ carry, const int64_t* __restrict__ tile_ord, int64_t n_tiles,
                   int64_t n_cols, const int64_t* __restrict__ panel_start,
                   const int32_t* __restrict__ tile_panel, int n_panels, int panel_shift,
-                  int32_t* status) {
+                  int32_t* status, int64_t tile_begin) {
   using S = StackShape<V>;
   const int lane = threadIdx.x & 31;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * (S::THREADS / 32) + (threadIdx.x >> 5);
+  // this launch covers tiles tile_begin .. n_tiles - 1 (n_tiles: end of the range)
+  const int64_t t =
+      tile_begin + static_cast<int64_t>(blockIdx.x) * (S::THREADS / 32) + (threadIdx.x >> 5);
   if (t >= n_tiles) return;  // warps share no barrier: leaving early is safe
   uint32_t c[S::SPT];
   V v[S::SPT];
@@ -412,13 +414,16 @@ extern "C" int b2s_spmv_stack_shared_cols(int val_type) {
   return vs ? static_cast<int>(b2s::kStackSharedBytes / vs) : 0;
 }
 
-extern "C" int b2s_spmv_stack(int val_type, const void* s_data_dev, const uint32_t* s_cols_dev,
-                              int64_t n_entries, int64_t n_stacked, int64_t n_cols,
-                              int n_panels, int panel_shift, const int64_t* panel_start_dev,
-                              const int32_t* tile_panel_dev, const int64_t* tile_ord_dev,
-                              const void* x_dev, void* ypart_dev, void* carry_dev,
-                              int32_t* status_dev, b2s_stream stream) {
-  if (n_entries < 0 || n_stacked < 0 || n_cols < 0) return B2S_ERR_ARG;
+extern "C" int b2s_spmv_stack_tiles(int val_type, const void* s_data_dev,
+                                    const uint32_t* s_cols_dev, int64_t n_entries,
+                                    int64_t n_stacked, int64_t n_cols, int n_panels,
+                                    int panel_shift, const int64_t* panel_start_dev,
+                                    const int32_t* tile_panel_dev, const int64_t* tile_ord_dev,
+                                    const void* x_dev, void* ypart_dev, void* carry_dev,
+                                    int32_t* status_dev, int64_t tile_begin, int64_t tile_count,
+                                    int run_fixup, b2s_stream stream) {
+  if (n_entries < 0 || n_stacked < 0 || n_cols < 0 || tile_begin < 0 || tile_count < 0)
+    return B2S_ERR_ARG;
   if (n_panels < 1 || panel_shift < 0 || panel_shift > 30) return B2S_ERR_ARG;
   if (n_entries == 0 || n_stacked == 0) return B2S_OK;
   if (!s_data_dev || !s_cols_dev || !tile_ord_dev || !x_dev || !ypart_dev || !carry_dev)
@@ -438,20 +443,39 @@ extern "C" int b2s_spmv_stack(int val_type, const void* s_data_dev, const uint32
     constexpr int TILE = b2s::StackShape<V>::TILE;
     if (n_entries % TILE) return B2S_ERR_ARG;  // the arrays are padded to whole tiles
     const int64_t n_tiles = n_entries / TILE;
-    const int64_t n_ctas = (n_tiles + THREADS / 32 - 1) / (THREADS / 32);
+    if (tile_begin + tile_count > n_tiles) return B2S_ERR_ARG;
+    const int64_t n_ctas = (tile_count + THREADS / 32 - 1) / (THREADS / 32);
     if (n_ctas > 0x7fffffffLL) return B2S_ERR_RANGE;
-    (b2s::spmv_stack_kernel<V><<<static_cast<unsigned>(n_ctas), THREADS, 0, s>>>(
-        static_cast<const V*>(s_data_dev), s_cols_dev, static_cast<const V*>(x_dev),
-        static_cast<V*>(ypart_dev), n_stacked, static_cast<V*>(carry_dev), tile_ord_dev, n_tiles,
-        n_cols,
-        n_panels > 1 ? panel_start_dev : nullptr, n_panels > 1 ? tile_panel_dev : nullptr,
-        n_panels, panel_shift, status_dev));
-    if (n_tiles > 1)
+    if (n_ctas > 0)
+      (b2s::spmv_stack_kernel<V><<<static_cast<unsigned>(n_ctas), THREADS, 0, s>>>(
+          static_cast<const V*>(s_data_dev), s_cols_dev, static_cast<const V*>(x_dev),
+          static_cast<V*>(ypart_dev), n_stacked, static_cast<V*>(carry_dev), tile_ord_dev,
+          tile_begin + tile_count, n_cols,
+          n_panels > 1 ? panel_start_dev : nullptr, n_panels > 1 ? tile_panel_dev : nullptr,
+          n_panels, panel_shift, status_dev, tile_begin));
+    if (run_fixup && n_tiles > 1)
       (b2s::stack_fixup_kernel<V><<<static_cast<unsigned>((n_tiles + 255) / 256), 256, 0, s>>>(
           static_cast<V*>(ypart_dev), static_cast<const V*>(carry_dev), tile_ord_dev, n_tiles));
     return b2s::launch_status();
   });
   return B2S_ERR_DTYPE;
+}
+
+extern "C" int b2s_spmv_stack(int val_type, const void* s_data_dev, const uint32_t* s_cols_dev,
+                              int64_t n_entries, int64_t n_stacked, int64_t n_cols,
+                              int n_panels, int panel_shift, const int64_t* panel_start_dev,
+                              const int32_t* tile_panel_dev, const int64_t* tile_ord_dev,
+                              const void* x_dev, void* ypart_dev, void* carry_dev,
+                              int32_t* status_dev, b2s_stream stream) {
+  const size_t vs = b2s::vsize(val_type);
+  if (vs == 0) return B2S_ERR_DTYPE;
+  if (n_entries < 0) return B2S_ERR_ARG;
+  int tile = 0;
+  B2S_DISPATCH_V(val_type, { tile = b2s::StackShape<V>::TILE; });
+  return b2s_spmv_stack_tiles(val_type, s_data_dev, s_cols_dev, n_entries, n_stacked, n_cols,
+                              n_panels, panel_shift, panel_start_dev, tile_panel_dev,
+                              tile_ord_dev, x_dev, ypart_dev, carry_dev, status_dev, 0,
+                              n_entries / tile, 1, stream);
 }
 
 extern "C" int b2s_spmv_stack_shared(int val_type, const void* s_data_dev,

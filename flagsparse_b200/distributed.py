@@ -72,6 +72,9 @@ class RowPartitionedCsr:
         # CTAs (of 256 threads) of a combine + store kernel that drains beside the tile kernel
         # of the next stage; 0 = one thread per row
         self.peer_store_ctas = 2 * 148
+        # SpMV with the peer gather: x is broadcast one column panel at a time and the kernel of
+        # a panel starts when its slice has landed
+        self.pipeline_broadcast = True
 
     @classmethod
     def from_global(cls, data, indices, indptr, shape, group=None, **kw):
@@ -86,6 +89,28 @@ class RowPartitionedCsr:
         """Replicate x / B: `dense` holds the data on `src` and is overwritten elsewhere."""
         dist.broadcast(dense, src=src, group=self.group)
         return dense
+
+    def broadcast_by_panel(self, x, src=0):
+        """Replicate x as one asynchronous broadcast per column panel of the SpMV panel layout
+        (the panel width follows from the value type alone, so all ranks cut x alike).  Returns
+        x_ready: x_ready(p) makes the current stream wait for the slices of panels 0..p,
+        x_ready(None) for all of x -- the kernel of panel 0 starts when 1 / P of x has landed
+        instead of all of it.  None when x is one panel wide (use broadcast_dense)."""
+        from ._plan import panel_shift
+        width = 1 << panel_shift(x.dtype)
+        n = int(x.shape[0])
+        if x.ndim != 1 or n <= width:
+            return None
+        works = [dist.broadcast(x[c0:min(c0 + width, n)], src=src, group=self.group,
+                                async_op=True) for c0 in range(0, n, width)]
+        waited = [0]
+
+        def x_ready(p):
+            upto = len(works) if p is None else min(int(p) + 1, len(works))
+            while waited[0] < upto:
+                works[waited[0]].wait()
+                waited[0] += 1
+        return x_ready
 
     def _padded(self, trailing, dtype, device):
         key = (tuple(trailing), dtype, device)
@@ -179,7 +204,7 @@ class RowPartitionedCsr:
         fence, so all their stores into this rank's buffer have landed."""
         dist.all_reduce(self._peer["flag"], group=self.group)
 
-    def _peer_spmv(self, x, out_local, alpha, beta):
+    def _peer_spmv(self, x, out_local, alpha, beta, x_ready=None):
         from .spmv import prepare_spmv_csr, spmv_block_to_peers
         peer = self._peer
         blocks = self._stages or [(self.data, self.indices, self.indptr)]
@@ -202,8 +227,11 @@ class RowPartitionedCsr:
             last = s + 1 == len(blocks)
             if not spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array"], peer["n"],
                                        row_offset, self.n_rows, store_stream=side,
-                                       store_ctas=0 if last else self.peer_store_ctas):
+                                       store_ctas=0 if last else self.peer_store_ctas,
+                                       x_ready=x_ready if s == 0 else None):
                 if s == 0:
+                    if x_ready is not None:
+                        x_ready(None)
                     return None
                 raise RuntimeError("row block cannot be stored to the peers")
         if side is not None:
@@ -266,13 +294,17 @@ class RowPartitionedCsr:
         out_local.  Returns the assembled y on every rank.  After enable_peer_gather the result
         is the symmetric-memory buffer that call returned (the next product overwrites it); an
         `out` that is another tensor receives a copy."""
-        self.broadcast_dense(x, src)
         peer = self._peer
         if peer is not None and peer["trailing"] == () and peer["dtype"] == x.dtype \
                 and self.local_spmv is _default_local_spmv:
-            done = self._peer_spmv(x, out_local, alpha, beta)
+            x_ready = self.broadcast_by_panel(x, src) if self.pipeline_broadcast else None
+            if x_ready is None:
+                self.broadcast_dense(x, src)
+            done = self._peer_spmv(x, out_local, alpha, beta, x_ready)
             if done is not None:
                 return self._into(out, done)
+        else:
+            self.broadcast_dense(x, src)
         if getattr(self, "_stages", None):
             return self._pipelined(self.local_spmv, x, out_local, out, alpha, beta)
         y_local = self.spmv_local(x, out=out_local, alpha=alpha, beta=beta)

@@ -284,22 +284,47 @@ def _spmv_launch_record(plan: CsrPlan):
     return rec
 
 
-def _launch_stack_partials(plan, lay, x, stream):
+def _launch_stack_partials(plan, lay, x, stream, x_ready=None):
     """Enqueue the kernels that fill the partials the combine adds: the wide-panel stack kernel
     (one value per (panel, row) with entries) and, when the long rows were taken out, the
-    shared-memory kernel over their narrow panels, whose per-row sums go behind the others."""
+    shared-memory kernel over their narrow panels, whose per-row sums go behind the others.
+
+    x_ready (several GPUs, x arriving slice by slice): callable; x_ready(p) makes the current
+    stream wait until the columns of panels 0..p are in place, x_ready(None) until all of x is.
+    The wide-panel kernel is then launched panel by panel, each launch behind its own slice."""
     lib = _lib.load()
     lr = lay.long_rows
     n_extra = 0 if lr is None else lr.n_long
     ypart = plan.scratch_on("spmv_panel_part", lay.n_stacked + n_extra, stream)
     carry = plan.scratch_on("spmv_stack_carry", lay.n_tiles, stream)
-    st = lib.b2s_spmv_stack(
-        plan.vcode, _lib.ptr(lay.vals), _lib.ptr(lay.cols), lay.n_entries, lay.n_stacked,
-        plan.n_cols, lay.n_panels, lay.shift, _lib.ptr(lay.panel_start),
-        _lib.ptr(lay.tile_panel), _lib.ptr(lay.tile_ord), _lib.ptr(x), _lib.ptr(ypart),
-        _lib.ptr(carry), _lib.ptr(plan.status), stream)
-    if st:
-        _lib.check(st, "b2s_spmv_stack")
+    if x_ready is None or lay.n_panels < 2:
+        if x_ready is not None:
+            x_ready(None)
+        st = lib.b2s_spmv_stack(
+            plan.vcode, _lib.ptr(lay.vals), _lib.ptr(lay.cols), lay.n_entries, lay.n_stacked,
+            plan.n_cols, lay.n_panels, lay.shift, _lib.ptr(lay.panel_start),
+            _lib.ptr(lay.tile_panel), _lib.ptr(lay.tile_ord), _lib.ptr(x), _lib.ptr(ypart),
+            _lib.ptr(carry), _lib.ptr(plan.status), stream)
+        if st:
+            _lib.check(st, "b2s_spmv_stack")
+    else:
+        bounds = lay.panel_tile_bounds()
+        t0 = 0
+        for p in range(lay.n_panels):
+            x_ready(p)
+            t1 = bounds[p]
+            last = p + 1 == lay.n_panels
+            if t1 > t0 or last:
+                st = lib.b2s_spmv_stack_tiles(
+                    plan.vcode, _lib.ptr(lay.vals), _lib.ptr(lay.cols), lay.n_entries,
+                    lay.n_stacked, plan.n_cols, lay.n_panels, lay.shift,
+                    _lib.ptr(lay.panel_start), _lib.ptr(lay.tile_panel), _lib.ptr(lay.tile_ord),
+                    _lib.ptr(x), _lib.ptr(ypart), _lib.ptr(carry), _lib.ptr(plan.status),
+                    t0, t1 - t0, 1 if last else 0, stream)
+                if st:
+                    _lib.check(st, "b2s_spmv_stack_tiles")
+            t0 = t1
+        x_ready(None)
     if lr is not None:
         part = plan.scratch_on("spmv_long_part", lr.n_stacked, stream)
         carry_l = plan.scratch_on("spmv_long_carry", lr.n_tiles, stream)
@@ -358,7 +383,7 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
 
 
 def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row_offset,
-                        peer_rows, store_stream=None, store_ctas=0):
+                        peer_rows, store_stream=None, store_ctas=0, x_ready=None):
     """Several GPUs: multiply this rank's row block and store the result block at rows
     [row_offset, row_offset + n_rows) of the y buffer (peer_rows rows) of every rank
     (`peer_array`: ctypes array of the n_peers device pointers, own buffer included).  On the
@@ -372,7 +397,8 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     that stream, ordered after this block's tile kernel by an event, so that the caller can go
     on launching the next block on the current stream while the stores drain over NVLink.
     store_ctas > 0 caps that kernel's grid (CTAs of 256 threads); together with a high-priority
-    store_stream a small grid runs beside the next block's tile kernel."""
+    store_stream a small grid runs beside the next block's tile kernel.
+    x_ready: see _launch_stack_partials (x still arriving slice by slice when this is called)."""
     plan = prepared.plan()
     lib = _lib.load()
     rec = _spmv_launch_record(plan)
@@ -383,12 +409,14 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     fused = rec[0] == "stack"   # the combine kernel itself stores to the peers
     if not fused and ((plan.n_rows * itemsize) % 16 or (row_offset * itemsize) % 16):
         return False
+    if not fused and x_ready is not None:
+        x_ready(None)
     a, b = _scalar(alpha, dtype), _scalar(beta, dtype)
     with torch.cuda.device(plan.device):
         stream = torch.cuda.current_stream(plan.device).cuda_stream
         if fused:
             lay = rec[1]
-            ypart = _launch_stack_partials(plan, lay, x, stream)
+            ypart = _launch_stack_partials(plan, lay, x, stream, x_ready)
             target = stream
             if store_stream is not None:
                 done = torch.cuda.Event()

@@ -189,6 +189,10 @@ int b2s_panel_build_global(int val_type, int idx_type, int ptr_type,
  * b2s_spmv_stack: wide panels (n_panels <= 256 of 2^panel_shift columns, the x slice of a panel
  * sized for L2); panel_start_dev[p] = first entry of panel p (n_panels + 1 entries),
  * tile_panel_dev[t] = panel of the first entry of tile t; both may be NULL when n_panels == 1.
+ * b2s_spmv_stack_tiles is the same kernel over tiles [tile_begin, tile_begin + tile_count)
+ * only, with the carry fix-up (which needs every tile done) run when run_fixup != 0: a caller
+ * whose x arrives slice by slice launches the tiles of a panel as soon as that panel's slice of
+ * x is in place and asks for the fix-up with the last range.
  *
  * b2s_spmv_stack_shared: narrow panels of 2^panel_shift <= b2s_spmv_stack_shared_cols(val_type)
  * columns for the long rows of a matrix.  Every panel is padded to whole tiles; CTA u copies
@@ -212,6 +216,13 @@ int b2s_spmv_stack(int val_type, const void* s_data_dev, const uint32_t* s_cols_
                    const int32_t* tile_panel_dev, const int64_t* tile_ord_dev,
                    const void* x_dev, void* ypart_dev, void* carry_dev, int32_t* status_dev,
                    b2s_stream stream);
+int b2s_spmv_stack_tiles(int val_type, const void* s_data_dev, const uint32_t* s_cols_dev,
+                         int64_t n_entries, int64_t n_stacked, int64_t n_cols, int n_panels,
+                         int panel_shift, const int64_t* panel_start_dev,
+                         const int32_t* tile_panel_dev, const int64_t* tile_ord_dev,
+                         const void* x_dev, void* ypart_dev, void* carry_dev,
+                         int32_t* status_dev, int64_t tile_begin, int64_t tile_count,
+                         int run_fixup, b2s_stream stream);
 int b2s_spmv_stack_shared(int val_type, const void* s_data_dev, const uint32_t* s_cols_dev,
                           int64_t n_entries, int64_t n_stacked, int64_t n_cols, int panel_shift,
                           const int32_t* unit_dev, int64_t n_units,

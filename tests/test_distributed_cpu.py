@@ -131,6 +131,42 @@ def test_staged_block_cyclic_gather_on_two_gloo_ranks():
         assert results[0] and results[1]
 
 
+def _panel_broadcast_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flagsparse_b200._plan import panel_shift
+        from flagsparse_b200.distributed import RowPartitionedCsr
+        data, idx, ptr, shape = _matrix()
+        part = RowPartitionedCsr(torch.from_numpy(data), torch.from_numpy(idx),
+                                 torch.from_numpy(ptr), shape[1], local_spmv=_oracle_spmv)
+        width = 1 << panel_shift(torch.float64)
+        n = 2 * width + 1000                      # three slices, the last one ragged
+        ref = torch.arange(n, dtype=torch.float64)
+        x = ref.clone() if rank == 0 else torch.zeros(n, dtype=torch.float64)
+        ready = part.broadcast_by_panel(x, src=0)
+        ok = ready is not None
+        ready(0)
+        ok = ok and bool(torch.equal(x[:width], ref[:width]))
+        ready(0)                                  # asking again is harmless
+        ready(None)
+        ok = ok and bool(torch.equal(x, ref))
+        # x no wider than one panel: one ordinary broadcast is the better call
+        ok = ok and part.broadcast_by_panel(torch.zeros(100, dtype=torch.float64)) is None
+        results[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_broadcast_by_panel_delivers_x_slice_by_slice_on_two_gloo_ranks():
+    world = 2
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_panel_broadcast_worker, args=(world, _free_port(), results), nprocs=world,
+                 join=True)
+        assert results[0] and results[1]
+
+
 def _free_port():
     import socket
     with socket.socket() as s:

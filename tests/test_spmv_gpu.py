@@ -12,6 +12,11 @@ from gpu_util import TORCH_OF, assert_parity, csr_from_lengths, dev, host, rando
 
 pytestmark = pytest.mark.gpu
 
+
+def _lib_mod():
+    from flagsparse_b200 import _lib
+    return _lib
+
 SPMV_CASES = sorted(load_golden("spmv_reference.npz"))
 DTYPES = [np.float32, np.float64, np.complex64, np.complex128]
 
@@ -320,6 +325,53 @@ def test_spmv_long_rows_from_shared_memory_slices(monkeypatch, dtype, idx_dtype,
     out2 = dev(y0)
     flagsparse_spmv_csr(*args, out=out2, alpha=alpha, beta=beta)
     assert torch.equal(out.view(torch.uint8), out2.view(torch.uint8))
+    clear_plan_cache()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: np.dtype(d).name)
+def test_spmv_stack_launched_panel_by_panel_equals_one_launch(monkeypatch, dtype):
+    """Several GPUs receive x one column panel at a time and launch the wide-panel kernel once
+    per panel (b2s_spmv_stack_tiles), each launch behind the arrival of its slice.  Here the
+    arrival hook only records its calls: the partial sums must equal those of the single launch
+    bit for bit, panels must be asked for in ascending order and all of x at the end."""
+    import flagsparse_b200._plan as plan_mod
+    from flagsparse_b200 import clear_plan_cache, prepare_spmv_csr
+    from flagsparse_b200.spmv import _launch_stack_partials, _spmv_launch_record
+    monkeypatch.setattr(plan_mod, "PANEL_TRIGGER_BYTES", 0)
+    monkeypatch.setattr(plan_mod, "PANEL_TARGET_BYTES", 1024 * np.dtype(dtype).itemsize)
+    monkeypatch.setattr(plan_mod, "PANEL_MIN_NNZ", 0)
+    clear_plan_cache()
+    rng = np.random.default_rng(77)
+    lengths = np.concatenate([rng.integers(0, 40, 2500), [3000, 0, 1]])
+    n_rows, n_cols = lengths.size, 5000
+    data, idx, ptr = csr_from_lengths(rng, lengths, n_cols, dtype, sort=False)
+    d, i, p = dev(data), dev(idx, torch.int64), dev(ptr, torch.int64)
+    x = dev(random_values(rng, n_cols, dtype))
+    plan = prepare_spmv_csr(d, i, p, (n_rows, n_cols)).plan()
+    rec = _spmv_launch_record(plan)
+    assert rec[0] == "stack"
+    lay = rec[1]
+    assert lay.n_panels >= 4
+    bounds = lay.panel_tile_bounds()
+    assert len(bounds) == lay.n_panels and bounds[-1] == lay.n_tiles
+    assert all(a <= b for a, b in zip(bounds, bounds[1:]))
+    stream = torch.cuda.current_stream().cuda_stream
+    whole = _launch_stack_partials(plan, lay, x, stream).clone()
+    asked = []
+    piecewise = _launch_stack_partials(plan, lay, x, stream, x_ready=asked.append)
+    torch.cuda.synchronize()
+    assert asked == list(range(lay.n_panels)) + [None]
+    assert torch.equal(whole.view(torch.uint8), piecewise.view(torch.uint8))
+    # ranges the C entry point refuses
+    lib = _lib_mod().load()
+    L = _lib_mod()
+    carry = plan.scratch_on("spmv_stack_carry", lay.n_tiles, stream)
+    st = lib.b2s_spmv_stack_tiles(
+        plan.vcode, L.ptr(lay.vals), L.ptr(lay.cols), lay.n_entries, lay.n_stacked, plan.n_cols,
+        lay.n_panels, lay.shift, L.ptr(lay.panel_start), L.ptr(lay.tile_panel),
+        L.ptr(lay.tile_ord), L.ptr(x), L.ptr(whole), L.ptr(carry), L.ptr(plan.status),
+        lay.n_tiles - 1, 2, 1, stream)
+    assert st == 2   # B2S_ERR_ARG: the range runs past the last tile
     clear_plan_cache()
 
 
