@@ -743,7 +743,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
         args.stages = 1 if world < 4 else 2
     if args.store_ctas >= 0:
         part.peer_store_ctas = args.store_ctas
-    part.pipeline_broadcast = not args.no_pipelined_broadcast
+    part.pipeline_broadcast = bool(args.pipelined_broadcast)
     staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
     gather_mode = args.gather
@@ -943,8 +943,9 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
                     help="N > 1: how y / C is assembled -- NCCL all-gather, or stores of the last "
                          "kernel into every rank's symmetric-memory buffer")
-    ap.add_argument("--no-pipelined-broadcast", action="store_true",
-                    help="N > 1: broadcast x in one piece before the first kernel")
+    ap.add_argument("--pipelined-broadcast", action="store_true",
+                    help="N > 1: broadcast x one column panel at a time, the kernel of a panel "
+                         "starting when its slice has landed (default: one broadcast first)")
     ap.add_argument("--no-cfg5", action="store_true",
                     help="N > 1: skip the partitioned 2^26-row matrix in extra.cfg5")
     ap.add_argument("--cfg5-scale", type=int, default=1,

@@ -671,6 +671,10 @@ class CsrPlan:
         examined at the next call, so that an error bit set later (a bounded wait that ran
         out, a bounds violation in the checked build) still raises, without a host
         synchronisation on the steady-state path."""
+        if torch.cuda.is_current_stream_capturing():
+            # inside a CUDA graph capture neither a copy to the host nor an event query is
+            # allowed; the word is read again by the first launch outside the capture
+            return
         if not self.status_checked:
             self.check_status()
             return

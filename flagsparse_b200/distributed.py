@@ -72,9 +72,11 @@ class RowPartitionedCsr:
         # CTAs (of 256 threads) of a combine + store kernel that drains beside the tile kernel
         # of the next stage; 0 = one thread per row
         self.peer_store_ctas = 2 * 148
-        # SpMV with the peer gather: x is broadcast one column panel at a time and the kernel of
-        # a panel starts when its slice has landed
-        self.pipeline_broadcast = True
+        # SpMV with the peer gather: broadcast x one column panel at a time and start the kernel
+        # of a panel when its slice has landed.  Off by default: on 2 GPUs the four small
+        # broadcasts and their waits cost more than the 0.2 ms of broadcast they hide
+        # (1.75 ms against 1.69 ms per step).
+        self.pipeline_broadcast = False
 
     @classmethod
     def from_global(cls, data, indices, indptr, shape, group=None, **kw):
