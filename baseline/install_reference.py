@@ -1,5 +1,6 @@
-"""Install the unmodified FlagSparse package, and the two accuracy suites of its own test tree
-that cover CSR SpMV / SpMM, under baseline/_ref (git-ignored; never committed).
+"""Install the unmodified FlagSparse package, and the accuracy suites of its own test tree that
+cover CSR SpMV / SpMM and the COO -> CSR front door, under baseline/_ref (git-ignored; never
+committed).
 
     python baseline/install_reference.py <path of a FlagSparse checkout>
 
@@ -21,7 +22,8 @@ DEST = Path(__file__).resolve().parent / "_ref"
 
 # tests/pytest/ of the checkout: the two suites and what they import
 SUITE_FILES = ("__init__.py", "conftest.py", "accuracy_utils.py", "param_shapes.py",
-               "test_spmv_csr_accuracy.py", "test_spmm_csr_accuracy.py")
+               "test_spmv_csr_accuracy.py", "test_spmm_csr_accuracy.py",
+               "test_spmv_coo_accuracy.py")
 
 
 def install_package(checkout: Path) -> None:

@@ -87,7 +87,7 @@ __all__ = [
 
 _PATCHED_NAMES = ("flagsparse_spmv_csr", "flagsparse_spmm_csr", "prepare_spmv_csr",
                   "PreparedCsrSpmv", "prepare_spmm_csr_route", "flagsparse_spmm_csr_run",
-                  "PreparedCsrSpmmRoute")
+                  "PreparedCsrSpmmRoute", "flagsparse_spmv_coo_tocsr", "prepare_spmv_coo_tocsr")
 
 
 def install(flagsparse_module=None, replace_modules=False):

@@ -8,7 +8,7 @@ calls ``install(replace_modules=True)``, so every name the suites touch resolves
 package.  The suites and the unmodified package come from baseline/_ref, which
 baseline/install_reference.py fills from a FlagSparse checkout; without it the tests skip.
 
-Selection is by the suites' own markers: ``spmv_csr`` and ``spmm_csr``.  The cases marked
+Selection is by the suites' own markers: ``spmv_csr``, ``spmm_csr`` and ``spmv_coo_tocsr``.  The cases marked
 ``spmm_csr_opt`` exercise FlagSparse's separate "opt" entry points, which install() leaves alone.
 """
 
@@ -58,3 +58,11 @@ def test_flagsparse_spmm_csr_accuracy_suite_passes_unmodified():
     # behaviour cases (timing meta of the transpose path, of the plain path, argument errors)
     passed, tail = _run_suite("test_spmm_csr_accuracy.py", "spmm_csr")
     assert passed == 2 * 4 + 2 * 4 * 2 * 3 + 3, tail
+
+
+def test_flagsparse_coo_tocsr_cases_of_the_coo_suite_pass_unmodified():
+    # the COO -> CSR front door (flagsparse_spmv_coo_tocsr / prepare_spmv_coo_tocsr), which feeds
+    # the CSR kernels: 3 shapes x 2 value types against torch, and the prepared path.  The
+    # suite's other cases exercise FlagSparse's COO kernels, which install() leaves alone.
+    passed, tail = _run_suite("test_spmv_coo_accuracy.py", "spmv_coo_tocsr")
+    assert passed == 3 * 2 + 1, tail
