@@ -668,10 +668,19 @@ def cfg5_extra(args, rank, world, device, timed):
     for kind, dense in (("spmv", g.x), ("spmm", g.B)):
         n = 1 if kind == "spmv" else int(dense.shape[1])
         trailing = () if kind == "spmv" else (n,)
+        if kind == "spmm":      # a partition object holds one assembled-result buffer
+            part = RowPartitionedCsr.from_global(g.data, g.indices, g.indptr, g.shape)
+        out_local = torch.empty((part.n_local, *trailing), dtype=g.data.dtype, device=device)
+        out_full, mode = None, "nccl"
+        if args.gather == "peer":
+            try:    # collective: raises on every rank or on none
+                out_full, mode = part.enable_peer_gather(g.data.dtype, trailing), "peer"
+            except RuntimeError as exc:
+                print(f"[rank {rank}] cfg5 {kind}: {exc}", file=sys.stderr, flush=True)
+        if out_full is None:
+            out_full = torch.empty((n_rows, *trailing), dtype=g.data.dtype, device=device)
         op = part.spmv if kind == "spmv" else part.spmm
         local = part.spmv_local if kind == "spmv" else part.spmm_local
-        out_local = torch.empty((part.n_local, *trailing), dtype=g.data.dtype, device=device)
-        out_full = torch.empty((n_rows, *trailing), dtype=g.data.dtype, device=device)
 
         def step():
             return op(dense, src=0, out_local=out_local, out=out_full)
@@ -698,11 +707,11 @@ def cfg5_extra(args, rank, world, device, timed):
         out[kind] = {
             "ms_per_step": per_step * 1e3, "job_gbs": nbytes / per_step / 1e9,
             "per_gpu_kernel_gbs": per_gpu / (phases["kernel_ms"] / 1e3) / 1e9,
-            "algorithmic_bytes": nbytes, "phases": phases,
+            "algorithmic_bytes": nbytes, "phases": phases, "gather": mode,
             "rel_l2_vs_torch_own_and_next_block": float(errs.item()),
             "parity_ok": bool(float(errs.item()) <= REL_L2_TOL[g.data.dtype]),
         }
-        del out_local, out_full, full
+        del out_local, out_full, full, part, op, local
         torch.cuda.empty_cache()
     return out
 
