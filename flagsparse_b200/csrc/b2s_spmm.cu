@@ -22,6 +22,9 @@ namespace b2s {
 #ifndef B2S_SPMM_CHUNK_WIDE
 #define B2S_SPMM_CHUNK_WIDE 16  // chunk length of the chunk kernel when B rows take more than 4 lanes
 #endif
+#ifndef B2S_SPMM_RUN_MEAN
+#define B2S_SPMM_RUN_MEAN 12  // mean entries per row piece of a tile up to which groups walk runs of rows
+#endif
 #ifndef B2S_SPMM_WIN_MINBLOCKS
 #define B2S_SPMM_WIN_MINBLOCKS 6  // CTAs per SM the float32 / int32 windowed kernel is compiled for
 #endif
@@ -310,6 +313,31 @@ __device__ inline void accumulate(Pack<V, S>& acc, const I* __restrict__ scol,
   }
 }
 
+// Bounds-checked build: every staged column must name a row of B (and, with a window, a row of
+// the window), every staged row end must lie inside the tile and not before the previous one.
+// A tile that fails sets B2S_ERR_BOUNDS and is skipped by the whole CTA.
+#ifdef B2S_CHECKED
+template <class I>
+__device__ inline bool spmm_tile_is_sound(const I* scol, const int* row_end, int n_nz, int n_end,
+                                          int64_t n_cols, int64_t lo, int64_t hi, int tid,
+                                          int threads, int32_t* status) {
+  int bad = 0;
+  for (int j = tid; j < n_nz; j += threads) {
+    const int64_t c = static_cast<int64_t>(scol[j]);
+    if (c < 0 || c >= n_cols || c < lo || c >= hi) bad = 1;
+  }
+  for (int k = tid; k <= n_end; k += threads) {
+    const int e = row_end[k], s = k ? row_end[k - 1] : 0;
+    if (e < s || e > n_nz || s < 0) bad = 1;
+  }
+  if (__syncthreads_or(bad)) {
+    if (status && tid == 0) atomicOr(status, 1 << B2S_ERR_BOUNDS);
+    return false;
+  }
+  return true;
+}
+#endif
+
 // ---- float32 / int32 window path ---------------------------------------------------------------
 // The staged columns and values of the tile and its window of B rows are all in shared memory;
 // everything is addressed with 32-bit shared addresses (one multiply-add per gather, no generic
@@ -413,7 +441,8 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
                  const ST* __restrict__ B, int64_t ldb, int64_t n_dense, const ST* C_in, ST* C,
                  int64_t ldc, int64_t cs, V* __restrict__ carry, V* __restrict__ first_part,
                  const int64_t* __restrict__ tile_row,
-                 int64_t n_rows, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int small_b,
+                 int64_t n_rows, int64_t n_cols, int64_t nnz, V alpha, V beta, int has_beta_i,
+                 int G, int small_b,
                  int vec_c, int32_t* status, int win_rows_cap = 0,
                  const int32_t* __restrict__ tile_win = nullptr) {
   static_assert(!WIN || VEC, "the shared-memory window is read with 16-byte loads");
@@ -496,6 +525,13 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
 
   const I* scol = sc.s;
   const ST* sval = sv.s;
+#ifdef B2S_CHECKED
+  if (!spmm_tile_is_sound(scol, row_end, n_nz, n_end, n_cols,
+                          WIN ? static_cast<int64_t>(win_lo) : 0,
+                          WIN ? static_cast<int64_t>(win_lo) + win_rows : n_cols, tid, THREADS,
+                          status))
+    return;
+#endif
   const bool open_row = tc.r1 < n_rows;
   const int n_seg = n_end + 1;
   const int64_t e0 =
@@ -547,8 +583,114 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
   const int team = S * G;  // lanes per row piece
   const int p1max = (S == groups_per_warp) ? kSpmmWarpRowMax : 64 * S;
 
-  // ---- strategy 1: one team of S groups per row piece ---------------------------------------
-  {
+  // ---- strategy 1 for short rows: one group per run of consecutive row pieces ------------------
+  // With a handful of entries per row a group that takes one row at a time has one or two
+  // gathers in flight.  Here the row pieces and entries of the tile are dealt out in equal
+  // shares of their merged sequence, whole pieces only; a group walks the entries of its pieces
+  // as one run, four gathers in flight across row borders, and stores a row whenever the run
+  // passes its end.  Sums are taken in entry order, as in the loop below.  Pieces longer than
+  // p1max are left to the warp / CTA strategies as before.
+  bool run_walk = false;
+  if constexpr (VEC && !WIN && std::is_same<ST, V>::value) {
+    // measured on the short-row part of the 2^24-row power-law matrix, N = 32 float64 (16
+    // lanes per row): 11.7 -> 11.0 ms for the whole product; with 4 lanes per row (N = 16
+    // float32, 2^26-row matrix) the walk was 4 % slower, so narrow rows keep the loop below
+    run_walk = S == 1 && stride16 < 0 && G >= 8 &&
+               (n_nz + n_seg - 1) / n_seg <= B2S_SPMM_RUN_MEAN;
+  }
+  if (run_walk) {
+    if constexpr (VEC && !WIN && std::is_same<ST, V>::value) {
+      const int team_id = tid / G;
+      const int n_team = THREADS / G;
+      const int total = n_seg + n_nz;
+      auto first_piece = [&](int m) {   // first piece k with k + (its first entry) >= m
+        int a = 0, b = n_seg;
+        while (a < b) {
+          const int mid = (a + b) >> 1;
+          if (mid + (mid ? row_end[mid - 1] : 0) < m) a = mid + 1; else b = mid;
+        }
+        return a;
+      };
+      int k = first_piece(static_cast<int>(static_cast<int64_t>(total) * team_id / n_team));
+      const int kend =
+          first_piece(static_cast<int>(static_cast<int64_t>(total) * (team_id + 1) / n_team));
+      const uint32_t s32 = static_cast<uint32_t>(-stride16);
+      const bool owner = e0 < n_dense;            // lanes beyond the last column only follow
+      auto flush = [&](int kk, const Pack<V, ST>& sum) {
+        if (!owner) return;
+        if (kk < n_end) {
+          const int64_t r = tc.r0 + kk;
+          store_pack(C + r * ldc, C_in + r * ldc, e0, n_dense, sum, alpha, beta, has_beta, vc, cs);
+        } else if (open_row) {
+          store_raw(carry_row, e0, n_dense, sum);
+        }
+      };
+      int i = k ? row_end[k - 1] : 0;
+      int stretch_end = i;                        // entries before it belong to short pieces
+      int e_k = k < kend ? row_end[k] : 0;
+      bool at_start = true;
+      Pack<V, ST> acc = pack_zero<V, ST>();
+      while (k < kend) {
+        if (at_start) {
+          if (i >= stretch_end) {
+            if (e_k - i > p1max) {                // a long piece: queued, skipped here
+              if ((tid & (G - 1)) == 0) {
+                if (e_k - i <= kSpmmWarpRowMax) {
+                  const int q = atomicAdd(&qcount[0], 1);
+                  if (q < kSpmmQueue2Cap) queue2[q] = k;
+                } else {
+                  const int q = atomicAdd(&qcount[1], 1);
+                  if (q < kSpmmQueue3Cap) queue3[q] = k;
+                }
+              }
+              i = e_k;
+              ++k;
+              e_k = k < kend ? row_end[k] : 0;
+              stretch_end = i;
+              continue;
+            }
+            int j = k, pos = i;
+            while (j < kend) {
+              const int ej = row_end[j];
+              if (ej - pos > p1max) break;
+              pos = ej;
+              ++j;
+            }
+            stretch_end = pos;
+          }
+          if (e_k == i) {                         // an empty piece
+            flush(k, acc);
+            ++k;
+            e_k = k < kend ? row_end[k] : 0;
+            continue;
+          }
+        }
+        const int n = min(4, stretch_end - i);    // >= 1: piece k has an entry at i
+        const int last = stretch_end - 1;
+        const int i1 = min(i + 1, last), i2 = min(i + 2, last), i3 = min(i + 3, last);
+        Pack<V, ST> b[4];
+        b[0] = unpack16<V, ST>(__ldg(Bv + static_cast<uint32_t>(scol[i]) * s32));
+        b[1] = unpack16<V, ST>(__ldg(Bv + static_cast<uint32_t>(scol[i1]) * s32));
+        b[2] = unpack16<V, ST>(__ldg(Bv + static_cast<uint32_t>(scol[i2]) * s32));
+        b[3] = unpack16<V, ST>(__ldg(Bv + static_cast<uint32_t>(scol[i3]) * s32));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < n) {
+            fma_pack(acc, to_acc(sval[i + j]), b[j]);
+            at_start = false;
+            while (k < kend && e_k == i + j + 1) {   // the piece ends here (and empty ones follow)
+              flush(k, acc);
+              acc = pack_zero<V, ST>();
+              ++k;
+              e_k = k < kend ? row_end[k] : 0;
+              at_start = true;
+            }
+          }
+        }
+        i += n;
+      }
+    }
+  } else {
     const int team_id = tid / team;
     const int n_team = THREADS / team;
     const int grp_in_team = (tid % team) / G;
@@ -678,7 +820,8 @@ spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
                   const P* __restrict__ ptr, const V* __restrict__ B, int64_t ldb,
                   int64_t n_dense, const V* C_in, V* C, int64_t ldc, int64_t cs,
                   V* __restrict__ carry, const int64_t* __restrict__ tile_row, int64_t n_rows,
-                  int64_t nnz, V alpha, V beta, int has_beta_i, int G, int CH, int vec_c,
+                  int64_t n_cols, int64_t nnz, V alpha, V beta, int has_beta_i, int G, int CH,
+                  int vec_c,
                   int32_t* status) {
   extern __shared__ __align__(16) unsigned char smem[];
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
@@ -724,6 +867,10 @@ spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
     }
   }
   __syncthreads();
+#ifdef B2S_CHECKED
+  if (!spmm_tile_is_sound(sc.s, row_end, n_nz, n_end, n_cols, 0, n_cols, tid, THREADS, status))
+    return;
+#endif
 
   const I* scol = sc.s;
   const V* sval = sv.s;
@@ -985,7 +1132,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
           static_cast<const S*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const S*>(B), ldb, n_dense,
           static_cast<const S*>(C_in), static_cast<S*>(C), ldc, cs, static_cast<V*>(carry),
-          first_part, tile_row, n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0,
+          first_part, tile_row, n_rows, n_cols, nnz, a, b, has_beta, G, small_b, vec_c, status, 0,
           nullptr);
     };
     if (vec)
@@ -1015,7 +1162,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
           static_cast<const V*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
           static_cast<const V*>(C_in), static_cast<V*>(C), ldc, cs, static_cast<V*>(carry),
-          tile_row, n_rows, nnz, a, b, has_beta, G, CH, vec_c, status);
+          tile_row, n_rows, n_cols, nnz, a, b, has_beta, G, CH, vec_c, status);
     };
     if (vec)
       launch(spmm_chunk_kernel<V, I, P, THREADS, ITEMS, true>);
@@ -1032,7 +1179,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
         static_cast<const V*>(data), static_cast<const I*>(indices),
         static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
         static_cast<const V*>(C_in), static_cast<V*>(C), ldc, cs, static_cast<V*>(carry),
-        first_part, tile_row, n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status,
+        first_part, tile_row, n_rows, n_cols, nnz, a, b, has_beta, G, small_b, vec_c, status,
         static_cast<int>(window_rows), tile_win);
   } else {
     constexpr size_t smem = spmm_smem_bytes<THREADS, ITEMS, V, I>();
@@ -1042,7 +1189,7 @@ int spmm_launch(const void* data, const void* indices, const void* indptr, int64
           static_cast<const V*>(data), static_cast<const I*>(indices),
           static_cast<const P*>(indptr), static_cast<const V*>(B), ldb, n_dense,
           static_cast<const V*>(C_in), static_cast<V*>(C), ldc, cs, static_cast<V*>(carry),
-          first_part, tile_row, n_rows, nnz, a, b, has_beta, G, small_b, vec_c, status, 0,
+          first_part, tile_row, n_rows, n_cols, nnz, a, b, has_beta, G, small_b, vec_c, status, 0,
           nullptr);
     };
     if (vec)
