@@ -672,7 +672,8 @@ def cfg5_extra(args, rank, world, device, timed):
             part = RowPartitionedCsr.from_global(g.data, g.indices, g.indptr, g.shape)
         out_local = torch.empty((part.n_local, *trailing), dtype=g.data.dtype, device=device)
         out_full, mode = None, "nccl"
-        if args.gather == "peer":
+        if args.gather in ("peer", "dma"):
+            part.peer_transfer = "dma" if args.gather == "dma" else "stores"
             try:    # collective: raises on every rank or on none
                 out_full, mode = part.enable_peer_gather(g.data.dtype, trailing), "peer"
             except RuntimeError as exc:
@@ -755,7 +756,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     part.pipeline_broadcast = bool(args.pipelined_broadcast)
     staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
-    gather_mode = args.gather
+    gather_mode = "peer" if args.gather == "dma" else args.gather
+    part.peer_transfer = "dma" if args.gather == "dma" else "stores"
     if gather_mode == "peer":
         # the last kernel of every rank stores its block into all ranks' result buffers; if
         # symmetric memory cannot be set up on any rank, every rank falls back to NCCL
@@ -893,12 +895,17 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                               "column panel; the kernel of a panel starts when its slice has "
                               "landed" if pipelined_bcast else
                               "NCCL broadcast of x / B from rank 0"),
-                "gather": ("stores of each rank's last kernel into every rank's "
-                           "symmetric-memory result buffer over NVLink, then a one-element "
-                           "NCCL all-reduce as the end-of-step fence"
+                "gather": (("each rank's last kernel writes its block into its own "
+                            "symmetric-memory result buffer and the copy engines take it to "
+                            "every other rank's buffer over NVLink (one asynchronous copy per "
+                            "peer)" if part.peer_transfer == "dma" and kind == "spmv" else
+                            "stores of each rank's last kernel into every rank's "
+                            "symmetric-memory result buffer over NVLink")
+                           + ", then a one-element NCCL all-reduce as the end-of-step fence"
                            if gather_mode == "peer" else "NCCL all-gather of y / C"),
                 "inside_timed_step": True, "stages": args.stages if staged else 1,
-                "mode": gather_mode, "store_ctas": part.peer_store_ctas},
+                "mode": args.gather if gather_mode == "peer" else gather_mode,
+                "store_ctas": part.peer_store_ctas},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
                          "peak_kind": peak_kind,
@@ -949,9 +956,11 @@ def main():
                          "of the next (1 = no overlap; 0 = 1 below four GPUs, 2 from four on: "
                          "measured 2.11 ms with 1 stage on 2 GPUs, 2.49 ms with 2 stages against "
                          "2.59 ms with 4 on 4 GPUs)")
-    ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
-                    help="N > 1: how y / C is assembled -- NCCL all-gather, or stores of the last "
-                         "kernel into every rank's symmetric-memory buffer")
+    ap.add_argument("--gather", default="peer", choices=["nccl", "peer", "dma"],
+                    help="N > 1: how y / C is assembled -- NCCL all-gather; stores of the last "
+                         "kernel into every rank's symmetric-memory buffer (peer); or the last "
+                         "kernel writes this rank's buffer and the copy engines move the block "
+                         "to the other ranks (dma)")
     ap.add_argument("--pipelined-broadcast", action="store_true",
                     help="N > 1: broadcast x one column panel at a time, the kernel of a panel "
                          "starting when its slice has landed (default: one broadcast first)")

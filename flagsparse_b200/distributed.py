@@ -72,6 +72,10 @@ class RowPartitionedCsr:
         # CTAs (of 256 threads) of a combine + store kernel that drains beside the tile kernel
         # of the next stage; 0 = one thread per row
         self.peer_store_ctas = 2 * 148
+        # how a finished block reaches the other ranks' copies of the result: 'stores' (the
+        # last kernel stores into every copy itself) or 'dma' (it writes this rank's copy and
+        # the copy engines move the block, leaving the SMs to the next block)
+        self.peer_transfer = "stores"
         # SpMV with the peer gather: broadcast x one column panel at a time and start the kernel
         # of a panel when its slice has landed.  Off by default: on 2 GPUs the four small
         # broadcasts and their waits cost more than the 0.2 ms of broadcast they hide
@@ -184,12 +188,54 @@ class RowPartitionedCsr:
         self._peer = {
             "full": full, "handle": hdl, "n": self.world,
             "array": (ctypes.c_void_p * self.world)(*ptrs),
+            "array_self": (ctypes.c_void_p * 1)(ptrs[self.rank]),
+            "views": self._peer_views(hdl, full, trailing, dtype),
             "flag": torch.zeros(1, dtype=torch.int32, device=dev),
             "trailing": tuple(int(t) for t in trailing), "dtype": dtype,
             "row_bytes": row_items * full.element_size(),
         }
         dist.barrier(group=self.group)
         return full
+
+    def _peer_views(self, hdl, full, trailing, dtype):
+        """Tensors over every rank's copy of the assembled result (for copies by the copy
+        engines, peer_transfer = 'dma'), or None when the handle does not hand them out or its
+        view of this rank's copy is not the buffer itself."""
+        try:
+            start = int(getattr(hdl, "offset", 0) or 0) // full.element_size()
+            views = [hdl.get_buffer(q, tuple(full.shape), dtype, start)
+                     for q in range(self.world)]
+            if views[self.rank].data_ptr() != full.data_ptr():
+                return None
+            return views
+        except Exception:  # noqa: BLE001 - the store route does not need them
+            return None
+
+    def _dma_block(self, row_offset, rows):
+        """Copy rows [row_offset, row_offset + rows) of this rank's assembled result to the same
+        rows of every other rank's copy: one asynchronous device-to-device copy per peer, each
+        on a stream of its own behind the kernels enqueued so far, so that the copy engines move
+        the block over NVLink while the SMs go on with the next block."""
+        peer = self._peer
+        dev = peer["full"].device
+        streams = peer.get("dma_streams")
+        if streams is None:
+            streams = peer["dma_streams"] = [torch.cuda.Stream(device=dev)
+                                             for _ in range(self.world)]
+        done = torch.cuda.Event()
+        done.record(torch.cuda.current_stream(dev))
+        src = peer["full"][row_offset:row_offset + rows]
+        for k in range(1, self.world):
+            q = (self.rank + k) % self.world           # every rank starts with another peer
+            streams[q].wait_event(done)
+            with torch.cuda.stream(streams[q]):
+                peer["views"][q][row_offset:row_offset + rows].copy_(src, non_blocking=True)
+
+    def _dma_join(self):
+        cur = torch.cuda.current_stream(self._peer["full"].device)
+        for q, st in enumerate(self._peer.get("dma_streams") or []):
+            if q != self.rank:
+                cur.wait_stream(st)
 
     @staticmethod
     def _into(out, full):
@@ -212,7 +258,8 @@ class RowPartitionedCsr:
         blocks = self._stages or [(self.data, self.indices, self.indptr)]
         h = self.n_local // len(blocks)
         side = None
-        if len(blocks) > 1:
+        dma = self.peer_transfer == "dma" and peer.get("views") is not None
+        if len(blocks) > 1 and not dma:
             # the stores of block s drain on a second stream while block s+1 is multiplied
             # (high priority: its few CTAs take the next free slots of the SMs instead of
             # queueing behind every CTA of the tile kernel launched after them)
@@ -227,10 +274,20 @@ class RowPartitionedCsr:
             else:
                 row_offset = (s * self.world + self.rank) * h
             last = s + 1 == len(blocks)
-            if not spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array"], peer["n"],
-                                       row_offset, self.n_rows, store_stream=side,
-                                       store_ctas=0 if last else self.peer_store_ctas,
-                                       x_ready=x_ready if s == 0 else None):
+            if dma:
+                # the last kernel writes the block into this rank's copy only; the copy engines
+                # take it to the other ranks while the next block is multiplied
+                ok = spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array_self"], 1,
+                                         row_offset, self.n_rows,
+                                         x_ready=x_ready if s == 0 else None)
+                if ok:
+                    self._dma_block(row_offset, h)
+            else:
+                ok = spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array"],
+                                         peer["n"], row_offset, self.n_rows, store_stream=side,
+                                         store_ctas=0 if last else self.peer_store_ctas,
+                                         x_ready=x_ready if s == 0 else None)
+            if not ok:
                 if s == 0:
                     if x_ready is not None:
                         x_ready(None)
@@ -238,6 +295,8 @@ class RowPartitionedCsr:
                 raise RuntimeError("row block cannot be stored to the peers")
         if side is not None:
             torch.cuda.current_stream(x.device).wait_stream(side)
+        if dma:
+            self._dma_join()
         self.fence()
         return peer["full"]
 

@@ -68,6 +68,12 @@ def _worker(rank, world, port, results):
         torch.cuda.synchronize()
         dist.barrier()
         used_peer = y3 is not None and part._peer is not None
+        part.peer_transfer = "dma"                     # same kernels, block moved by copy engines
+        y4 = part.spmv(x, src=0).clone()
+        torch.cuda.synchronize()
+        dist.barrier()
+        dma_same = bool(torch.equal(y4, y3)) and part._peer.get("views") is not None
+        part.peer_transfer = "stores"
         err_panel = float(torch.linalg.vector_norm(y3 - single) / torch.linalg.vector_norm(single))
         plan_mod.PANEL_POLICY = "off"
         clear_plan_cache()
@@ -79,7 +85,7 @@ def _worker(rank, world, port, results):
         same_mm = bool(torch.equal(C2, C))
         results[rank] = (err, err_mm, part.rows_per_rank, same, err_panel, same_mm,
                          y2.data_ptr() == y_full.data_ptr(), C2.data_ptr() == C_full.data_ptr(),
-                         same_short, two_differ)
+                         same_short, two_differ, dma_same)
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -152,7 +158,8 @@ def test_two_nccl_ranks_match_single_gpu():
         mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
         for rank in range(2):
             (err, err_mm, rows, same, err_panel, same_mm, y_in_place, c_in_place,
-             same_short, two_differ) = results[rank]
+             same_short, two_differ, dma_same) = results[rank]
+            assert dma_same, "the copy-engine transfer gives another result than the peer stores"
             assert same_short, "rows of one entry differ between 1 and 2 GPUs"
             assert two_differ == 0, f"{two_differ} rows of two entries differ between 1 and 2 GPUs"
             assert err <= 1e-5 and err_mm <= 1e-5, (err, err_mm)   # float32 tolerance
