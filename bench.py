@@ -672,10 +672,12 @@ def cfg5_extra(args, rank, world, device, timed):
             part = RowPartitionedCsr.from_global(g.data, g.indices, g.indptr, g.shape)
         out_local = torch.empty((part.n_local, *trailing), dtype=g.data.dtype, device=device)
         out_full, mode = None, "nccl"
-        if args.gather in ("peer", "dma"):
-            part.peer_transfer = "dma" if args.gather == "dma" else "stores"
+        if args.gather in ("peer", "dma", "mc"):
+            part.peer_transfer = {"dma": "dma", "mc": "multicast"}.get(args.gather, "stores")
             try:    # collective: raises on every rank or on none
-                out_full, mode = part.enable_peer_gather(g.data.dtype, trailing), "peer"
+                out_full = part.enable_peer_gather(g.data.dtype, trailing,
+                                                   multicast=args.gather == "mc")
+                mode = "peer"
             except RuntimeError as exc:
                 print(f"[rank {rank}] cfg5 {kind}: {exc}", file=sys.stderr, flush=True)
         if out_full is None:
@@ -756,14 +758,15 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     part.pipeline_broadcast = bool(args.pipelined_broadcast)
     staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
     op = part.spmv if kind == "spmv" else part.spmm
-    gather_mode = "peer" if args.gather == "dma" else args.gather
-    part.peer_transfer = "dma" if args.gather == "dma" else "stores"
+    gather_mode = "peer" if args.gather in ("dma", "mc") else args.gather
+    part.peer_transfer = {"dma": "dma", "mc": "multicast"}.get(args.gather, "stores")
     if gather_mode == "peer":
         # the last kernel of every rank stores its block into all ranks' result buffers; if
         # symmetric memory cannot be set up on any rank, every rank falls back to NCCL
         ok = torch.ones(1, dtype=torch.int32, device=device)
         try:
-            peer_full = part.enable_peer_gather(p.data.dtype, trailing)
+            peer_full = part.enable_peer_gather(p.data.dtype, trailing,
+                                                multicast=args.gather == "mc")
         except Exception as exc:  # noqa: BLE001 - reported below, decided collectively
             ok.zero_()
             print(f"[rank {rank}] peer gather unavailable: {exc}", file=sys.stderr, flush=True)
@@ -905,6 +908,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                            if gather_mode == "peer" else "NCCL all-gather of y / C"),
                 "inside_timed_step": True, "stages": args.stages if staged else 1,
                 "mode": args.gather if gather_mode == "peer" else gather_mode,
+                "multicast": bool(part._peer and part._peer.get("multicast_ptr")
+                                  and part.peer_transfer == "multicast"),
                 "store_ctas": part.peer_store_ctas},
             "roofline": {"bound": "hbm", "achieved": kernel_gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": kernel_gbs / world / peak, "traffic": None,
@@ -956,11 +961,12 @@ def main():
                          "of the next (1 = no overlap; 0 = 1 below four GPUs, 2 from four on: "
                          "measured 2.11 ms with 1 stage on 2 GPUs, 2.49 ms with 2 stages against "
                          "2.59 ms with 4 on 4 GPUs)")
-    ap.add_argument("--gather", default="peer", choices=["nccl", "peer", "dma"],
+    ap.add_argument("--gather", default="peer", choices=["nccl", "peer", "dma", "mc"],
                     help="N > 1: how y / C is assembled -- NCCL all-gather; stores of the last "
                          "kernel into every rank's symmetric-memory buffer (peer); or the last "
                          "kernel writes this rank's buffer and the copy engines move the block "
-                         "to the other ranks (dma)")
+                         "to the other ranks (dma); or it stores once into an NVSwitch multicast "
+                         "mapping of all buffers (mc; falls back to peer where there is none)")
     ap.add_argument("--pipelined-broadcast", action="store_true",
                     help="N > 1: broadcast x one column panel at a time, the kernel of a panel "
                          "starting when its slice has landed (default: one broadcast first)")

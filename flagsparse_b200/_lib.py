@@ -80,6 +80,9 @@ SIGNATURES = {
     "b2s_panel_combine_peers": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                         c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                         c_int, c_void_p]),
+    "b2s_panel_combine_multicast": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p,
+                                            c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                            c_int, c_void_p]),
     "b2s_spmm_csr_colmajor_c": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                         c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -409,7 +409,36 @@ struct PeerList {
 // A thread finishes the 16 / sizeof(V) consecutive rows that make up 16 bytes of y and stores
 // them to every peer with one 16-byte store (vec_ok: the peers' buffers are 16-byte aligned and
 // row_offset is a multiple of that row count); ragged ends and unaligned blocks store by value.
+// NVSwitch multicast: one store to an address of the multicast mapping of the ranks' buffers is
+// replicated by the switch into every rank's copy (multimem.st), so a block leaves this GPU once
+// instead of once per peer.  The payload travels as 32-bit lanes; a store changes no bits.
+__device__ inline void multimem_store4(void* mc, uint32_t a) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(__uint_as_float(a))
+               : "memory");
+}
+__device__ inline void multimem_store8(void* mc, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y))
+               : "memory");
+}
+__device__ inline void multimem_store16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
 template <class V>
+__device__ inline void multimem_store_value(V* mc, const V& v) {
+  if constexpr (sizeof(V) == 4)
+    multimem_store4(mc, *reinterpret_cast<const uint32_t*>(&v));
+  else if constexpr (sizeof(V) == 8)
+    multimem_store8(mc, *reinterpret_cast<const uint2*>(&v));
+  else
+    multimem_store16(mc, *reinterpret_cast<const uint4*>(&v));
+}
+
+// MC: peers.p[0] is the multicast address of the assembled result (n_peers is 1)
+template <class V, bool MC = false>
 __global__ void panel_combine_peers_kernel(const V* __restrict__ ypart,
                                            const int32_t* __restrict__ subpos, int64_t n_rows,
                                            int n_panels, const V* y_in, PeerList peers,
@@ -445,14 +474,23 @@ __global__ void panel_combine_peers_kernel(const V* __restrict__ ypart,
     }
     if (vec_ok && r0 + RP <= n_rows) {
       const uint4 raw = *reinterpret_cast<const uint4*>(out);
-      for (int q = 0; q < n_peers; ++q)
-        *reinterpret_cast<uint4*>(static_cast<V*>(peers.p[q]) + row_offset + r0) = raw;
+      if constexpr (MC) {
+        multimem_store16(static_cast<V*>(peers.p[0]) + row_offset + r0, raw);
+      } else {
+        for (int q = 0; q < n_peers; ++q)
+          *reinterpret_cast<uint4*>(static_cast<V*>(peers.p[q]) + row_offset + r0) = raw;
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < RP; ++j)
-        if (r0 + j < n_rows)
-          for (int q = 0; q < n_peers; ++q)
-            static_cast<V*>(peers.p[q])[row_offset + r0 + j] = out[j];
+        if (r0 + j < n_rows) {
+          if constexpr (MC) {
+            multimem_store_value(static_cast<V*>(peers.p[0]) + row_offset + r0 + j, out[j]);
+          } else {
+            for (int q = 0; q < n_peers; ++q)
+              static_cast<V*>(peers.p[q])[row_offset + r0 + j] = out[j];
+          }
+        }
     }
   }
 }
@@ -523,11 +561,12 @@ extern "C" int b2s_panel_combine(int val_type, const void* ypart_dev, const int3
   return b2s::launch_status();
 }
 
-extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
-                                       const int32_t* subpos_dev, int64_t n_rows, int n_panels,
-                                       const void* y_in_dev, void* const* peer_y, int n_peers,
-                                       int64_t row_offset, int64_t peer_rows, const void* alpha,
-                                       const void* beta, int grid_limit, b2s_stream stream) {
+static int panel_combine_to_ranks(int val_type, const void* ypart_dev,
+                                  const int32_t* subpos_dev, int64_t n_rows, int n_panels,
+                                  const void* y_in_dev, void* const* peer_y, int n_peers,
+                                  int64_t row_offset, int64_t peer_rows, const void* alpha,
+                                  const void* beta, int grid_limit, b2s_stream stream,
+                                  bool multicast) {
   if (n_rows < 0 || row_offset < 0 || n_panels < 1 || n_panels > 256 || !alpha || !beta ||
       grid_limit < 0)
     return B2S_ERR_ARG;
@@ -554,11 +593,37 @@ extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
     const V b = *static_cast<const V*>(beta);
     const int has_beta = b2s::vt<V>::is_zero(b) ? 0 : 1;
     if (has_beta && y_in_dev == nullptr) return B2S_ERR_ARG;
-    (b2s::panel_combine_peers_kernel<V><<<grid, threads, 0, s>>>(
-        static_cast<const V*>(ypart_dev), subpos_dev, n_rows, n_panels,
-        static_cast<const V*>(y_in_dev), peers, n_peers, row_offset, a, b, has_beta, vec_ok));
+    if (multicast)
+      (b2s::panel_combine_peers_kernel<V, true><<<grid, threads, 0, s>>>(
+          static_cast<const V*>(ypart_dev), subpos_dev, n_rows, n_panels,
+          static_cast<const V*>(y_in_dev), peers, 1, row_offset, a, b, has_beta, vec_ok));
+    else
+      (b2s::panel_combine_peers_kernel<V, false><<<grid, threads, 0, s>>>(
+          static_cast<const V*>(ypart_dev), subpos_dev, n_rows, n_panels,
+          static_cast<const V*>(y_in_dev), peers, n_peers, row_offset, a, b, has_beta, vec_ok));
   });
   return b2s::launch_status();
+}
+
+extern "C" int b2s_panel_combine_peers(int val_type, const void* ypart_dev,
+                                       const int32_t* subpos_dev, int64_t n_rows, int n_panels,
+                                       const void* y_in_dev, void* const* peer_y, int n_peers,
+                                       int64_t row_offset, int64_t peer_rows, const void* alpha,
+                                       const void* beta, int grid_limit, b2s_stream stream) {
+  return panel_combine_to_ranks(val_type, ypart_dev, subpos_dev, n_rows, n_panels, y_in_dev,
+                                peer_y, n_peers, row_offset, peer_rows, alpha, beta, grid_limit,
+                                stream, false);
+}
+
+extern "C" int b2s_panel_combine_multicast(int val_type, const void* ypart_dev,
+                                           const int32_t* subpos_dev, int64_t n_rows,
+                                           int n_panels, const void* y_in_dev, void* multicast_y,
+                                           int64_t row_offset, int64_t peer_rows,
+                                           const void* alpha, const void* beta, int grid_limit,
+                                           b2s_stream stream) {
+  void* one[1] = {multicast_y};
+  return panel_combine_to_ranks(val_type, ypart_dev, subpos_dev, n_rows, n_panels, y_in_dev, one,
+                                1, row_offset, peer_rows, alpha, beta, grid_limit, stream, true);
 }
 
 extern "C" int b2s_peer_scatter(const void* src_dev, int64_t bytes, void* const* peer_dst,

@@ -73,8 +73,9 @@ class RowPartitionedCsr:
         # of the next stage; 0 = one thread per row
         self.peer_store_ctas = 2 * 148
         # how a finished block reaches the other ranks' copies of the result: 'stores' (the
-        # last kernel stores into every copy itself) or 'dma' (it writes this rank's copy and
-        # the copy engines move the block, leaving the SMs to the next block)
+        # last kernel stores into every copy itself), 'multicast' (it stores once into the
+        # multicast mapping and the switch replicates; needs enable_peer_gather(multicast=True))
+        # or 'dma' (it writes this rank's copy and the copy engines move the block)
         self.peer_transfer = "stores"
         # SpMV with the peer gather: broadcast x one column panel at a time and start the kernel
         # of a panel when its slice has landed.  Off by default: on 2 GPUs the four small
@@ -149,19 +150,24 @@ class RowPartitionedCsr:
         return out
 
     # -- all-gather fused into the kernels: stores into every rank's buffer ------------------------
-    def enable_peer_gather(self, dtype, trailing=()):
+    def enable_peer_gather(self, dtype, trailing=(), multicast=False):
         """Allocate the assembled y / C in symmetric memory (one buffer per rank, each mapped
         into every process so that kernels can store into it over NVLink).  Afterwards spmv() /
         spmm() have their last kernel store this rank's block straight into all copies instead
         of calling an all-gather.  Collective: every rank calls it with the same arguments.
-        Plain peer stores only: NVLink multicast is switched off for these buffers.
+        multicast=False (default): plain peer stores only, NVLink multicast is switched off for
+        these buffers.  multicast=True: the allocation is also bound to an NVSwitch multicast
+        object where the platform offers one, and `peer_transfer = "multicast"` then stores every
+        value once for all ranks; every process must make this choice before its first
+        symmetric-memory allocation.
 
         The caller owns the ordering between steps: a rank may start storing the next result as
         soon as it has passed the end-of-step fence, so a consumer that reads the assembled
         result asynchronously must finish (or call ``fence()``) before the next product."""
         import ctypes
         import os
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        if not multicast:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         dev = self.data.device
         group = self.group if self.group is not None else dist.group.WORLD
@@ -189,6 +195,7 @@ class RowPartitionedCsr:
             "full": full, "handle": hdl, "n": self.world,
             "array": (ctypes.c_void_p * self.world)(*ptrs),
             "array_self": (ctypes.c_void_p * 1)(ptrs[self.rank]),
+            "multicast_ptr": self._multicast_address(hdl) if multicast else 0,
             "views": self._peer_views(hdl, full, trailing, dtype),
             "flag": torch.zeros(1, dtype=torch.int32, device=dev),
             "trailing": tuple(int(t) for t in trailing), "dtype": dtype,
@@ -196,6 +203,15 @@ class RowPartitionedCsr:
         }
         dist.barrier(group=self.group)
         return full
+
+    @staticmethod
+    def _multicast_address(hdl):
+        """Address of the buffer in the multicast mapping, 0 when there is none."""
+        try:
+            base = int(hdl.multicast_ptr or 0)
+        except Exception:  # noqa: BLE001 - no multicast on this platform / build
+            return 0
+        return base + int(getattr(hdl, "offset", 0) or 0) if base else 0
 
     def _peer_views(self, hdl, full, trailing, dtype):
         """Tensors over every rank's copy of the assembled result (for copies by the copy
@@ -259,6 +275,7 @@ class RowPartitionedCsr:
         h = self.n_local // len(blocks)
         side = None
         dma = self.peer_transfer == "dma" and peer.get("views") is not None
+        mc_ptr = peer.get("multicast_ptr", 0) if self.peer_transfer == "multicast" else 0
         if len(blocks) > 1 and not dma:
             # the stores of block s drain on a second stream while block s+1 is multiplied
             # (high priority: its few CTAs take the next free slots of the SMs instead of
@@ -286,7 +303,8 @@ class RowPartitionedCsr:
                 ok = spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer["array"],
                                          peer["n"], row_offset, self.n_rows, store_stream=side,
                                          store_ctas=0 if last else self.peer_store_ctas,
-                                         x_ready=x_ready if s == 0 else None)
+                                         x_ready=x_ready if s == 0 else None,
+                                         multicast_ptr=mc_ptr)
             if not ok:
                 if s == 0:
                     if x_ready is not None:

@@ -383,7 +383,8 @@ def _launch_spmv(plan: CsrPlan, x, y, y_in, alpha, beta):
 
 
 def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row_offset,
-                        peer_rows, store_stream=None, store_ctas=0, x_ready=None):
+                        peer_rows, store_stream=None, store_ctas=0, x_ready=None,
+                        multicast_ptr=0):
     """Several GPUs: multiply this rank's row block and store the result block at rows
     [row_offset, row_offset + n_rows) of the y buffer (peer_rows rows) of every rank
     (`peer_array`: ctypes array of the n_peers device pointers, own buffer included).  On the
@@ -398,7 +399,10 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
     on launching the next block on the current stream while the stores drain over NVLink.
     store_ctas > 0 caps that kernel's grid (CTAs of 256 threads); together with a high-priority
     store_stream a small grid runs beside the next block's tile kernel.
-    x_ready: see _launch_stack_partials (x still arriving slice by slice when this is called)."""
+    x_ready: see _launch_stack_partials (x still arriving slice by slice when this is called).
+    multicast_ptr: address of the assembled result in a multicast mapping of the ranks' buffers;
+    when given (and the combine kernel does the storing) every value is stored once and the
+    switch replicates it (b2s_panel_combine_multicast)."""
     plan = prepared.plan()
     lib = _lib.load()
     rec = _spmv_launch_record(plan)
@@ -423,10 +427,17 @@ def spmv_block_to_peers(prepared, x, y_in, alpha, beta, peer_array, n_peers, row
                 done.record(torch.cuda.current_stream(plan.device))
                 store_stream.wait_event(done)
                 target = store_stream.cuda_stream
-            st = lib.b2s_panel_combine_peers(
-                plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows, lay.n_panels,
-                _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows, a, b,
-                int(store_ctas) if store_stream is not None else 0, target)
+            grid_limit = int(store_ctas) if store_stream is not None else 0
+            if multicast_ptr:
+                st = lib.b2s_panel_combine_multicast(
+                    plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows,
+                    lay.n_panels, _lib.ptr(y_in), ctypes.c_void_p(int(multicast_ptr)),
+                    row_offset, peer_rows, a, b, grid_limit, target)
+            else:
+                st = lib.b2s_panel_combine_peers(
+                    plan.vcode, _lib.ptr(ypart), _lib.ptr(lay.subpos), plan.n_rows,
+                    lay.n_panels, _lib.ptr(y_in), peer_array, n_peers, row_offset, peer_rows,
+                    a, b, grid_limit, target)
             _lib.check(st, "b2s_panel_combine_peers")
         else:
             tmp = plan.scratch_on("spmv_peer_block", plan.n_rows, stream)

@@ -263,6 +263,16 @@ int b2s_panel_combine_peers(int val_type, const void* ypart_dev, const int32_t* 
                             void* const* peer_y, int n_peers, int64_t row_offset,
                             int64_t peer_rows, const void* alpha, const void* beta,
                             int grid_limit, b2s_stream stream);
+/* The same step with ONE store per value: multicast_y is the address of the assembled result in
+ * a multicast mapping of the ranks' buffers (NVSwitch replicates a multimem.st into every
+ * rank's copy, this rank's included), so a block leaves the GPU once instead of once per peer.
+ * The caller provides the mapping (e.g. the multicast pointer of a symmetric-memory
+ * allocation) and orders the ranks afterwards as above. */
+int b2s_panel_combine_multicast(int val_type, const void* ypart_dev, const int32_t* subpos_dev,
+                                int64_t n_rows, int n_panels, const void* y_in_dev,
+                                void* multicast_y, int64_t row_offset, int64_t peer_rows,
+                                const void* alpha, const void* beta, int grid_limit,
+                                b2s_stream stream);
 
 /* ---- dense transpose ---------------------------------------------------------------------------
  * dst[c * ld_dst + r] = src[r * ld_src + c] for a rows x cols matrix of 2-, 4-, 8- or 16-byte

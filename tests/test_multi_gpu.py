@@ -167,3 +167,54 @@ def test_two_nccl_ranks_match_single_gpu():
             assert err_panel <= 1e-5, err_panel
             assert c_in_place, "SpMM result did not come back in the symmetric buffer"
             assert sum(rows) == (1 << 26) // 512
+
+
+def _multicast_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        import flagsparse_b200._plan as plan_mod
+        from flagsparse_b200 import flagsparse_spmv_csr, workloads
+        from flagsparse_b200.distributed import RowPartitionedCsr
+        plan_mod.PANEL_TRIGGER_BYTES, plan_mod.PANEL_MIN_NNZ = 0, 0
+        plan_mod.PANEL_TARGET_BYTES = 4096 * 8
+        q = workloads.cfg2_powerlaw_spmv(device="cuda", scale=256, seed=5)
+        part = RowPartitionedCsr.from_global(q.data, q.indices, q.indptr, q.shape)
+        part.enable_peer_gather(q.x.dtype, multicast=True)
+        x = q.x.clone() if rank == 0 else torch.zeros_like(q.x)
+        have = bool(part._peer.get("multicast_ptr"))
+        y_stores = part.spmv(x, src=0).clone()          # peer stores (panel route)
+        torch.cuda.synchronize()
+        dist.barrier()
+        part.peer_transfer = "multicast"
+        y_mc = part.spmv(x, src=0).clone()              # one multimem store per value
+        torch.cuda.synchronize()
+        dist.barrier()
+        single = flagsparse_spmv_csr(q.data, q.indices, q.indptr, q.x, q.shape)
+        err = float(torch.linalg.vector_norm(y_mc - single) / torch.linalg.vector_norm(single))
+        results[rank] = (have, bool(torch.equal(y_mc, y_stores)), err)
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_multicast_stores_give_the_same_assembled_result_as_peer_stores():
+    """The combine kernel storing once into the NVSwitch multicast mapping of the ranks' result
+    buffers (b2s_panel_combine_multicast) against the same kernel storing into every buffer.
+    Skipped where the platform hands out no multicast mapping."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_multicast_worker, args=(2, port, results), nprocs=2, join=True)
+        if not all(results[r][0] for r in range(2)):
+            pytest.skip("no multicast mapping on this platform")
+        for rank in range(2):
+            have, same, err = results[rank]
+            assert same and err <= 1e-12, (same, err)
