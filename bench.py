@@ -29,8 +29,9 @@ rows up to 100,000 entries, y = 1.5 * A x + 0.5 * y.  A step is one such product
 With N > 1 (launched by torchrun, one rank per GPU) every rank owns one row block of the same
 size (weak scaling): x is broadcast from rank 0 (NCCL), each rank multiplies its block, and y is
 assembled on every rank -- by default the last kernel of each rank stores its block straight into
-all ranks' symmetric-memory buffers over NVLink (--gather peer), alternatively by an NCCL
-all-gather (--gather nccl); value counts the bytes all ranks processed over the slowest rank's
+all ranks' symmetric-memory buffers over NVLink (--gather peer, through peer pointers; from four
+GPUs on --gather mc, one multimem store per value that the NVSwitch replicates), alternatively by
+an NCCL all-gather (--gather nccl); value counts the bytes all ranks processed over the slowest rank's
 time.  Every rank checks its own block and the block of the next rank of the assembled y against
 torch's CSR product.  The N > 1 line also carries extra.cfg5: ONE 2^26-row float32 / int64 matrix
 row-partitioned by non-zeros over the ranks (RowPartitionedCsr.from_global), SpMV and SpMM
@@ -751,8 +752,12 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     def gather():
         part.gather_rows(out_local, out=out_full)
 
+    if args.gather == "auto":
+        # measured (step, ms): 2 GPUs peer stores 1.68, multicast 1.72; 4 GPUs 1.96 / 1.92;
+        # 8 GPUs 2.56 / 2.19 -- from four ranks on the block leaves the GPU once
+        args.gather = "peer" if world < 4 else "mc"
     if args.stages <= 0:
-        args.stages = 1 if world < 4 else 2
+        args.stages = 1 if world < 4 else 4
     if args.store_ctas >= 0:
         part.peer_store_ctas = args.store_ctas
     part.pipeline_broadcast = bool(args.pipelined_broadcast)
@@ -937,6 +942,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
         if cfg5 is not None:
             line["extra"]["cfg5"] = cfg5
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()      # nothing of this rank in flight when the ranks part
     dist.barrier()
     dist.destroy_process_group()
     if not parity["ok"]:
@@ -958,11 +964,10 @@ def main():
                          "0 = one thread per row)")
     ap.add_argument("--stages", type=int, default=0,
                     help="N > 1: row sub-blocks per rank; the gather of one overlaps the kernel "
-                         "of the next (1 = no overlap; 0 = 1 below four GPUs, 2 from four on: "
-                         "measured 2.11 ms with 1 stage on 2 GPUs, 2.49 ms with 2 stages against "
-                         "2.59 ms with 4 on 4 GPUs)")
-    ap.add_argument("--gather", default="peer", choices=["nccl", "peer", "dma", "mc"],
-                    help="N > 1: how y / C is assembled -- NCCL all-gather; stores of the last "
+                         "of the next (1 = no overlap; 0 = 1 below four GPUs, 4 from four on)")
+    ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer", "dma", "mc"],
+                    help="N > 1: how y / C is assembled (auto: peer below four GPUs, mc from four "
+                         "on) -- NCCL all-gather; stores of the last "
                          "kernel into every rank's symmetric-memory buffer (peer); or the last "
                          "kernel writes this rank's buffer and the copy engines move the block "
                          "to the other ranks (dma); or it stores once into an NVSwitch multicast "
