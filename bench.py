@@ -903,7 +903,11 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                               "column panel; the kernel of a panel starts when its slice has "
                               "landed" if pipelined_bcast else
                               "NCCL broadcast of x / B from rank 0"),
-                "gather": (("each rank's last kernel writes its block into its own "
+                "gather": (("one multimem store per 16 bytes by each rank's last kernel into "
+                            "an NVSwitch multicast mapping of all ranks' symmetric-memory result "
+                            "buffers" if (part.peer_transfer == "multicast" and kind == "spmv"
+                                          and part._peer and part._peer.get("multicast_ptr"))
+                            else "each rank's last kernel writes its block into its own "
                             "symmetric-memory result buffer and the copy engines take it to "
                             "every other rank's buffer over NVLink (one asynchronous copy per "
                             "peer)" if part.peer_transfer == "dma" and kind == "spmv" else

@@ -459,8 +459,13 @@ spmm_tile_kernel(const ST* __restrict__ val, const I* __restrict__ col, const P*
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  // an earlier CTA already gave up on a copy: do not queue more waits behind it
-  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+  // an earlier CTA already gave up on a copy: do not queue more waits behind it (one thread
+  // reads the word and the whole CTA leaves or stays together)
+  {
+    const int gave_up =
+        (tid == 0 && status) ? (*reinterpret_cast<volatile int32_t*>(status) != 0) : 0;
+    if (__syncthreads_or(gave_up)) return;
+  }
   const bool has_beta = has_beta_i != 0;
   const int64_t t = blockIdx.x;
   const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
@@ -835,7 +840,11 @@ spmm_chunk_kernel(const V* __restrict__ val, const I* __restrict__ col,
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  if (status && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+  {
+    const int gave_up =
+        (tid == 0 && status) ? (*reinterpret_cast<volatile int32_t*>(status) != 0) : 0;
+    if (__syncthreads_or(gave_up)) return;
+  }
   const bool has_beta = has_beta_i != 0;
   const int64_t t = blockIdx.x;
   const TileCoord tc = tile_coord(tile_row, t, ITEMS, n_rows + nnz);
