@@ -60,7 +60,7 @@ NOMINAL_HBM_GBS = 8000.0
 # DRAM bytes (read + written) of one step from an ncu capture of the same command
 # (dram__bytes_read.sum + dram__bytes_write.sum over the kernels of a step), keyed by
 # (workload, scale); to be re-captured whenever the kernels of the step change
-NCU_TRAFFIC_BYTES = {("cfg2", 1): 4.76e9}
+NCU_TRAFFIC_BYTES = {("cfg2", 1): 4.76e9, ("cfg3", 1): 1.93e9}
 
 REL_L2_TOL = {torch.float32: 1e-5, torch.complex64: 1e-5, torch.float64: 1e-12,
               torch.complex128: 1e-12}
