@@ -282,3 +282,43 @@ def test_panel_combine_peers_stores_the_same_values_as_panel_combine(dtype, n_ro
     assert lib.b2s_panel_combine_peers(vcode, L.ptr(ypart), L.ptr(subpos), n_rows, n_panels,
                                        L.ptr(y_in), arr, 2, 8, n_rows + 7, a, b, 0, stream) == \
         2   # B2S_ERR_ARG
+
+
+def test_window_entry_points_say_when_the_windowed_kernel_can_run():
+    """b2s_spmm_window_tile_items / b2s_spmm_window_usable, and b2s_spmm_csr_windowed refusing a
+    window it cannot use instead of running the wrong tile plan."""
+    lib, L = _lib()
+    assert lib.b2s_spmm_window_tile_items(L.B2S_F32, L.B2S_I32) == 1536
+    for v, i in ((L.B2S_F64, L.B2S_I32), (L.B2S_F32, L.B2S_I64), (L.B2S_C64, L.B2S_I32)):
+        assert lib.b2s_spmm_window_tile_items(v, i) == lib.b2s_spmm_tile_items(v, i)
+    n, N = 4096, 32
+    B = torch.zeros((n, N + 4), dtype=torch.float32, device="cuda")
+    C = torch.zeros((n, N), dtype=torch.float32, device="cuda")
+    ok = lambda b, ldb, nd, c, ldc, rows: lib.b2s_spmm_window_usable(  # noqa: E731
+        L.B2S_F32, b, ldb, nd, None, c, ldc, n, rows)
+    assert ok(L.ptr(B), N + 4, N, L.ptr(C), N, 100) == 1
+    assert ok(L.ptr(B), N + 4, N, L.ptr(C), N, 0) == 0                 # no window
+    assert ok(L.ptr(B), N + 4, N, L.ptr(C), N, 300) == 0               # 300 rows x 144 B > 32 KB
+    assert ok(L.ptr(B), N + 3, N, L.ptr(C), N, 100) == 0               # pitch not a multiple of 16
+    assert ok(L.ptr(B[:, 1:]), N + 4, N, L.ptr(C), N, 100) == 0        # B not 16-byte aligned
+    assert ok(L.ptr(B), N + 4, N - 2, L.ptr(C), N, 100) == 0           # ragged last pack
+    assert ok(L.ptr(B), N + 4, 256, L.ptr(C), 256, 10) == 0            # more than one column tile
+    # a window that cannot be used is refused, not silently run on the plain kernel's tiles
+    data = torch.ones(8, dtype=torch.float32, device="cuda")
+    col = torch.arange(8, dtype=torch.int32, device="cuda")
+    ptr = torch.arange(0, 9, dtype=torch.int32, device="cuda")
+    items = lib.b2s_spmm_window_tile_items(L.B2S_F32, L.B2S_I32)
+    T = lib.b2s_tile_count(8, 8, items)
+    tile_row = torch.zeros(T + 1, dtype=torch.int64, device="cuda")
+    table = torch.zeros(2 * T, dtype=torch.int32, device="cuda")
+    carry = torch.zeros(T * N, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    s = L.stream_handle(data.device)
+    assert lib.b2s_tile_plan(L.ptr(ptr), L.B2S_I32, 8, 8, items, L.ptr(tile_row), s) == 0
+    a, b = L.scalar_buffer(1.0, torch.float32), L.scalar_buffer(0.0, torch.float32)
+    st = lib.b2s_spmm_csr_windowed(L.B2S_F32, L.B2S_I32, L.B2S_I32, L.ptr(data), L.ptr(col),
+                                   L.ptr(ptr), 8, n, 8, L.ptr(B), N + 3, N, None, L.ptr(C), N,
+                                   a, b, L.ptr(tile_row), L.ptr(carry), L.ptr(status), 100,
+                                   L.ptr(table), s)
+    assert st == 2   # B2S_ERR_ARG
+    torch.cuda.synchronize()
