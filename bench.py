@@ -621,24 +621,18 @@ def gather_ceiling(device, spmv_gathers_per_s):
             "frac": spmv_gathers_per_s / rate, "x_bytes": n_x * 8, "gathers": n}
 
 
-def check_assembled(part, out_full, own, nxt, dense, alpha, beta, staged_rows):
+def check_assembled(part, out_full, own, nxt, dense, alpha, beta):
     """Every rank compares two row blocks of the assembled result with torch's CSR product: its
     own and the next rank's.  `own` / `nxt` are (data, indices, indptr, y0 or None, rank) of
-    those blocks; staged_rows = rows per stage when the global row order is block-cyclic
-    (sub-block s of rank r at rows (s * world + r) * h), else 0.  Returns the largest rel-L2."""
+    those blocks; where a rank's rows sit in the assembled result (one slice, or one slice per
+    stage) comes from part.stage_slices.  Returns the largest rel-L2."""
     worst = 0.0
     for data, indices, indptr, y0, r in (own, nxt):
         n_local = int(indptr.numel()) - 1
         want = alpha * torch_product(data, indices, indptr, (n_local, part.n_cols), dense)
         if beta != 0.0:
             want = want + beta * y0.to(want.dtype)
-        if staged_rows:
-            h = staged_rows
-            got = torch.cat([out_full[(s * part.world + r) * h:(s * part.world + r + 1) * h]
-                             for s in range(n_local // h)])
-        else:
-            off = sum(part.rows_per_rank[:r])
-            got = out_full[off:off + n_local]
+        got = torch.cat([out_full[first:first + rows] for first, rows in part.stage_slices(r)])
         worst = max(worst, rel_l2(got, want))
         del want
     return worst
@@ -691,7 +685,7 @@ def cfg5_extra(args, rank, world, device, timed):
 
         full = step()
         torch.cuda.synchronize()
-        err = check_assembled(part, full, own, nxt, dense, 1.0, 0.0, 0)
+        err = check_assembled(part, full, own, nxt, dense, 1.0, 0.0)
         errs = torch.tensor([err], dtype=torch.float64, device=device)
         dist.all_reduce(errs, op=dist.ReduceOp.MAX)
         steps = max(3, min(args.steps, 10))
@@ -761,7 +755,8 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     if args.store_ctas >= 0:
         part.peer_store_ctas = args.store_ctas
     part.pipeline_broadcast = bool(args.pipelined_broadcast)
-    staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1)
+    staged = part.split_stages(args.stages if kind == "spmv" or args.gather == "nccl" else 1,
+                               first_fraction=args.first_stage if args.first_stage > 0 else None)
     op = part.spmv if kind == "spmv" else part.spmm
     gather_mode = "peer" if args.gather in ("dma", "mc") else args.gather
     part.peer_transfer = {"dma": "dma", "mc": "multicast"}.get(args.gather, "stores")
@@ -827,8 +822,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
     torch.cuda.synchronize()
     worst = check_assembled(
         part, checked, (p.data, p.indices, p.indptr, y0_of(p), rank),
-        (q.data, q.indices, q.indptr, y0_of(q), (rank + 1) % world), dense, alpha, beta,
-        part._stage_rows if staged else 0)
+        (q.data, q.indices, q.indptr, y0_of(q), (rank + 1) % world), dense, alpha, beta)
     del q
     torch.cuda.empty_cache()
     errs = torch.tensor([worst], dtype=torch.float64, device=device)
@@ -916,6 +910,7 @@ def run_multi_gpu(args, rank, world, local_rank, device):
                            + ", then a one-element NCCL all-reduce as the end-of-step fence"
                            if gather_mode == "peer" else "NCCL all-gather of y / C"),
                 "inside_timed_step": True, "stages": args.stages if staged else 1,
+                "stage_rows": list(part._stage_heights) if staged else [part.n_local],
                 "mode": args.gather if gather_mode == "peer" else gather_mode,
                 "multicast": bool(part._peer and part._peer.get("multicast_ptr")
                                   and part.peer_transfer == "multicast"),
@@ -969,6 +964,10 @@ def main():
     ap.add_argument("--stages", type=int, default=0,
                     help="N > 1: row sub-blocks per rank; the gather of one overlaps the kernel "
                          "of the next (1 = no overlap; 0 = 1 below four GPUs, 4 from four on)")
+    ap.add_argument("--first-stage", type=float, default=0.0,
+                    help="N > 1 with stages: share of a rank's rows in its first sub-block "
+                         "(0 = equal sub-blocks); the exchange cannot start before the first "
+                         "sub-block is done")
     ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer", "dma", "mc"],
                     help="N > 1: how y / C is assembled (auto: peer below four GPUs, mc from four "
                          "on) -- NCCL all-gather; stores of the last "

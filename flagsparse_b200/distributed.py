@@ -272,7 +272,10 @@ class RowPartitionedCsr:
         from .spmv import prepare_spmv_csr, spmv_block_to_peers
         peer = self._peer
         blocks = self._stages or [(self.data, self.indices, self.indptr)]
-        h = self.n_local // len(blocks)
+        if self._stages:
+            starts, heights = self._stage_starts, self._stage_heights
+        else:
+            starts, heights = [0], [self.n_local]
         side = None
         dma = self.peer_transfer == "dma" and peer.get("views") is not None
         mc_ptr = peer.get("multicast_ptr", 0) if self.peer_transfer == "multicast" else 0
@@ -284,12 +287,13 @@ class RowPartitionedCsr:
             if side is None:
                 side = peer["side"] = torch.cuda.Stream(device=x.device, priority=-1)
         for s, (d, i, p) in enumerate(blocks):
+            t, h = starts[s], heights[s]
             prepared = prepare_spmv_csr(d, i, p, (h, self.n_cols))
-            y_in = None if out_local is None else out_local[s * h:(s + 1) * h]
+            y_in = None if out_local is None else out_local[t:t + h]
             if len(blocks) == 1:
                 row_offset = self.row_offset
             else:
-                row_offset = (s * self.world + self.rank) * h
+                row_offset = self.world * t + self.rank * h
             last = s + 1 == len(blocks)
             if dma:
                 # the last kernel writes the block into this rank's copy only; the copy engines
@@ -319,28 +323,53 @@ class RowPartitionedCsr:
         return peer["full"]
 
     # -- pipelined variant: several row blocks per rank ------------------------------------------
-    def split_stages(self, stages):
-        """Cut this rank's block into `stages` consecutive sub-blocks of equal height so that
-        the all-gather of one sub-block can run while the next one is multiplied.  The global
-        row order becomes block-cyclic: sub-block s of rank p holds global rows
-        [(s*world + p)*h, (s*world + p + 1)*h), h = n_local / stages -- i.e. the all-gather of
-        stage s fills one contiguous slice of y / C and no repacking is needed.  Needs equal
-        n_local on all ranks and n_local divisible by stages; otherwise returns False and the
+    def split_stages(self, stages, first_fraction=None):
+        """Cut this rank's block into `stages` consecutive sub-blocks so that the gather of one
+        sub-block can run while the next one is multiplied.  The global row order becomes
+        stage-major: with sub-block s of every rank h_s rows tall and starting at local row
+        t_s, sub-block s of rank p holds global rows [world * t_s + p * h_s, + h_s) -- i.e. the
+        gather of stage s fills one contiguous slice of y / C and no repacking is needed.
+        Heights are equal, or, with first_fraction (0 < f < 1 / stages), the first sub-block
+        holds about that share of the rows and the others split the rest equally: the exchange
+        can start no earlier than the first sub-block is done, so a short first one leaves
+        more of the step for the exchange to hide in.  Needs equal n_local on all ranks and
+        heights that come out as multiples of 32 rows; otherwise returns False and the
         single-stage path stays in use."""
         stages = int(stages)
-        if stages <= 1 or self.n_local % stages or len(set(self.rows_per_rank)) != 1:
-            self._stages = None
+        self._stages = None
+        if stages <= 1 or len(set(self.rows_per_rank)) != 1:
             return False
-        h = self.n_local // stages
+        heights = None
+        if first_fraction and stages >= 2 and 0.0 < first_fraction < 1.0 / stages:
+            h0 = int(self.n_local * first_fraction) // 32 * 32
+            rest = self.n_local - h0
+            if h0 > 0 and rest % (stages - 1) == 0 and (rest // (stages - 1)) % 32 == 0:
+                heights = [h0] + [rest // (stages - 1)] * (stages - 1)
+        if heights is None:
+            if self.n_local % stages:
+                return False
+            heights = [self.n_local // stages] * stages
+        starts = [0]
+        for h in heights:
+            starts.append(starts[-1] + h)
         self._stages = []
         for s in range(stages):
-            d, i, p = slice_rows(self.data, self.indices, self.indptr, s * h, (s + 1) * h)
+            d, i, p = slice_rows(self.data, self.indices, self.indptr, starts[s], starts[s + 1])
             self._stages.append((d.contiguous(), i.contiguous(), p.contiguous()))
-        self._stage_rows = h
+        self._stage_heights, self._stage_starts = heights, starts[:-1]
+        self._stage_rows = heights[0] if len(set(heights)) == 1 else None
         return True
 
+    def stage_slices(self, rank):
+        """[(global first row, rows)] of the sub-blocks of `rank` in the assembled result, in
+        stage order (one entry, the rank's whole block, without stages)."""
+        if not self._stages:
+            return [(sum(self.rows_per_rank[:rank]), self.rows_per_rank[rank])]
+        return [(self.world * t + rank * h, h)
+                for t, h in zip(self._stage_starts, self._stage_heights)]
+
     def _pipelined(self, local_op, dense, out_local, out, alpha, beta):
-        h, W = self._stage_rows, self.world
+        W = self.world
         trailing = tuple(dense.shape[1:])
         if out is None:
             out = torch.empty((self.n_rows, *trailing), dtype=dense.dtype, device=dense.device)
@@ -348,12 +377,12 @@ class RowPartitionedCsr:
             out_local = torch.empty((self.n_local, *trailing), dtype=dense.dtype,
                                     device=dense.device)
         works = []
-        for s, (d, i, p) in enumerate(self._stages):
-            blk = out_local[s * h:(s + 1) * h]
+        for (d, i, p), t, h in zip(self._stages, self._stage_starts, self._stage_heights):
+            blk = out_local[t:t + h]
             local_op(d, i, p, dense, (h, self.n_cols), out=blk, alpha=alpha, beta=beta)
             # asynchronous: the collective waits for the kernels enqueued so far and runs on
             # NCCL's stream while the next stage is being multiplied
-            works.append(dist.all_gather_into_tensor(out[s * W * h:(s + 1) * W * h], blk,
+            works.append(dist.all_gather_into_tensor(out[W * t:W * (t + h)], blk,
                                                      group=self.group, async_op=True))
         for w in works:
             w.wait()

@@ -112,10 +112,21 @@ def _staged_worker(rank, world, port, results):
         expect = torch.cat([single[q * half + s * h: q * half + (s + 1) * h]
                             for s in range(stages) for q in range(world)])
         out = {}
-        for gather in ("nccl", "peer"):
+        for gather in ("nccl", "peer", "peer_short_first", "nccl_short_first"):
             part = RowPartitionedCsr(d.contiguous(), i.contiguous(), ptr.contiguous(), p.shape[1])
-            assert part.split_stages(stages)
-            if gather == "peer":
+            if gather.endswith("short_first"):
+                # a first sub-block of 1/16 of the rows, the other three share the rest
+                assert part.split_stages(stages, first_fraction=1.0 / 16)
+                assert part._stage_heights == [half // 16, 5 * half // 16, 5 * half // 16,
+                                               5 * half // 16]
+                expect = torch.cat([single[q * half + t: q * half + t + hs]
+                                    for t, hs in zip(part._stage_starts, part._stage_heights)
+                                    for q in range(world)])
+                assert part.stage_slices(1)[1] == (world * (half // 16) + 5 * half // 16,
+                                                   5 * half // 16)
+            else:
+                assert part.split_stages(stages)
+            if gather.startswith("peer"):
                 part.enable_peer_gather(p.x.dtype)
             x = p.x.clone() if rank == 0 else torch.zeros_like(p.x)
             y = part.spmv(x, src=0, out_local=y0_block.clone(), alpha=1.5, beta=0.5)
@@ -143,7 +154,8 @@ def test_block_cyclic_stages_with_nccl_and_with_peer_stores():
         results = manager.dict()
         mp.spawn(_staged_worker, args=(2, port, results), nprocs=2, join=True)
         for rank in range(2):
-            assert results[rank]["nccl"] <= 1e-12 and results[rank]["peer"] <= 1e-12, results[rank]
+            assert all(results[rank][k] <= 1e-12 for k in
+                       ("nccl", "peer", "peer_short_first", "nccl_short_first")), results[rank]
 
 
 def test_two_nccl_ranks_match_single_gpu():
