@@ -332,7 +332,9 @@ class RowPartitionedCsr:
         Heights are equal, or, with first_fraction (0 < f < 1 / stages), the first sub-block
         holds about that share of the rows and the others split the rest equally: the exchange
         can start no earlier than the first sub-block is done, so a short first one leaves
-        more of the step for the exchange to hide in.  Needs equal n_local on all ranks and
+        more of the step for the exchange to hide in (measured on 8 GPUs with 4 sub-blocks:
+        2.31 / 2.20 ms with a first share of 1/16 / 1/8 against 2.19 ms with equal heights, so
+        equal heights stay the default).  Needs equal n_local on all ranks and
         heights that come out as multiples of 32 rows; otherwise returns False and the
         single-stage path stays in use."""
         stages = int(stages)
