@@ -131,6 +131,44 @@ def test_staged_block_cyclic_gather_on_two_gloo_ranks():
         assert results[0] and results[1]
 
 
+def _short_first_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from flagsparse_b200.distributed import RowPartitionedCsr
+        n_local, n_cols = 2048, 50
+        rng = np.random.default_rng(100 + rank)
+        lengths = rng.integers(0, 5, n_local)
+        ptr = np.zeros(n_local + 1, dtype=np.int64)
+        np.cumsum(lengths, out=ptr[1:])
+        idx = rng.integers(0, n_cols, int(ptr[-1]))
+        data = rng.standard_normal(int(ptr[-1]))
+        part = RowPartitionedCsr(torch.from_numpy(data), torch.from_numpy(idx),
+                                 torch.from_numpy(ptr), n_cols, local_spmv=_oracle_spmv)
+        # a first share that is not below 1 / stages is ignored: equal heights
+        ok = part.split_stages(4, first_fraction=0.3) and part._stage_heights == [512] * 4
+        ok = ok and part.split_stages(4, first_fraction=1.0 / 16)
+        ok = ok and part._stage_heights == [128, 640, 640, 640]
+        ok = ok and part.stage_slices(1) == [(128, 128), (2 * 128 + 640, 640),
+                                             (2 * 768 + 640, 640), (2 * 1408 + 640, 640)]
+        x = torch.from_numpy(np.random.default_rng(7).standard_normal(n_cols))
+        y = part.spmv(x.clone() if rank == 0 else torch.zeros_like(x), src=0)
+        mine = oracle.spmv(data, idx, ptr, x.numpy(), (n_local, n_cols))
+        got = np.concatenate([y.numpy()[a:a + h] for a, h in part.stage_slices(rank)])
+        results[rank] = bool(ok and np.array_equal(got, mine) and y.numel() == 2 * n_local)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_stages_with_a_short_first_sub_block_on_two_gloo_ranks():
+    world = 2
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_short_first_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert results[0] and results[1]
+
+
 def _panel_broadcast_worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
