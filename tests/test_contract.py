@@ -118,6 +118,18 @@ def test_install_rebinds_a_flagsparse_like_package():
         assert spmv.flagsparse_spmv_csr is flagsparse_b200.flagsparse_spmv_csr
         flagsparse_b200.uninstall(replaced)
         assert ops.flagsparse_spmv_csr is sentinel and not hasattr(root, "flagsparse_spmv_csr")
+        # replace_modules=True: the two submodules themselves are swapped for this package's,
+        # in sys.modules and as attributes, and put back by uninstall()
+        replaced = flagsparse_b200.install(root, replace_modules=True)
+        import flagsparse_b200.spmm as our_spmm
+        import flagsparse_b200.spmv as our_spmv
+        assert sys.modules["fake_flagsparse.sparse_operations.spmv_csr"] is our_spmv
+        assert sys.modules["fake_flagsparse.sparse_operations.spmm_csr"] is our_spmm
+        assert ops.spmv_csr is our_spmv and ops.spmm_csr is our_spmm
+        flagsparse_b200.uninstall(replaced)
+        assert sys.modules["fake_flagsparse.sparse_operations.spmv_csr"] is spmv
+        assert ops.spmv_csr is spmv and ops.spmm_csr is spmm
+        assert ops.flagsparse_spmv_csr is sentinel
     finally:
         for m in (root, ops, spmv, spmm):
             sys.modules.pop(m.__name__, None)

@@ -45,3 +45,32 @@ def test_half_dtypes_have_value_codes_and_float32_scalars():
     assert _half.is_half(h) and not _half.is_half(h.float()) and not _half.is_half(None)
     buf = _lib.scalar_buffer(0.5, torch.bfloat16)
     assert isinstance(buf, ctypes.Array) and ctypes.sizeof(buf) == 4 and buf[0] == 0.5
+
+
+def test_panel_width_follows_from_the_value_type_alone():
+    """Every rank of a partitioned matrix must cut x into the same panels: the width depends on
+    the value size only (largest power of two whose x slice is at most 40 MB)."""
+    import torch
+
+    from flagsparse_b200 import _plan
+    assert _plan.panel_shift(torch.float64) == 22
+    assert _plan.panel_shift(torch.float32) == 23
+    assert _plan.panel_shift(torch.complex64) == 22
+    assert _plan.panel_shift(torch.complex128) == 21
+
+
+def test_panel_tile_bounds_give_a_straddling_tile_to_the_later_panel():
+    """Tiles launched behind the arrival of panel p's slice of x are those that need no x beyond
+    panel p; a tile that starts in one panel and ends in the next waits for the next."""
+    import torch
+
+    from flagsparse_b200._plan import StackLayout
+    tile, n_tiles = 256, 4
+    vals = torch.zeros(tile * n_tiles)
+    cols = torch.zeros(tile * n_tiles, dtype=torch.int32)
+    panel_start = torch.tensor([0, 300, 300, 1000], dtype=torch.int64)   # panel 1 is empty
+    lay = StackLayout(vals, cols, 10, torch.zeros(n_tiles + 1, dtype=torch.int64),
+                      torch.zeros(n_tiles, dtype=torch.int32), panel_start, 3, 4, None, tile)
+    # tile 0 = entries 0..255 lies in panel 0; tile 1 = 256..511 straddles panels 0 and 2
+    assert lay.panel_tile_bounds() == [1, 1, 4]
+    assert lay.panel_tile_bounds() is lay.panel_tile_bounds()          # read back once
