@@ -672,7 +672,7 @@ def cfg5_extra(args, rank, world, device, timed):
             try:    # collective: raises on every rank or on none
                 out_full = part.enable_peer_gather(g.data.dtype, trailing,
                                                    multicast=args.gather == "mc")
-                mode = "peer"
+                mode = args.gather
             except RuntimeError as exc:
                 print(f"[rank {rank}] cfg5 {kind}: {exc}", file=sys.stderr, flush=True)
         if out_full is None:
