@@ -74,3 +74,25 @@ def test_panel_tile_bounds_give_a_straddling_tile_to_the_later_panel():
     # tile 0 = entries 0..255 lies in panel 0; tile 1 = 256..511 straddles panels 0 and 2
     assert lay.panel_tile_bounds() == [1, 1, 4]
     assert lay.panel_tile_bounds() is lay.panel_tile_bounds()          # read back once
+
+
+def test_algorithmic_bytes_of_the_headline_configuration():
+    """The bench line's numerator: each array once at the caller's widths.  The headline
+    configuration (float64 / int64, 2^24 rows and columns, 268,532,588 non-zeros, beta != 0) is
+    4,833,392,328 bytes per product; SpMM N = 32 on the same matrix 13,020,673,736."""
+    import sys
+    from pathlib import Path
+
+    from flagsparse_b200 import workloads as W
+    n, nnz = 1 << 24, 268_532_588
+    assert W.spmv_bytes(n, n, nnz, 8, 8, 8, beta_nonzero=True) == 4_833_392_328
+    assert W.spmm_bytes(n, n, nnz, 32, 8, 8, 8, beta_nonzero=False) == 13_020_673_736
+    assert W.sp_flops(nnz) == 2 * nnz and W.sp_flops(10, 4, complex_values=True) == 320
+    # bench.problem_bytes_flops applies the same formulas to a problem object (CPU tensors)
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    p = W.cfg2_powerlaw_spmv(device="cpu", scale=4096)
+    p.extra.update(alpha=p.alpha, beta=p.beta, y0=p.y0, op="non")
+    nbytes, flops = bench.problem_bytes_flops(p, "spmv")
+    assert nbytes == W.spmv_bytes(p.shape[0], p.shape[1], p.nnz, 8, 8, 8, beta_nonzero=True)
+    assert flops == 2 * p.nnz
